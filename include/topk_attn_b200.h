@@ -1,0 +1,107 @@
+/*
+ * topk_attn_b200 — C ABI of the decode-time top-k sparse-attention path for NVIDIA B200
+ * (sm_100a).
+ *
+ * Every entry point is plain C: raw device pointers, sizes and a CUDA stream handle; no
+ * torch types, no exceptions, no exit().  Each returns an int status (RA_OK == 0,
+ * ra_strerror() gives the text).  Work is enqueued on the caller's stream and the call
+ * returns without synchronising; no entry point allocates device memory — scratch comes
+ * from a caller-provided workspace sized by ra_workspace_bytes().
+ *
+ * Tensor layouts are the reference project's:
+ *   q      fp16 [B, Hq, D]                       retrieval_attn/retrieval_attention.cu:257
+ *   k, v   fp16 [N, Hkv, D] token-major, one cache shared by all batch rows (kv_batch_stride
+ *          == 0), or one cache per batch row (kv_batch_stride != 0)        ...:258-259,282-284
+ *   out    fp16 [B, Hq, D]                                                  ...:260
+ *   centers fp16 [H, CSZ, D]                      center_only_topk/gemv_topk.cu:99
+ *   indices int32 [.., H, S] global token ids     gemv_topk.cu:373-377, flash_decoding.cu:105
+ * D must be 128 (the reference's only head size, retrieval_attention.cu:31).
+ */
+#ifndef TOPK_ATTN_B200_H_
+#define TOPK_ATTN_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RA_OK 0
+#define RA_ERR_INVALID_ARGUMENT 1   /* null pointer, bad shape, k > N, misaligned pointer */
+#define RA_ERR_UNSUPPORTED 2        /* head_dim != 128, sizes beyond what the kernels hold */
+#define RA_ERR_WORKSPACE 3          /* workspace missing or smaller than ra_workspace_bytes() */
+#define RA_ERR_CUDA 4               /* a CUDA runtime/driver call failed; see ra_last_cuda_error() */
+#define RA_ERR_DEVICE_TIMEOUT 5     /* a bounded wait inside a kernel gave up (ra_check_status) */
+#define RA_ERR_NOT_BUILT 6
+
+/* Operands of one decode step.  Unused optional pointers are NULL. */
+typedef struct ra_params {
+  const void* q;            /* fp16 [batch, num_q_heads, 128] contiguous */
+  const void* k;            /* fp16 key cache */
+  const void* v;            /* fp16 value cache, same strides as k */
+  void* out;                /* fp16 [batch, num_q_heads, 128]; may be NULL when only
+                               candidates/indices are wanted */
+  int32_t batch;
+  int32_t num_q_heads;
+  int32_t num_kv_heads;     /* divides num_q_heads; query head h reads kv head h / group */
+  int32_t head_dim;         /* 128 */
+  int32_t num_tokens;       /* N, tokens present in the cache (of this shard) */
+  int64_t kv_batch_stride;  /* elements between the caches of two batch rows; 0 = shared */
+  int64_t kv_token_stride;  /* elements between tokens (num_kv_heads*128 for [N,Hkv,D]) */
+  int64_t kv_head_stride;   /* elements between heads (128 for [N,Hkv,D]) */
+  int32_t topk;             /* keys kept per segment */
+  int32_t num_segments;     /* 1 = global top-k; 4 = the legacy per-chunk selection */
+  float sm_scale;           /* softmax(sm_scale * q.k); 1.0 reproduces exp(s)/sum exp(s) */
+  int32_t index_base;       /* added to reported token ids (shard offset) */
+  int32_t* out_indices;     /* optional int32 [batch, num_q_heads, num_segments*topk] */
+  float* out_scores;        /* optional fp32, same shape: raw q.k of each kept key */
+  float* out_lse;           /* optional fp32 [batch, num_q_heads, 2]: (max of sm_scale*s,
+                               sum of exp) of the kept keys */
+  void* workspace;          /* device scratch, 256-byte aligned */
+  size_t workspace_bytes;
+  void* stream;             /* cudaStream_t */
+} ra_params;
+
+const char* ra_strerror(int status);
+int ra_version(void);
+/* Text of the last failing CUDA call made by this library on the calling thread. */
+const char* ra_last_cuda_error(void);
+
+/* Scratch needed by ra_topk_attention / ra_gemv_topk for these operands (the largest any
+ * internal plan may use).  Replaces the per-call cudaMalloc of the reference's host runners
+ * (retrieval_attn/retrieval_attention.cu:1658-1659,1738-1741). */
+size_t ra_workspace_bytes(const ra_params* p);
+
+/* Fused decode step: scan K, keep the exact top-k per (batch row, query head[, segment]),
+ * softmax over the kept keys, mix their V rows.  One kernel when a thread-block cluster
+ * can cover a head's whole context, scan + merge kernels otherwise.
+ * Replaces launch_retrieval_attention*_K and run_retrieval_attention*<K>
+ * (retrieval_attn/retrieval_attention.cu:1389-2282) and the fused pipelines
+ * topk_attn_fused_kernel (baseline_2.cu:583-1058). */
+int ra_topk_attention(const ra_params* p);
+
+/* Selection only: out_indices (and out_scores) must be given, out/v are ignored.  The role of
+ * gemv_topk_kernel (gemv_topk.cu:173-380) with a global top-k over the N keys. */
+int ra_gemv_topk(const ra_params* p);
+
+/* After the stream has been synchronised by the caller: RA_OK, or RA_ERR_DEVICE_TIMEOUT if a
+ * kernel that used this workspace abandoned a bounded wait.  Synchronises the stream itself. */
+int ra_check_status(void* workspace, void* stream);
+
+/* The reference extension's entry points (retrieval_attn/bind.cpp:5-243 declare
+ * launch_retrieval_attention{,_global,_pipelined,_pipelined_global,_two_kernels,
+ * _gather_baseline}_{32,128,256,512,1024}(q, k, v, out, batch)): N = num_tokens keys in a shared
+ * [N,32,128] cache cut in 4 chunks, top-K per chunk, raw-exp softmax, no scale.
+ * variant: 0 fused, 1 global-scratch, 2 pipelined, 3 pipelined-global, 4 two kernels,
+ * 5 gather + dense baseline; all variants return the same result. */
+int ra_legacy_retrieval_attention(const void* q, const void* k, const void* v, void* out,
+                                  int32_t batch, int32_t num_tokens, int32_t topk_per_chunk,
+                                  int32_t variant, void* workspace, size_t workspace_bytes,
+                                  void* stream);
+size_t ra_legacy_workspace_bytes(int32_t batch, int32_t num_tokens, int32_t topk_per_chunk);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TOPK_ATTN_B200_H_ */

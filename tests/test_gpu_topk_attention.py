@@ -1,0 +1,178 @@
+"""GPU parity of the fused scan + top-k + softmax.V path, called through the C ABI."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import topk_attn_oracle as O
+from topk_attn_b200 import workloads as W
+
+from gpu_util import check_topk_attention, rand_case
+
+pytestmark = pytest.mark.gpu
+
+
+def test_config0_reference_cpu_case():
+    w = W.reference_cpu_case()
+    check_topk_attention(w.q, w.k, w.v, w.topk, w.sm_scale)
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,N,k,per_batch", [
+    (1, 8, 8, 1024, 64, False),
+    (2, 8, 8, 5000, 300, True),        # ragged N: not a multiple of any tile
+    (2, 8, 2, 4096, 128, False),       # GQA 4 and a shared cache: 8 queries per K row
+    (1, 32, 8, 65536, 1024, False),    # GQA, context split over several clusters
+    (4, 32, 32, 16384, 512, False),    # shared cache MHA, batch scored together
+    (3, 4, 4, 777, 777, True),         # k == N, odd batch
+    (1, 1, 1, 1, 1, False),            # single key
+    (1, 2, 1, 130, 1, False),          # k == 1
+    (2, 16, 16, 40000, 2048, True),
+    (1, 8, 1, 3000, 100, False),       # 8 query heads on one kv head
+    (5, 6, 3, 2049, 33, False),        # batch that does not share evenly
+])
+def test_random_shapes(B, Hq, Hkv, N, k, per_batch):
+    q, k_, v = rand_case(B, Hq, Hkv, N, per_batch, seed=N + k)
+    check_topk_attention(q, k_, v, k, sm_scale=1.0)
+
+
+@pytest.mark.parametrize("scale", [0.25, 1.0 / math.sqrt(128), 2.0])
+def test_softmax_scale(scale):
+    q, k, v = rand_case(2, 8, 8, 4096, True, seed=5)
+    check_topk_attention(q, k, v, 256, sm_scale=scale)
+
+
+def test_index_base_is_added():
+    q, k, v = rand_case(1, 8, 8, 2048, False, seed=7)
+    check_topk_attention(q, k, v, 64, index_base=1 << 20)
+
+
+@pytest.mark.parametrize("topk", [32, 128, 1024])
+def test_segmented_selection(topk):
+    q, k, v = rand_case(2, 32, 32, 8192, False, seed=topk)
+    q = (q.float() * 3).half()
+    check_topk_attention(q, k, v, topk, num_segments=4)
+
+
+def test_ties_everywhere():
+    """All keys identical: any k distinct keys are a valid selection.  The output must be the
+    attention over exactly the keys that were reported."""
+    from topk_attn_b200 import ops
+    q = torch.ones(1, 4, 128).half() * 0.1
+    k = torch.ones(512, 4, 128).half()
+    v = torch.randn(512, 4, 128, generator=torch.Generator().manual_seed(1)).half()
+    dev = torch.device("cuda:0")
+    out, idx, sc = ops.topk_attention(q.to(dev), k.to(dev), v.to(dev), 100, return_indices=True)
+    ops.check_status(dev)
+    s = O.full_scores(q, k)
+    O.check_index_sets(s, idx.cpu(), 100)
+    O.check_topk_scores(s, idx.cpu(), sc.cpu(), 100)
+    O.check_output(O.gathered_attention(q, k, v, idx.cpu().long(), 1.0), out)
+
+
+def test_ascending_scores_worst_case_for_the_filter():
+    """Scores rise with the token index, so every key beats the running threshold and the
+    candidate lists are cut back as often as they can be."""
+    N = 20000
+    q = torch.zeros(1, 2, 128)
+    q[:, :, 0] = 1.0
+    k = torch.zeros(N, 2, 128)
+    k[:, 0, 0] = torch.linspace(-4, 4, N)
+    k[:, 1, 0] = torch.linspace(4, -4, N)          # descending on the other head
+    k[:, :, 1:] = torch.randn(N, 2, 127, generator=torch.Generator().manual_seed(2))
+    v = torch.randn(N, 2, 128, generator=torch.Generator().manual_seed(3))
+    # fp16 rounds neighbouring scores to the same value, so the boundary of the selection is a
+    # run of exact ties: check the selection by the band rule and the output against attention
+    # over the keys that were reported
+    from topk_attn_b200 import ops
+    dev = torch.device("cuda:0")
+    q, k, v = q.half(), k.half(), v.half()
+    out, idx, sc = ops.topk_attention(q.to(dev), k.to(dev), v.to(dev), 512, return_indices=True)
+    ops.check_status(dev)
+    s = O.full_scores(q, k)
+    O.check_index_sets(s, idx.cpu(), 512)
+    O.check_topk_scores(s, idx.cpu(), sc.cpu(), 512)
+    O.check_output(O.gathered_attention(q, k, v, idx.cpu().long(), 1.0), out)
+    top = idx.cpu()[0, 0].sort().values
+    assert top.min().item() >= N - 600
+
+
+def test_infinite_and_nan_keys():
+    """+inf scores are kept first, -inf never; NaN sorts above everything as in torch.topk."""
+    from topk_attn_b200 import ops
+    q, k, v = rand_case(1, 2, 2, 1024, False, seed=11)
+    k[5, 0, :] = float("inf") * torch.sign(q[0, 0].float()).half()     # score +inf on head 0
+    k[9, 0, :] = -float("inf") * torch.sign(q[0, 0].float()).half()    # score -inf on head 0
+    dev = torch.device("cuda:0")
+    idx, sc = ops.gemv_topk(q.to(dev), k.to(dev), 16)
+    ops.check_status(dev)
+    i0 = set(idx[0, 0].cpu().tolist())
+    assert 5 in i0 and 9 not in i0
+    s = O.full_scores(q, k)
+    ref = set(torch.topk(torch.nan_to_num(s[0, 1], nan=float("inf")), 16).indices.tolist())
+    assert set(idx[0, 1].cpu().tolist()) == ref
+
+
+def test_selection_only_matches_fused_lists():
+    from topk_attn_b200 import ops
+    q, k, v = rand_case(2, 8, 8, 30000, True, seed=13)
+    dev = torch.device("cuda:0")
+    idx, sc = ops.gemv_topk(q.to(dev), k.to(dev), 700)
+    ops.check_status(dev)
+    s = O.full_scores(q, k)
+    O.check_index_sets(s, idx.cpu(), 700)
+    O.check_topk_scores(s, idx.cpu(), sc.cpu(), 700)
+
+
+def test_repeat_gives_same_selection_and_close_output():
+    from topk_attn_b200 import ops
+    q, k, v = rand_case(2, 8, 8, 20000, True, seed=17)
+    dev = torch.device("cuda:0")
+    a = ops.topk_attention(q.to(dev), k.to(dev), v.to(dev), 512, return_indices=True)
+    b = ops.topk_attention(q.to(dev), k.to(dev), v.to(dev), 512, return_indices=True)
+    ops.check_status(dev)
+    assert torch.equal(a[1].sort(-1).values, b[1].sort(-1).values)
+    assert torch.allclose(a[0].float(), b[0].float(), atol=1e-3, rtol=1e-2)
+
+
+def test_golden_legacy_outputs(golden_dir):
+    """The reference extension's own test shape (B=4, N=8192, 4 chunks) against the vectors its
+    torch oracle produced, through the legacy C entry point."""
+    import ctypes as C
+    import os
+    from topk_attn_b200 import capi, ops
+    w = W.legacy_test_case()
+    g = np.load(os.path.join(golden_dir, "legacy_retrieval_attention.npz"))
+    dev = torch.device("cuda:0")
+    q, k, v = w.q.to(dev), w.k.to(dev), w.v.to(dev)
+    lib = capi.lib()
+    for variant, topk in [(0, 32), (1, 128), (2, 256), (3, 512), (4, 1024), (5, 128)]:
+        out = torch.zeros_like(q)
+        need = lib.ra_legacy_workspace_bytes(4, 8192, topk)
+        ws = ops.workspace(need, dev)
+        st = lib.ra_legacy_retrieval_attention(q.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                               out.data_ptr(), 4, 8192, topk, variant,
+                                               ws.data_ptr(), ws.numel(),
+                                               torch.cuda.current_stream().cuda_stream)
+        capi.check(st)
+        ops.check_status(dev)
+        ref = torch.from_numpy(g[f"out_{topk}"])
+        O.check_output(ref, out)
+        assert (out.float().cpu() - ref).abs().max().item() < 1e-2      # the reference's own bar
+
+
+def test_bad_arguments_are_rejected():
+    import ctypes as C
+    from topk_attn_b200 import capi, ops
+    q, k, v = rand_case(1, 8, 8, 1024, False)
+    dev = torch.device("cuda:0")
+    with pytest.raises(capi.RaError) as e:
+        ops.topk_attention(q.to(dev), k.to(dev), v.to(dev), 2000)       # k > N
+    assert e.value.status == capi.RA_ERR_INVALID_ARGUMENT
+    with pytest.raises(capi.RaError):
+        ops.topk_attention(q.to(dev), k.to(dev), v.to(dev), 64, num_segments=3)   # 1024 % 3
+    with pytest.raises(capi.RaError):
+        ops.topk_attention(q.to(dev), k.to(dev), v.to(dev), 64, sm_scale=0.0)
+    p = capi.RaParams()
+    assert capi.lib().ra_topk_attention(C.byref(p)) != capi.RA_OK
+    assert capi.lib().ra_topk_attention(None) == capi.RA_ERR_INVALID_ARGUMENT

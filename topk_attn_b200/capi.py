@@ -1,0 +1,83 @@
+"""ctypes binding of the C ABI declared in include/topk_attn_b200.h.
+
+The library is the product: if it has not been built (``python -m topk_attn_b200.build``) the
+import of any operator fails loudly; there is no Python or CPU fallback.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "lib", "libtopk_attn_b200.so")
+
+RA_OK = 0
+RA_ERR_INVALID_ARGUMENT = 1
+RA_ERR_UNSUPPORTED = 2
+RA_ERR_WORKSPACE = 3
+RA_ERR_CUDA = 4
+RA_ERR_DEVICE_TIMEOUT = 5
+
+
+class RaParams(C.Structure):
+    """Mirror of ``struct ra_params``."""
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("out", C.c_void_p),
+        ("batch", C.c_int32), ("num_q_heads", C.c_int32), ("num_kv_heads", C.c_int32),
+        ("head_dim", C.c_int32), ("num_tokens", C.c_int32),
+        ("kv_batch_stride", C.c_int64), ("kv_token_stride", C.c_int64),
+        ("kv_head_stride", C.c_int64),
+        ("topk", C.c_int32), ("num_segments", C.c_int32), ("sm_scale", C.c_float),
+        ("index_base", C.c_int32),
+        ("out_indices", C.c_void_p), ("out_scores", C.c_void_p), ("out_lse", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("stream", C.c_void_p),
+    ]
+
+
+class RaError(RuntimeError):
+    def __init__(self, status: int, text: str, detail: str = ""):
+        super().__init__(f"topk_attn_b200: {text} (status {status})" + (f": {detail}" if detail else ""))
+        self.status = status
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(
+                f"{LIB_PATH} is missing: build it with `python -m topk_attn_b200.build` "
+                "(nvcc, sm_100a). There is no fallback implementation.")
+        _lib = C.CDLL(LIB_PATH)
+        _declare(_lib)
+    return _lib
+
+
+def _declare(l: C.CDLL) -> None:
+    P = C.POINTER(RaParams)
+    vp, i32, sz, f32 = C.c_void_p, C.c_int32, C.c_size_t, C.c_float
+    sigs = {
+        "ra_strerror": (C.c_char_p, [C.c_int]),
+        "ra_version": (C.c_int, []),
+        "ra_last_cuda_error": (C.c_char_p, []),
+        "ra_workspace_bytes": (sz, [P]),
+        "ra_topk_attention": (C.c_int, [P]),
+        "ra_gemv_topk": (C.c_int, [P]),
+        "ra_check_status": (C.c_int, [vp, vp]),
+        "ra_legacy_retrieval_attention": (C.c_int, [vp, vp, vp, vp, i32, i32, i32, i32, vp, sz, vp]),
+        "ra_legacy_workspace_bytes": (sz, [i32, i32, i32]),
+    }
+    for name, (res, args) in sigs.items():
+        if not hasattr(l, name):
+            continue
+        fn = getattr(l, name)
+        fn.restype = res
+        fn.argtypes = args
+
+
+def check(status: int) -> None:
+    if status != RA_OK:
+        l = lib()
+        raise RaError(status, l.ra_strerror(status).decode(), l.ra_last_cuda_error().decode())

@@ -1,0 +1,456 @@
+// Host side of the C ABI: argument validation, launch planning, tensor-map encoding and kernel
+// launches.  Nothing here allocates device memory or synchronises (ra_check_status excepted).
+#include "topk_attn_b200.h"
+
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <string>
+#include <tuple>
+
+#include "merge_attend.cuh"
+#include "scan_select.cuh"
+
+namespace ra {
+int scan_max_active_clusters(int hg, int nq, int cluster, size_t smem);
+}
+
+namespace {
+
+using namespace ra;
+
+thread_local std::string g_last_error;
+
+int cuda_fail(cudaError_t e, const char* what) {
+  g_last_error = std::string(what) + ": " + cudaGetErrorString(e);
+  (void)cudaGetLastError();
+  return RA_ERR_CUDA;
+}
+int invalid(const char* why) {
+  g_last_error = why;
+  return RA_ERR_INVALID_ARGUMENT;
+}
+int unsupported(const char* why) {
+  g_last_error = why;
+  return RA_ERR_UNSUPPORTED;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+constexpr size_t kSmemBudget = 227 * 1024;
+constexpr size_t kStatusBytes = 256;
+constexpr int kMaxSplit = 16;  // parts one head's context may be cut into
+
+struct Plan {
+  bool ok = false;
+  int hg = 0, nq = 0, bshare = 1, nq_valid = 1;
+  int cluster = 1, nsplit = 1, cap = 0, nstages = 0, per = 0, part_len = 0, grid = 0;
+  size_t smem = 0;
+  // second stage (only when parts > 1)
+  int cluster2 = 1, cap2 = 0, per2 = 0;
+  size_t smem2 = 0;
+  double cost = 0;
+};
+
+struct Shape {
+  int batch, hq, hkv, n, topk, segments, per_batch, head_major, fused_ok;
+  bool operator<(const Shape& o) const {
+    return std::tie(batch, hq, hkv, n, topk, segments, per_batch, head_major, fused_ok) <
+           std::tie(o.batch, o.hq, o.hkv, o.n, o.topk, o.segments, o.per_batch, o.head_major,
+                    o.fused_ok);
+  }
+};
+
+int next_pow2(int x) {
+  int p = 1;
+  while (p < x) p <<= 1;
+  return p;
+}
+
+bool combo_built(int hg, int nq) {
+  static const int ok[][2] = {{1, 1}, {2, 1}, {4, 1}, {8, 1}, {1, 2}, {2, 2}, {4, 2}, {1, 4}, {2, 4}, {1, 8}};
+  for (auto& c : ok)
+    if (c[0] == hg && c[1] == nq) return true;
+  return false;
+}
+
+// Second-stage geometry for m_total candidates per row with `topk` winners.
+bool plan_merge(int m_total, int topk, Plan& pl) {
+  for (int c2 : {1, 2, 4, 8}) {
+    const int cap2 = ceil_div(m_total, c2), per2 = ceil_div(topk, c2);
+    const size_t smem2 = merge_attend_smem_bytes(per2, cap2);
+    if (smem2 > kSmemBudget) continue;
+    // prefer enough CTAs per row to keep the gather short, but never more than needed
+    if (cap2 > 4096 && c2 < 8) continue;
+    pl.cluster2 = c2;
+    pl.cap2 = cap2;
+    pl.per2 = per2;
+    pl.smem2 = smem2;
+    return true;
+  }
+  return false;
+}
+
+// Pick the launch geometry with the lowest modelled time.  The model: every CTA streams its
+// slab at min(per-SM rate, its fair share of HBM); clusters that do not fit at once run in
+// waves; a second kernel costs a fixed latency.
+Plan make_plan(const Shape& s) {
+  static std::mutex mu;
+  static std::map<Shape, Plan> cache;
+  {
+    std::lock_guard<std::mutex> g(mu);
+    auto it = cache.find(s);
+    if (it != cache.end()) return it->second;
+  }
+  Plan best;
+  const int group = s.hq / s.hkv;
+  int bshare = 1;
+  if (!s.per_batch) {
+    for (int b = 1; b <= s.batch; ++b)
+      if (s.batch % b == 0 && b * group <= 8) bshare = b;
+  }
+  const int nq_valid = bshare * group;
+  const int nq = next_pow2(nq_valid);
+  const int seg_len = s.n / s.segments;
+  const double hbm = 6.5e12, per_sm = 75e9;
+  for (int hg : {8, 4, 2, 1}) {
+    if (s.hkv % hg || !combo_built(hg, nq)) continue;
+    if (s.head_major && hg != 1) continue;
+    const int nl = hg * nq, T = kTileRows / hg;
+    const int groups = (s.batch / bshare) * (s.hkv / hg) * s.segments;
+    for (int cluster : {1, 2, 4, 8, 16}) {
+      for (int nsplit = 1; nsplit <= kMaxSplit; ++nsplit) {
+        if (nsplit > 1 && s.segments > 1) break;
+        int part_len = ceil_div(ceil_div(seg_len, nsplit), T) * T;
+        if (nsplit > 1 && part_len < s.topk) break;           // every part must hold k keys
+        if (nsplit > 1 && part_len * (nsplit - 1) >= seg_len) continue;  // empty last part
+        if (nsplit == 1) part_len = seg_len;
+        const int tiles = ceil_div(part_len, T);
+        if (cluster > 1 && tiles < cluster) continue;
+        const int per = ceil_div(s.topk, cluster);
+        const size_t scratch = merge_scratch_bytes(nl, per);
+        // stages and list capacity within the shared-memory budget
+        int nstages = 0, cap = 0;
+        for (int st = kMaxStages; st >= 3; --st) {
+          if ((size_t)st * kStageBytes < scratch) break;
+          const size_t fixed = scan_smem_bytes(nl, 0, st);
+          if (fixed >= kSmemBudget) continue;
+          int c = (int)((kSmemBudget - fixed) / ((size_t)nl * 8));
+          c = std::min(c, 2 * s.topk + 2 * T);
+          const int want = (st > 4) ? (3 * s.topk) / 2 + 2 * T : s.topk + 2 * T + 64;
+          if (c >= std::min(want, 2 * s.topk + 2 * T)) {
+            nstages = st;
+            cap = c;
+            break;
+          }
+        }
+        if (!nstages) continue;
+        const size_t smem = scan_smem_bytes(nl, cap, nstages);
+        const int nclusters = groups * nsplit;
+        const int active = scan_max_active_clusters(hg, nq, cluster, smem);
+        if (active <= 0) continue;
+        const int waves = ceil_div(nclusters, active);
+        const int live = std::min(nclusters, active) * cluster;
+        const double bytes_cta = (double)ceil_div(tiles, cluster) * kStageBytes;
+        const double rate = std::min(per_sm, hbm / live) * (hg * kRowBytes >= 1024 ? 1.0 : 0.93);
+        const bool two_stage = nsplit > 1 || s.segments > 1 || !s.fused_ok;
+        double cost = waves * (bytes_cta / rate + 6e-6 + 1.5e-6 * cluster) + (two_stage ? 8e-6 : 0.0);
+        Plan pl;
+        pl.hg = hg; pl.nq = nq; pl.bshare = bshare; pl.nq_valid = nq_valid;
+        pl.cluster = cluster; pl.nsplit = nsplit; pl.cap = cap; pl.nstages = nstages;
+        pl.per = per; pl.part_len = part_len; pl.grid = nclusters * cluster; pl.smem = smem;
+        pl.cost = cost;
+        if (two_stage && !plan_merge(s.segments * nsplit * s.topk,
+                                     s.segments > 1 ? s.segments * s.topk : s.topk, pl))
+          continue;
+        pl.ok = true;
+        if (!best.ok || pl.cost < best.cost) best = pl;
+      }
+    }
+  }
+  std::lock_guard<std::mutex> g(mu);
+  cache[s] = best;
+  return best;
+}
+
+struct Checked {
+  Shape shape;
+  int group;
+};
+
+int check_shape(const ra_params* p, Checked& c) {
+  if (!p) return invalid("params is null");
+  if (p->head_dim != kHeadDim) return unsupported("head_dim must be 128");
+  if (p->batch < 1 || p->num_q_heads < 1 || p->num_kv_heads < 1 || p->num_tokens < 1)
+    return invalid("batch, heads and num_tokens must be positive");
+  if (p->num_q_heads % p->num_kv_heads) return invalid("num_kv_heads must divide num_q_heads");
+  c.group = p->num_q_heads / p->num_kv_heads;
+  if (c.group > 8) return unsupported("more than 8 query heads per kv head");
+  if (p->num_segments < 1 || p->num_tokens % p->num_segments)
+    return invalid("num_tokens must be a multiple of num_segments");
+  if (p->topk < 1 || p->topk > p->num_tokens / p->num_segments)
+    return invalid("topk must be in [1, tokens per segment]");
+  if (p->topk > 8192) return unsupported("topk above 8192");
+  if (p->kv_token_stride < kHeadDim || p->kv_head_stride < kHeadDim || (p->kv_token_stride % 8) ||
+      (p->kv_head_stride % 8) || (p->kv_batch_stride % 8) || p->kv_batch_stride < 0)
+    return invalid("kv strides must be multiples of 8 elements and at least 128");
+  c.shape.batch = p->batch;
+  c.shape.hq = p->num_q_heads;
+  c.shape.hkv = p->num_kv_heads;
+  c.shape.n = p->num_tokens;
+  c.shape.topk = p->topk;
+  c.shape.segments = p->num_segments;
+  c.shape.per_batch = p->kv_batch_stride != 0;
+  c.shape.head_major = p->kv_head_stride > p->kv_token_stride;
+  c.shape.fused_ok = 1;
+  return RA_OK;
+}
+
+int check_params(const ra_params* p, bool need_v, bool need_out, Checked& c) {
+  int st = check_shape(p, c);
+  if (st != RA_OK) return st;
+  if (!p->q || !p->k) return invalid("q or k is null");
+  if (need_v && !p->v) return invalid("v is null");
+  if (need_out && !p->out) return invalid("out is null");
+  auto mis = [](const void* x) { return (reinterpret_cast<uintptr_t>(x) & 15u) != 0; };
+  if (mis(p->q) || mis(p->k) || (p->v && mis(p->v)) || (p->out && mis(p->out)))
+    return invalid("q, k, v and out must be 16-byte aligned");
+  if (!(p->sm_scale > 0.f)) return invalid("sm_scale must be positive");
+  if (!p->workspace) {
+    g_last_error = "workspace is null";
+    return RA_ERR_WORKSPACE;
+  }
+  if (reinterpret_cast<uintptr_t>(p->workspace) & 255u) return invalid("workspace must be 256-byte aligned");
+  return RA_OK;
+}
+
+// Device-independent upper bound of the scratch any plan for this shape may use.
+size_t workspace_bound(const Shape& s) {
+  const int seg_len = s.n / s.segments;
+  int maxsplit = 1;
+  if (s.segments == 1) maxsplit = std::max(1, std::min(kMaxSplit, seg_len / std::max(s.topk, 128)));
+  size_t w = kStatusBytes + (size_t)s.batch * s.hq * s.segments * maxsplit * s.topk * 8;
+  return (w + 255) & ~size_t(255);
+}
+
+int encode_kmap(CUtensorMap* map, const ra_params* p, const Shape& s, int hg) {
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) {
+    g_last_error = "cuTensorMapEncodeTiled is not available from the driver";
+    return RA_ERR_CUDA;
+  }
+  const cuuint64_t nb = s.per_batch ? (cuuint64_t)p->batch : 1;
+  const cuuint64_t bstride =
+      s.per_batch ? (cuuint64_t)p->kv_batch_stride * 2
+                  : (cuuint64_t)16 * (((cuuint64_t)p->num_tokens * p->kv_token_stride * 2 + 15) / 16);
+  cuuint64_t dims[4], strides[3];
+  cuuint32_t box[4], estr[4] = {1, 1, 1, 1};
+  const int T = kTileRows / hg;
+  if (s.head_major) {
+    dims[0] = kHeadDim; dims[1] = p->num_tokens; dims[2] = p->num_kv_heads; dims[3] = nb;
+    strides[0] = (cuuint64_t)p->kv_token_stride * 2; strides[1] = (cuuint64_t)p->kv_head_stride * 2;
+    box[0] = kHeadDim; box[1] = T; box[2] = 1; box[3] = 1;
+  } else {
+    dims[0] = kHeadDim; dims[1] = p->num_kv_heads; dims[2] = p->num_tokens; dims[3] = nb;
+    strides[0] = (cuuint64_t)p->kv_head_stride * 2; strides[1] = (cuuint64_t)p->kv_token_stride * 2;
+    box[0] = kHeadDim; box[1] = hg; box[2] = T; box[3] = 1;
+  }
+  strides[2] = bstride;
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(p->k), dims, strides,
+                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    char buf[96];
+    snprintf(buf, sizeof buf, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    g_last_error = buf;
+    return RA_ERR_CUDA;
+  }
+  return RA_OK;
+}
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+// attend == false: selection only (indices/scores out).
+int run(const ra_params* p, bool attend) {
+  Checked c;
+  int st = check_params(p, attend, attend, c);
+  if (st != RA_OK) return st;
+  if (!attend && !p->out_indices) return invalid("out_indices is required");
+  Shape s = c.shape;
+  s.fused_ok = 1;
+  const Plan pl = make_plan(s);
+  if (!pl.ok) return unsupported("no launch geometry fits these sizes");
+  static const bool verbose = getenv("RA_VERBOSE") != nullptr;
+  static thread_local Shape last_shown = {};
+  const bool show = verbose && ((last_shown < s) || (s < last_shown));
+  if (show) last_shown = s;
+  if (show)
+    fprintf(stderr,
+            "[topk_attn_b200] plan: hg=%d nq=%d(valid %d) bshare=%d cluster=%d nsplit=%d cap=%d "
+            "stages=%d per=%d part_len=%d grid=%d smem=%zu | merge: cluster=%d cap=%d smem=%zu | "
+            "model %.1f us\n",
+            pl.hg, pl.nq, pl.nq_valid, pl.bshare, pl.cluster, pl.nsplit, pl.cap, pl.nstages, pl.per,
+            pl.part_len, pl.grid, pl.smem, pl.cluster2, pl.cap2, pl.smem2, pl.cost * 1e6);
+  if (p->workspace_bytes < workspace_bound(s)) {
+    g_last_error = "workspace smaller than ra_workspace_bytes()";
+    return RA_ERR_WORKSPACE;
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
+  unsigned* status = static_cast<unsigned*>(p->workspace);
+  const int parts = s.segments * pl.nsplit;
+  const bool two_stage = parts > 1;
+  float* ws_score = reinterpret_cast<float*>(static_cast<char*>(p->workspace) + kStatusBytes);
+  int* ws_idx = reinterpret_cast<int*>(ws_score + (size_t)s.batch * s.hq * parts * s.topk);
+
+  ScanParams sp;
+  memset(&sp, 0, sizeof sp);
+  st = encode_kmap(&sp.kmap, p, s, pl.hg);
+  if (st != RA_OK) return st;
+  sp.q = static_cast<const __half*>(p->q);
+  sp.status = status;
+  sp.batch = s.batch; sp.hq = s.hq; sp.hkv = s.hkv; sp.n_tokens = s.n;
+  sp.group = c.group; sp.bshare = pl.bshare; sp.nq_valid = pl.nq_valid;
+  sp.kv_per_batch = s.per_batch;
+  sp.cap = pl.cap; sp.nstages = pl.nstages; sp.nparts = parts; sp.part_len = pl.part_len;
+  sp.head_major = s.head_major;
+  MergeArgs& m = sp.m;
+  m.topk = s.topk; m.per = pl.per; m.cluster = pl.cluster;
+  m.hq_total = s.hq; m.list_pitch = parts * s.topk; m.list_off = 0;
+  m.index_base = two_stage ? 0 : p->index_base;
+  m.own_lo = 0; m.own_hi = 0x7fffffff; m.id_shift = 0;
+  m.v = static_cast<const __half*>(p->v);
+  m.v_batch_stride = p->kv_batch_stride; m.v_token_stride = p->kv_token_stride;
+  m.v_head_stride = p->kv_head_stride;
+  m.out = static_cast<__half*>(p->out);
+  m.out_lse = p->out_lse; m.out_partial = nullptr;
+  m.scale_log2e = p->sm_scale * kLog2e; m.sm_scale = p->sm_scale;
+  // Per-chunk selection (segments > 1): every chunk's winners are final, so the scan writes
+  // them straight into the caller's lists when given and the second stage only mixes V.
+  const bool lists_final = s.segments > 1;
+  if (two_stage) {
+    m.out_mode = kOutNone;
+    m.sel_idx = (lists_final && p->out_indices) ? p->out_indices : ws_idx;
+    m.sel_score = (lists_final && p->out_scores) ? p->out_scores : ws_score;
+    if (lists_final) m.index_base = p->index_base;
+  } else {
+    m.out_mode = attend ? kOutFinal : kOutNone;
+    m.sel_idx = p->out_indices; m.sel_score = p->out_scores;
+  }
+  cudaError_t e = launch_scan_select(sp, pl.hg, pl.nq, pl.grid, pl.smem, stream);
+  if (e != cudaSuccess) return cuda_fail(e, "scan_select launch");
+  if (!two_stage) return RA_OK;
+
+  if (lists_final && !attend) return RA_OK;
+  MergeParams mp;
+  memset(&mp, 0, sizeof mp);
+  mp.m = sp.m;
+  mp.m.topk = lists_final ? s.segments * s.topk : s.topk;
+  mp.m.per = pl.per2; mp.m.cluster = pl.cluster2;
+  mp.m.list_pitch = mp.m.topk; mp.m.list_off = 0;
+  mp.m.out_mode = attend ? kOutFinal : kOutNone;
+  if (lists_final) {
+    // ids in the lists already carry index_base; nothing more to write
+    mp.m.index_base = 0;
+    mp.m.own_lo = p->index_base; mp.m.id_shift = p->index_base;
+    mp.m.sel_idx = nullptr; mp.m.sel_score = nullptr;
+  } else {
+    mp.m.index_base = p->index_base;
+    mp.m.sel_idx = p->out_indices; mp.m.sel_score = p->out_scores;
+  }
+  mp.cand_score = sp.m.sel_score; mp.cand_idx = sp.m.sel_idx;
+  mp.m_total = parts * s.topk; mp.cap = pl.cap2; mp.group = c.group;
+  e = launch_merge_attend(mp, s.batch * s.hq, pl.smem2, stream);
+  if (e != cudaSuccess) return cuda_fail(e, "merge_attend launch");
+  return RA_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* ra_strerror(int status) {
+  switch (status) {
+    case RA_OK: return "ok";
+    case RA_ERR_INVALID_ARGUMENT: return "invalid argument";
+    case RA_ERR_UNSUPPORTED: return "unsupported configuration";
+    case RA_ERR_WORKSPACE: return "workspace missing or too small";
+    case RA_ERR_CUDA: return "CUDA call failed";
+    case RA_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait gave up";
+    case RA_ERR_NOT_BUILT: return "not built";
+    default: return "unknown status";
+  }
+}
+
+int ra_version(void) { return 100; }
+
+const char* ra_last_cuda_error(void) { return g_last_error.c_str(); }
+
+size_t ra_workspace_bytes(const ra_params* p) {
+  Checked c;
+  if (check_shape(p, c) != RA_OK) return 0;
+  return workspace_bound(c.shape);
+}
+
+int ra_topk_attention(const ra_params* p) { return run(p, true); }
+
+int ra_gemv_topk(const ra_params* p) { return run(p, false); }
+
+int ra_check_status(void* workspace, void* stream) {
+  if (!workspace) return RA_ERR_WORKSPACE;
+  unsigned h = 0;
+  cudaError_t e = cudaMemcpyAsync(&h, workspace, sizeof h, cudaMemcpyDeviceToHost,
+                                  static_cast<cudaStream_t>(stream));
+  if (e == cudaSuccess) e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "ra_check_status");
+  return (h & ra::kStatusTimeout) ? RA_ERR_DEVICE_TIMEOUT : RA_OK;
+}
+
+static void legacy_params(ra_params* p, const void* q, const void* k, const void* v, void* out,
+                          int32_t batch, int32_t num_tokens, int32_t topk, void* ws, size_t wsb,
+                          void* stream) {
+  memset(p, 0, sizeof *p);
+  p->q = q; p->k = k; p->v = v; p->out = out;
+  p->batch = batch; p->num_q_heads = 32; p->num_kv_heads = 32; p->head_dim = 128;
+  p->num_tokens = num_tokens;
+  p->kv_batch_stride = 0; p->kv_token_stride = 32 * 128; p->kv_head_stride = 128;
+  p->topk = topk; p->num_segments = 4; p->sm_scale = 1.0f;
+  p->workspace = ws; p->workspace_bytes = wsb; p->stream = stream;
+}
+
+int ra_legacy_retrieval_attention(const void* q, const void* k, const void* v, void* out,
+                                  int32_t batch, int32_t num_tokens, int32_t topk_per_chunk,
+                                  int32_t variant, void* workspace, size_t workspace_bytes,
+                                  void* stream) {
+  if (variant < 0 || variant > 5) return invalid("variant must be 0..5");
+  ra_params p;
+  legacy_params(&p, q, k, v, out, batch, num_tokens, topk_per_chunk, workspace, workspace_bytes,
+                stream);
+  return ra_topk_attention(&p);
+}
+
+size_t ra_legacy_workspace_bytes(int32_t batch, int32_t num_tokens, int32_t topk_per_chunk) {
+  ra_params p;
+  legacy_params(&p, reinterpret_cast<void*>(uintptr_t(256)), reinterpret_cast<void*>(uintptr_t(256)),
+                reinterpret_cast<void*>(uintptr_t(256)), reinterpret_cast<void*>(uintptr_t(256)), batch,
+                num_tokens, topk_per_chunk, nullptr, 0, nullptr);
+  return ra_workspace_bytes(&p);
+}
+
+}  // extern "C"

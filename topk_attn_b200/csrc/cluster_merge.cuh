@@ -1,0 +1,373 @@
+// Cluster-wide exact k-select over per-CTA candidate lists held in shared memory, followed by
+// either writing the winners out or softmax.V over them.  Shared by the scan kernel (lists
+// filled while streaming K) and the merge kernel (lists loaded from global candidate buffers).
+//
+// All CTAs of the cluster run the same code.  Histograms, counts, winners and partial outputs
+// cross CTAs through distributed shared memory between hardware cluster barriers; there are no
+// polled flags (the reference hands scores to a consumer CTA that spins on a counter,
+// retrieval_attn/retrieval_attention.cu:381-394, and reduces max/sum with 2(C-1) cluster
+// barriers, baseline_1.cu:549-588).
+#pragma once
+#include <cooperative_groups.h>
+
+#include "common.cuh"
+
+namespace ra {
+
+namespace cg = cooperative_groups;
+
+struct MergeScratch {
+  int hist[2][kMaxLists][256];
+  int ghist[kMaxLists][256];
+  uint32_t prefix[kMaxLists];
+  int remaining[kMaxLists];
+  uint32_t counts[kMaxLists][4];  // n_gt, n_eq, best key — read by the other CTAs
+  int ctr_gt[kMaxLists], ctr_eq[kMaxLists];
+  int off_gt[kMaxLists], off_eq[kMaxLists], take_eq[kMaxLists], total_sel[kMaxLists];
+  uint32_t maxkey[kMaxLists];
+  float red[kWarps][kHeadDim];
+  float lred[kWarps];
+  float o_part[kMaxLists][kHeadDim];  // read by the other CTAs
+  float l_part[kMaxLists];            // read by the other CTAs
+};
+
+enum OutMode : int {
+  kOutNone = 0,     // only the winner lists are written
+  kOutFinal = 1,    // normalised fp16 output
+  kOutPartial = 2,  // un-normalised fp32 sum, its weight, and the common maximum
+};
+
+struct MergeArgs {
+  int topk;        // winners per list
+  int per;         // ceil(topk / cluster)
+  int cluster;
+  int out_mode;
+  int hq_total;    // query heads (row pitch of the outputs)
+  int list_pitch;  // winners slots per (batch row, head) in sel_idx/sel_score
+  int list_off;    // offset of this cluster's winners inside that pitch
+  int index_base;
+  int own_lo, own_hi;  // only winners with own_lo <= id < own_hi are mixed (id before index_base)
+  int id_shift;        // subtracted from an id to address V (ids of another shard's frame)
+  int* sel_idx;        // optional
+  float* sel_score;    // optional
+  const __half* v;
+  long long v_batch_stride, v_token_stride, v_head_stride;
+  __half* out;          // kOutFinal
+  float* out_lse;       // optional (max*scale, sum)
+  float* out_partial;   // kOutPartial: [B,Hq,130] = 128 sums, weight, max*scale
+  float scale_log2e, sm_scale;
+};
+
+// One list's destination: batch row, query head, kv head, and whether it is in use.
+struct ListDest {
+  int bq, hq, hkv;
+  bool valid;
+};
+
+// Among 256 bins find the one holding the `remaining`-th largest element (bins ordered by
+// digit, larger digit = larger key).  Executed by one full warp.  If the bins hold fewer than
+// `remaining` elements bin 0 is returned.  new_remaining = 1-based rank inside that bin.
+__device__ __forceinline__ void warp_find_digit(const int* hist, int remaining, int lane,
+                                                int& digit, int& new_remaining) {
+  int c[8];
+  int s = 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    c[i] = hist[255 - 8 * lane - i];
+    s += c[i];
+  }
+  int incl = s;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    int n = __shfl_up_sync(0xffffffffu, incl, off);
+    if (lane >= off) incl += n;
+  }
+  const int excl = incl - s;
+  const bool cross = (excl < remaining) && (remaining <= incl);
+  const unsigned bal = __ballot_sync(0xffffffffu, cross);
+  const int src = bal ? (__ffs(bal) - 1) : 31;
+  int d = 0, nr = 1;
+  if (lane == src) {
+    int run = excl;
+    bool found = false;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (!found && run + c[i] >= remaining) {
+        d = 255 - 8 * lane - i;
+        nr = remaining - run;
+        found = true;
+      }
+      if (!found) run += c[i];
+    }
+    if (!found) {  // fewer elements than asked for: everything is kept
+      d = 0;
+      nr = max(1, remaining - (run - c[7]));
+    }
+  }
+  digit = __shfl_sync(0xffffffffu, d, src);
+  new_remaining = __shfl_sync(0xffffffffu, nr, src);
+}
+
+// keys/idxs: NL lists of capacity `cap` in this CTA's shared memory with cnt[l] entries each.
+// scratch: shared memory of at least sizeof(MergeScratch) + NL*per*8 bytes, at the same
+// offset in every CTA of the cluster.  dest(l) gives the ListDest of list l.
+template <int NL, typename DestFn>
+__device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char* scratch,
+                                      const uint32_t* keys, const int* idxs, const int* cnt,
+                                      int cap, const MergeArgs& A, DestFn dest) {
+  MergeScratch* ms = reinterpret_cast<MergeScratch*>(scratch);
+  const int per = A.per, k = A.topk, C = A.cluster;
+  uint32_t* sel_key = reinterpret_cast<uint32_t*>(scratch + sizeof(MergeScratch));
+  int* sel_idx = reinterpret_cast<int*>(sel_key + (size_t)NL * per);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int crank = (int)cluster.block_rank();
+
+  for (int i = tid; i < 2 * kMaxLists * 256; i += kThreads) (&ms->hist[0][0][0])[i] = 0;
+  if (tid < kMaxLists) {
+    ms->prefix[tid] = 0u;
+    ms->remaining[tid] = k;
+    ms->counts[tid][0] = 0u;
+    ms->counts[tid][1] = 0u;
+    ms->counts[tid][2] = 0u;
+    ms->ctr_gt[tid] = 0;
+    ms->ctr_eq[tid] = 0;
+  }
+  __syncthreads();
+
+  // radix select, most significant byte first; one cluster barrier per pass
+  uint32_t mask = 0u;
+  int buf = 0;
+#pragma unroll 1
+  for (int shift = 24; shift >= 0; shift -= 8) {
+#pragma unroll
+    for (int l = 0; l < NL; ++l) {
+      const int n = min(cnt[l], cap);
+      const uint32_t pre = ms->prefix[l];
+      const uint32_t* kl = keys + (size_t)l * cap;
+      for (int i = tid; i < n; i += kThreads) {
+        const uint32_t key = kl[i];
+        if ((key & mask) == pre) atomicAdd(&ms->hist[buf][l][(key >> shift) & 255], 1);
+      }
+    }
+    cluster.sync();
+#pragma unroll
+    for (int l = 0; l < NL; ++l) {
+      int sum = 0;
+      for (int c = 0; c < C; ++c) {
+        const int* rh = cluster.map_shared_rank(&ms->hist[buf][l][0], c);
+        sum += rh[tid];
+      }
+      ms->ghist[l][tid] = sum;
+      ms->hist[buf ^ 1][l][tid] = 0;  // peers finished reading it before the barrier above
+    }
+    __syncthreads();
+    for (int l = warp; l < NL; l += kWarps) {
+      int d, nr;
+      warp_find_digit(ms->ghist[l], ms->remaining[l], lane, d, nr);
+      if (lane == 0) {
+        ms->prefix[l] |= (uint32_t)d << shift;
+        ms->remaining[l] = nr;
+      }
+    }
+    __syncthreads();
+    mask |= 255u << shift;
+    buf ^= 1;
+  }
+
+  // my candidates above / equal to the k-th key, and my best key
+#pragma unroll
+  for (int l = 0; l < NL; ++l) {
+    const int n = min(cnt[l], cap);
+    const uint32_t kth = ms->prefix[l];
+    const uint32_t* kl = keys + (size_t)l * cap;
+    int ngt = 0, neq = 0;
+    uint32_t mx = 0u;
+    for (int i = tid; i < n; i += kThreads) {
+      const uint32_t key = kl[i];
+      ngt += key > kth;
+      neq += key == kth;
+      mx = max(mx, key);
+    }
+#pragma unroll
+    for (int off = 16; off; off >>= 1) {
+      ngt += __shfl_xor_sync(0xffffffffu, ngt, off);
+      neq += __shfl_xor_sync(0xffffffffu, neq, off);
+      mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    }
+    if (lane == 0) {
+      atomicAdd(&ms->counts[l][0], (uint32_t)ngt);
+      atomicAdd(&ms->counts[l][1], (uint32_t)neq);
+      atomicMax(&ms->counts[l][2], mx);
+    }
+  }
+  cluster.sync();
+  if (tid < NL) {
+    const int l = tid;
+    const int need_eq = ms->remaining[l];
+    int total_gt = 0, off_gt = 0, eq_before = 0, eq_taken = 0, my_take = 0, off_take = 0;
+    uint32_t mx = 0u;
+    for (int c = 0; c < C; ++c) {
+      const uint32_t* rc = cluster.map_shared_rank(&ms->counts[l][0], c);
+      const int g = (int)rc[0], e = (int)rc[1];
+      mx = max(mx, rc[2]);
+      if (c < crank) off_gt += g;
+      total_gt += g;
+      const int take = max(0, min(e, need_eq - eq_before));
+      if (c < crank) off_take += take;
+      if (c == crank) my_take = take;
+      eq_taken += take;
+      eq_before += e;
+    }
+    ms->off_gt[l] = off_gt;
+    ms->off_eq[l] = total_gt + off_take;
+    ms->take_eq[l] = my_take;
+    ms->total_sel[l] = min(k, total_gt + eq_taken);
+    ms->maxkey[l] = mx;
+  }
+  __syncthreads();
+  // deal the winners evenly: global position p goes to CTA p / per, slot p % per
+#pragma unroll
+  for (int l = 0; l < NL; ++l) {
+    const int n = min(cnt[l], cap);
+    const uint32_t kth = ms->prefix[l];
+    const uint32_t* kl = keys + (size_t)l * cap;
+    const int* il = idxs + (size_t)l * cap;
+    const int off_gt = ms->off_gt[l], off_eq = ms->off_eq[l], take_eq = ms->take_eq[l];
+    for (int i = tid; i < n; i += kThreads) {
+      const uint32_t key = kl[i];
+      int p = -1;
+      if (key > kth) {
+        p = off_gt + atomicAdd(&ms->ctr_gt[l], 1);
+      } else if (key == kth) {
+        const int e = atomicAdd(&ms->ctr_eq[l], 1);
+        if (e < take_eq) p = off_eq + e;
+      }
+      if (p >= 0 && p < k) {
+        const int dst = p / per, slot = p - dst * per;
+        uint32_t* rk = cluster.map_shared_rank(sel_key, dst);
+        int* ri = cluster.map_shared_rank(sel_idx, dst);
+        rk[(size_t)l * per + slot] = key;
+        ri[(size_t)l * per + slot] = il[i];
+      }
+    }
+  }
+  cluster.sync();
+
+#pragma unroll 1
+  for (int l = 0; l < NL; ++l) {
+    const ListDest ld = dest(l);
+    if (!ld.valid) continue;  // uniform over the CTA
+    const int n_l = max(0, min(per, ms->total_sel[l] - crank * per));
+    const uint32_t* sk = sel_key + (size_t)l * per;
+    const int* si = sel_idx + (size_t)l * per;
+    if (A.sel_idx) {
+      const size_t dst = ((size_t)ld.bq * A.hq_total + ld.hq) * A.list_pitch + A.list_off +
+                         (size_t)crank * per;
+      for (int e = tid; e < n_l; e += kThreads) {
+        A.sel_idx[dst + e] = si[e] + A.index_base;
+        if (A.sel_score) A.sel_score[dst + e] = key_score(sk[e]);
+      }
+      // a part with fewer than k keys pads its slots with entries that can never win
+      const int slots = max(0, min(per, k - crank * per));
+      for (int e = n_l + tid; e < slots; e += kThreads) {
+        A.sel_idx[dst + e] = -1;
+        if (A.sel_score) A.sel_score[dst + e] = -INFINITY;
+      }
+    }
+    if (A.out_mode == kOutNone) continue;
+    // softmax weights against the cluster-wide best score; V rows mixed by half-warps
+    const float smax = key_score(ms->maxkey[l]);
+    const __half* vb = A.v + (size_t)ld.bq * A.v_batch_stride + (size_t)ld.hkv * A.v_head_stride +
+                       (lane & 15) * 8;
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    float lsum = 0.f;
+    constexpr int UN = 4;
+    for (int e0 = warp * 2 + (lane >> 4); e0 < n_l; e0 += 16 * UN) {
+      uint4 vv[UN];
+      float w[UN];
+#pragma unroll
+      for (int u = 0; u < UN; ++u) {
+        const int e = e0 + 16 * u;
+        const int id = (e < n_l) ? si[e] : -1;
+        if (id >= A.own_lo && id < A.own_hi) {
+          w[u] = fast_exp2((key_score(sk[e]) - smax) * A.scale_log2e);
+          vv[u] = ldg128_nc(vb + (size_t)(id - A.id_shift) * A.v_token_stride);
+        } else {
+          w[u] = 0.f;
+          vv[u] = make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < UN; ++u) {
+        const uint32_t ww[4] = {vv[u].x, vv[u].y, vv[u].z, vv[u].w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = h2f2(ww[i]);
+          acc[2 * i] = fmaf(w[u], f.x, acc[2 * i]);
+          acc[2 * i + 1] = fmaf(w[u], f.y, acc[2 * i + 1]);
+        }
+        lsum += w[u];
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], 16);
+    lsum += __shfl_xor_sync(0xffffffffu, lsum, 16);
+    if (lane < 16) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ms->red[warp][lane * 8 + i] = acc[i];
+    }
+    if (lane == 0) ms->lred[warp] = lsum;
+    __syncthreads();
+    if (tid < kHeadDim) {
+      float o = 0.f;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) o += ms->red[w][tid];
+      ms->o_part[l][tid] = o;
+      if (tid == 0) {
+        float ls = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) ls += ms->lred[w];
+        ms->l_part[l] = ls;
+      }
+    }
+    __syncthreads();
+  }
+
+  if (A.out_mode != kOutNone) {
+    cluster.sync();
+    const int dper = kHeadDim / C;  // the cluster size divides 128
+    for (int item = tid; item < NL * dper; item += kThreads) {
+      const int l = item / dper, d = crank * dper + item % dper;
+      const ListDest ld = dest(l);
+      if (!ld.valid) continue;
+      float o = 0.f, lt = 0.f;
+      for (int c = 0; c < C; ++c) {
+        const float* ro = cluster.map_shared_rank(&ms->o_part[l][0], c);
+        const float* rl = cluster.map_shared_rank(&ms->l_part[0], c);
+        o += ro[d];
+        lt += rl[l];
+      }
+      const size_t row = (size_t)ld.bq * A.hq_total + ld.hq;
+      const float mscaled = key_score(ms->maxkey[l]) * A.sm_scale;
+      if (A.out_mode == kOutFinal) {
+        A.out[row * kHeadDim + d] = __float2half_rn(o / lt);
+        if (A.out_lse && d == 0) {
+          A.out_lse[row * 2 + 0] = mscaled;
+          A.out_lse[row * 2 + 1] = lt;
+        }
+      } else {
+        float* dstp = A.out_partial + row * (kHeadDim + 2);
+        dstp[d] = o;
+        if (d == 0) {
+          dstp[kHeadDim] = lt;
+          dstp[kHeadDim + 1] = mscaled;
+        }
+      }
+    }
+    cluster.sync();  // nobody leaves while a peer may still read its shared memory
+  }
+}
+
+}  // namespace ra

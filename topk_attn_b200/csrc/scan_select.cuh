@@ -1,0 +1,29 @@
+// Parameters shared by the scan+select kernel and its host launcher.
+#pragma once
+#include "cluster_merge.cuh"
+
+namespace ra {
+
+struct ScanParams {
+  CUtensorMap kmap;          // 4-D map over the key cache (or the centroid table)
+  MergeArgs m;               // selection / output arguments (list_off is set per cluster)
+  const __half* q;           // [B,Hq,128]
+  unsigned* status;          // one word, bit 0 = a bounded wait gave up
+  int batch, hq, hkv, n_tokens;
+  int group;                 // hq / hkv
+  int bshare;                // batch rows that share one cache and are scored together
+  int nq_valid;              // bshare * group, queries scored per K row (<= NQ)
+  int kv_per_batch;          // 1: every batch row has its own cache
+  int cap;                   // capacity of a candidate list (>= topk + 2 tiles)
+  int nstages;               // TMA pipeline depth
+  int nparts;                // parts (segments x splits) per (batch row, head)
+  int part_len;              // tokens per part
+  int head_major;            // 1: table is [H, N, 128] (centroids); one head per CTA
+};
+
+size_t scan_smem_bytes(int nl, int cap, int nstages);
+size_t merge_scratch_bytes(int nl, int per);
+cudaError_t launch_scan_select(const ScanParams& P, int hg, int nq, int grid, size_t smem,
+                               cudaStream_t stream);
+
+}  // namespace ra
