@@ -1,0 +1,284 @@
+#!/usr/bin/env python3
+"""Benchmark of the decode-time top-k sparse-attention path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload cfg2|cfg2_shared|cfg0|cfg1|cfg3|cfg4]
+
+One step = one decode step of the fused path (scan K, exact top-k, softmax over the kept keys,
+mix V) on synthetic inputs of the headline configuration: batch 4, 32 heads, head_dim 128,
+context 131072, top-k 2048, fp16, one cache per batch row with 2 % planted keys.  Prints one JSON
+line.  `value` is tokens scanned per second with the caches resident in HBM; `e2e` is the same
+quantity through the public operator with the step's query coming from pinned host memory and
+its output read back to the host inside the timed region (the KV cache is decode state that
+lives in HBM across steps, like weights, so it is not re-uploaded per step).
+
+With --gpus N > 1 (launched under torchrun, one rank per GPU) the context is sharded by tokens:
+every rank holds a 131072-token shard of every sequence (weak scaling), proposes its local
+top-k, candidates are merged over NCCL and partial outputs are combined through their
+log-sum-exp.  `--impl reference` times the CPU oracle (the reference's torch path) on the host
+cores on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+def measured_peak_gbs():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self._halt = threading.Event()
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def run(self):
+        if self.nv is None:
+            return
+        nv = self.nv
+        names = {
+            nv.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap",
+            nv.nvmlClocksThrottleReasonHwSlowdown: "hw_slowdown",
+            nv.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
+            nv.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
+        }
+        while not self._halt.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in names.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def stop(self):
+        self._halt.set()
+        self.join(timeout=1.0)
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+def physical_gpu_index(local: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local])
+        except Exception:
+            return local
+    return local
+
+
+def make_workload(name: str, device):
+    from topk_attn_b200 import workloads as W
+    if name == "cfg2":
+        return W.fused_topk_128k(device=device)
+    if name == "cfg2_shared":
+        return W.fused_topk_128k(device=device, shared_cache=True)
+    if name == "cfg0":
+        return W.reference_cpu_case(device=device)
+    if name == "cfg4":
+        return W.sharded_long_context_shard(0, 1, device=device)
+    raise SystemExit(f"workload {name} is not available in this bench")
+
+
+def cpu_sample(workload: str):
+    """A bounded sample of the workload for the CPU oracle: one batch row."""
+    from topk_attn_b200 import workloads as W
+    if workload in ("cfg2", "cfg2_shared"):
+        return W.fused_topk_128k(device="cpu", batch=1), "one batch row of cfg2 (N=131072, 32 heads, k=2048)"
+    if workload == "cfg0":
+        return W.reference_cpu_case(), "cfg0 in full"
+    if workload == "cfg4":
+        return (W.sharded_long_context_shard(0, 8, device="cpu"),
+                "one eighth of cfg4 (131072 tokens, 32 q / 8 kv heads, k=4096)")
+    raise SystemExit(f"no CPU sample for {workload}")
+
+
+def time_cpu_oracle(w, repeats: int):
+    from oracle import topk_attn_oracle as O
+    torch.set_num_threads(os.cpu_count() or 1)
+    best = None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        O.topk_sparse_attention(w.q, w.k, w.v, w.topk, w.sm_scale, w.num_segments)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return best
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    w, what = cpu_sample(args.workload)
+    for _ in range(min(args.warmup, 1)):
+        time_cpu_oracle(w, 1)
+    steps = max(1, min(args.steps, 5))
+    t0 = time.perf_counter()
+    times = [time_cpu_oracle(w, 1) for _ in range(steps)]
+    total = time.perf_counter() - t0
+    per = sum(times) / len(times)
+    tokens = w.batch * w.n_tokens
+    val = tokens / per
+    cores = torch.get_num_threads()
+    line = {
+        "impl": "reference", "metric": "tokens_scanned_per_s", "value": val, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 1),
+        "ms_per_step": per * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "sample": what},
+        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port",
+                         "sample": what},
+        "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "wall_s": total,
+    }
+    print(json.dumps(line))
+
+
+def run_ours(args):
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback")
+    from topk_attn_b200 import ops
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    if world > 1:
+        from topk_attn_b200 import sharded
+        return sharded.bench(args, rank, local, world, ClockSampler, measured_peak_gbs)
+
+    w = make_workload(args.workload, dev)
+    q, k, v = w.q, w.k, w.v
+    out = torch.empty_like(q)
+
+    def step():
+        ops.topk_attention(q, k, v, w.topk, w.sm_scale, w.num_segments, out=out)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    ops.check_status(dev)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(physical_gpu_index(local))
+    sampler.start()
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    torch.cuda.synchronize()
+    evs[0].record()
+    for i in range(args.steps):
+        step()
+        evs[i + 1].record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    total_ms = evs[0].elapsed_time(evs[-1])
+    per_ms = total_ms / args.steps
+    launch_ms = sorted(evs[i].elapsed_time(evs[i + 1]) for i in range(args.steps))
+    ops.check_status(dev)
+
+    # end to end: query from pinned host memory, output read back, every step
+    q_host = q.cpu().pin_memory()
+    out_host = torch.empty_like(q_host).pin_memory()
+    q_dev = torch.empty_like(q)
+    e2e_steps = args.steps
+
+    def e2e_step():
+        q_dev.copy_(q_host, non_blocking=True)
+        ops.topk_attention(q_dev, k, v, w.topk, w.sm_scale, w.num_segments, out=out)
+        out_host.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(3):
+        e2e_step()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+
+    tokens = w.batch * w.n_tokens
+    alg_bytes = w.algorithmic_bytes()
+    peak, peak_kind = measured_peak_gbs()
+    achieved = alg_bytes / (per_ms * 1e-3) / 1e9
+
+    cw, what = cpu_sample(args.workload)
+    cpu_t = time_cpu_oracle(cw, 2)
+    line = {
+        "metric": "tokens_scanned_per_s", "value": tokens / (per_ms * 1e-3), "unit": "tokens/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": per_ms, "us_per_step": per_ms * 1e3,
+        "us_per_step_median": launch_ms[len(launch_ms) // 2] * 1e3,
+        "us_per_step_min": launch_ms[0] * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f16 inputs, f32 accumulate", "data": "synthetic",
+        "config": {"workload": args.workload, "batch": w.batch, "heads_q": q.size(1),
+                   "heads_kv": k.size(-2), "head_dim": 128, "context": w.n_tokens,
+                   "topk": w.topk, "caches": w.bkv, "l2": "inputs_exceed_l2"
+                   if w.kv_bytes_scanned() > (256 << 20) else "resident_in_l2"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "peak_kind": peak_kind + " (burst copy)",
+                     "algorithmic_bytes": alg_bytes, "traffic": None,
+                     "kernel": "scan_select_kernel"},
+        "cpu_baseline": {"value": cw.batch * cw.n_tokens / cpu_t, "unit": "tokens/s",
+                         "cores": torch.get_num_threads(), "kind": "port", "sample": what},
+        "e2e": {"value": tokens / e2e_s, "unit": "tokens/s", "us_per_step": e2e_s * 1e6,
+                "h2d_bytes_per_step": q_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 2},
+        "gpu_launches": args.steps,
+        "clocks": clocks,
+    }
+    traffic_file = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(traffic_file):
+        try:
+            line["roofline"]["traffic"] = json.load(open(traffic_file)).get(args.workload)
+        except Exception:
+            pass
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg2")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
