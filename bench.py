@@ -102,6 +102,8 @@ def make_workload(name: str, device):
     from topk_attn_b200 import workloads as W
     if name == "cfg2":
         return W.fused_topk_128k(device=device)
+    if name == "cfg2_n32k":      # the headline geometry at a quarter of the context (profiling)
+        return W.fused_topk_128k(device=device, n=32768)
     if name == "cfg2_shared":
         return W.fused_topk_128k(device=device, shared_cache=True)
     if name == "cfg0":
@@ -114,7 +116,7 @@ def make_workload(name: str, device):
 def cpu_sample(workload: str):
     """A bounded sample of the workload for the CPU oracle: one batch row."""
     from topk_attn_b200 import workloads as W
-    if workload in ("cfg2", "cfg2_shared"):
+    if workload in ("cfg2", "cfg2_shared", "cfg2_n32k"):
         return W.fused_topk_128k(device="cpu", batch=1), "one batch row of cfg2 (N=131072, 32 heads, k=2048)"
     if workload == "cfg0":
         return W.reference_cpu_case(), "cfg0 in full"
@@ -232,8 +234,11 @@ def run_ours(args):
     peak, peak_kind = measured_peak_gbs()
     achieved = alg_bytes / (per_ms * 1e-3) / 1e9
 
-    cw, what = cpu_sample(args.workload)
-    cpu_t = time_cpu_oracle(cw, 2)
+    if args.no_cpu:
+        cw, what, cpu_t = None, "skipped (--no-cpu)", None
+    else:
+        cw, what = cpu_sample(args.workload)
+        cpu_t = time_cpu_oracle(cw, 2)
     line = {
         "metric": "tokens_scanned_per_s", "value": tokens / (per_ms * 1e-3), "unit": "tokens/s",
         "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
@@ -250,7 +255,8 @@ def run_ours(args):
                      "frac": achieved / peak, "peak_kind": peak_kind + " (burst copy)",
                      "algorithmic_bytes": alg_bytes, "traffic": None,
                      "kernel": "scan_select_kernel"},
-        "cpu_baseline": {"value": cw.batch * cw.n_tokens / cpu_t, "unit": "tokens/s",
+        "cpu_baseline": {"value": (cw.batch * cw.n_tokens / cpu_t) if cw is not None else None,
+                         "unit": "tokens/s",
                          "cores": torch.get_num_threads(), "kind": "port", "sample": what},
         "e2e": {"value": tokens / e2e_s, "unit": "tokens/s", "us_per_step": e2e_s * 1e6,
                 "h2d_bytes_per_step": q_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 2},
@@ -273,6 +279,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

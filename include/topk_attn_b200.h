@@ -34,6 +34,7 @@ extern "C" {
 #define RA_ERR_CUDA 4               /* a CUDA runtime/driver call failed; see ra_last_cuda_error() */
 #define RA_ERR_DEVICE_TIMEOUT 5     /* a bounded wait inside a kernel gave up (ra_check_status) */
 #define RA_ERR_NOT_BUILT 6
+#define RA_ERR_DEVICE_CHECK 7       /* a kernel found and skipped inconsistent data (ra_check_status) */
 
 /* Operands of one decode step.  Unused optional pointers are NULL. */
 typedef struct ra_params {
@@ -86,7 +87,8 @@ int ra_topk_attention(const ra_params* p);
 int ra_gemv_topk(const ra_params* p);
 
 /* After the stream has been synchronised by the caller: RA_OK, or RA_ERR_DEVICE_TIMEOUT if a
- * kernel that used this workspace abandoned a bounded wait.  Synchronises the stream itself. */
+ * kernel that used this workspace abandoned a bounded wait, or RA_ERR_DEVICE_CHECK if one
+ * skipped data that failed its own bounds checks.  Synchronises the stream itself. */
 int ra_check_status(void* workspace, void* stream);
 
 /* The reference extension's entry points (retrieval_attn/bind.cpp:5-243 declare

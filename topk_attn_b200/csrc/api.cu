@@ -2,6 +2,7 @@
 // launches.  Nothing here allocates device memory or synchronises (ra_check_status excepted).
 #include "topk_attn_b200.h"
 
+#include <cmath>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -120,6 +121,10 @@ Plan make_plan(const Shape& s) {
     if (it != cache.end()) return it->second;
   }
   Plan best;
+  // RA_FORCE_PLAN="hg,cluster,nsplit" pins the geometry (0 = free); for tuning only
+  int f_hg = 0, f_cluster = 0, f_nsplit = 0, f_stages = 0;
+  if (const char* f = getenv("RA_FORCE_PLAN"))
+    sscanf(f, "%d,%d,%d,%d", &f_hg, &f_cluster, &f_nsplit, &f_stages);
   const int group = s.hq / s.hkv;
   int bshare = 1;
   if (!s.per_batch) {
@@ -133,11 +138,14 @@ Plan make_plan(const Shape& s) {
   for (int hg : {8, 4, 2, 1}) {
     if (s.hkv % hg || !combo_built(hg, nq)) continue;
     if (s.head_major && hg != 1) continue;
+    if (f_hg && hg != f_hg) continue;
     const int nl = hg * nq, T = kTileRows / hg;
     const int groups = (s.batch / bshare) * (s.hkv / hg) * s.segments;
     for (int cluster : {1, 2, 4, 8, 16}) {
+      if (f_cluster && cluster != f_cluster) continue;
       for (int nsplit = 1; nsplit <= kMaxSplit; ++nsplit) {
         if (nsplit > 1 && s.segments > 1) break;
+        if (f_nsplit && nsplit != f_nsplit) continue;
         int part_len = ceil_div(ceil_div(seg_len, nsplit), T) * T;
         if (nsplit > 1 && part_len < s.topk) break;           // every part must hold k keys
         if (nsplit > 1 && part_len * (nsplit - 1) >= seg_len) continue;  // empty last part
@@ -148,14 +156,17 @@ Plan make_plan(const Shape& s) {
         const size_t scratch = merge_scratch_bytes(nl, per);
         // stages and list capacity within the shared-memory budget
         int nstages = 0, cap = 0;
-        for (int st = kMaxStages; st >= 3; --st) {
+        for (int st = kMaxStages; st >= 2 * kConsumerGroups; st -= kConsumerGroups) {
+          if (f_stages && st != f_stages) continue;
           if ((size_t)st * kStageBytes < scratch) break;
           const size_t fixed = scan_smem_bytes(nl, 0, st);
           if (fixed >= kSmemBudget) continue;
           int c = (int)((kSmemBudget - fixed) / ((size_t)nl * 8));
-          c = std::min(c, 2 * s.topk + 2 * T);
-          const int want = (st > 4) ? (3 * s.topk) / 2 + 2 * T : s.topk + 2 * T + 64;
-          if (c >= std::min(want, 2 * s.topk + 2 * T)) {
+          // room for the keys that may arrive between two overflow checks
+          const int margin = kRendezvous * kConsumerGroups * T;
+          c = std::min(c, 2 * s.topk + margin);
+          const int want = (st > 4) ? (3 * s.topk) / 2 + margin : s.topk + margin + 64;
+          if (c >= std::min(want, 2 * s.topk + margin)) {
             nstages = st;
             cap = c;
             break;
@@ -169,9 +180,16 @@ Plan make_plan(const Shape& s) {
         const int waves = ceil_div(nclusters, active);
         const int live = std::min(nclusters, active) * cluster;
         const double bytes_cta = (double)ceil_div(tiles, cluster) * kStageBytes;
-        const double rate = std::min(per_sm, hbm / live) * (hg * kRowBytes >= 1024 ? 1.0 : 0.93);
+        const double rate = std::min(per_sm, hbm / live);
+        // every cut of a candidate list stalls the CTA's consumers for a few microseconds; the
+        // seen-token count grows by (1 + room/k) between two cuts of one list
+        const int margin = kRendezvous * kConsumerGroups * T;
+        const double room = std::max(64, cap - s.topk - margin);
+        const double slab = (double)ceil_div(tiles, cluster) * T;
+        const double cuts = slab > cap ? std::log(slab / cap) / std::log1p(room / s.topk) + 1.0 : 0.0;
         const bool two_stage = nsplit > 1 || s.segments > 1 || !s.fused_ok;
-        double cost = waves * (bytes_cta / rate + 6e-6 + 1.5e-6 * cluster) + (two_stage ? 8e-6 : 0.0);
+        double cost = waves * (bytes_cta / rate + cuts * nl * 4e-6 + 6e-6 + 1.5e-6 * cluster) +
+                      (two_stage ? 8e-6 : 0.0);
         Plan pl;
         pl.hg = hg; pl.nq = nq; pl.bshare = bshare; pl.nq_valid = nq_valid;
         pl.cluster = cluster; pl.nsplit = nsplit; pl.cap = cap; pl.nstages = nstages;
@@ -330,11 +348,13 @@ int run(const ra_params* p, bool attend) {
   sp.kv_per_batch = s.per_batch;
   sp.cap = pl.cap; sp.nstages = pl.nstages; sp.nparts = parts; sp.part_len = pl.part_len;
   sp.head_major = s.head_major;
+  if (const char* d = getenv("RA_DEBUG_FLAGS")) sp.debug = atoi(d);
   MergeArgs& m = sp.m;
   m.topk = s.topk; m.per = pl.per; m.cluster = pl.cluster;
   m.hq_total = s.hq; m.list_pitch = parts * s.topk; m.list_off = 0;
   m.index_base = two_stage ? 0 : p->index_base;
   m.own_lo = 0; m.own_hi = 0x7fffffff; m.id_shift = 0;
+  m.n_tokens = s.n; m.status = status;
   m.v = static_cast<const __half*>(p->v);
   m.v_batch_stride = p->kv_batch_stride; m.v_token_stride = p->kv_token_stride;
   m.v_head_stride = p->kv_head_stride;
@@ -394,6 +414,7 @@ const char* ra_strerror(int status) {
     case RA_ERR_CUDA: return "CUDA call failed";
     case RA_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait gave up";
     case RA_ERR_NOT_BUILT: return "not built";
+    case RA_ERR_DEVICE_CHECK: return "a device-side self-check failed";
     default: return "unknown status";
   }
 }
@@ -419,7 +440,13 @@ int ra_check_status(void* workspace, void* stream) {
                                   static_cast<cudaStream_t>(stream));
   if (e == cudaSuccess) e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail(e, "ra_check_status");
-  return (h & ra::kStatusTimeout) ? RA_ERR_DEVICE_TIMEOUT : RA_OK;
+  if (h & ra::kStatusTimeout) return RA_ERR_DEVICE_TIMEOUT;
+  if (h & (ra::kStatusBadId | ra::kStatusOverflow)) {
+    g_last_error = (h & ra::kStatusBadId) ? "a kernel skipped a key id outside the value cache"
+                                          : "a candidate list overflowed";
+    return RA_ERR_DEVICE_CHECK;
+  }
+  return RA_OK;
 }
 
 static void legacy_params(ra_params* p, const void* q, const void* k, const void* v, void* out,

@@ -25,8 +25,8 @@ struct MergeScratch {
   int ctr_gt[kMaxLists], ctr_eq[kMaxLists];
   int off_gt[kMaxLists], off_eq[kMaxLists], take_eq[kMaxLists], total_sel[kMaxLists];
   uint32_t maxkey[kMaxLists];
-  float red[kWarps][kHeadDim];
-  float lred[kWarps];
+  float red[kMaxWarps][kHeadDim];
+  float lred[kMaxWarps];
   float o_part[kMaxLists][kHeadDim];  // read by the other CTAs
   float l_part[kMaxLists];            // read by the other CTAs
 };
@@ -48,6 +48,8 @@ struct MergeArgs {
   int index_base;
   int own_lo, own_hi;  // only winners with own_lo <= id < own_hi are mixed (id before index_base)
   int id_shift;        // subtracted from an id to address V (ids of another shard's frame)
+  int n_tokens;        // rows of V; ids outside [0, n_tokens) after the shift are never read
+  unsigned* status;    // device status word (bit kStatusBadId is set on such an id)
   int* sel_idx;        // optional
   float* sel_score;    // optional
   const __half* v;
@@ -120,9 +122,12 @@ __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char*
   uint32_t* sel_key = reinterpret_cast<uint32_t*>(scratch + sizeof(MergeScratch));
   int* sel_idx = reinterpret_cast<int*>(sel_key + (size_t)NL * per);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int nthr = blockDim.x, nwarps = nthr >> 5;
   const int crank = (int)cluster.block_rank();
 
-  for (int i = tid; i < 2 * kMaxLists * 256; i += kThreads) (&ms->hist[0][0][0])[i] = 0;
+  for (int i = tid; i < 2 * kMaxLists * 256; i += nthr) (&ms->hist[0][0][0])[i] = 0;
+  // winner slots start out empty; a slot nobody fills is skipped by the mixing loop
+  for (int i = tid; i < NL * per; i += nthr) sel_idx[i] = -1;
   if (tid < kMaxLists) {
     ms->prefix[tid] = 0u;
     ms->remaining[tid] = k;
@@ -144,24 +149,24 @@ __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char*
       const int n = min(cnt[l], cap);
       const uint32_t pre = ms->prefix[l];
       const uint32_t* kl = keys + (size_t)l * cap;
-      for (int i = tid; i < n; i += kThreads) {
+      for (int i = tid; i < n; i += nthr) {
         const uint32_t key = kl[i];
         if ((key & mask) == pre) atomicAdd(&ms->hist[buf][l][(key >> shift) & 255], 1);
       }
     }
     cluster.sync();
-#pragma unroll
-    for (int l = 0; l < NL; ++l) {
+    for (int item = tid; item < NL * 256; item += nthr) {
+      const int l = item >> 8, bin = item & 255;
       int sum = 0;
       for (int c = 0; c < C; ++c) {
         const int* rh = cluster.map_shared_rank(&ms->hist[buf][l][0], c);
-        sum += rh[tid];
+        sum += rh[bin];
       }
-      ms->ghist[l][tid] = sum;
-      ms->hist[buf ^ 1][l][tid] = 0;  // peers finished reading it before the barrier above
+      ms->ghist[l][bin] = sum;
+      ms->hist[buf ^ 1][l][bin] = 0;  // peers finished reading it before the barrier above
     }
     __syncthreads();
-    for (int l = warp; l < NL; l += kWarps) {
+    for (int l = warp; l < NL; l += nwarps) {
       int d, nr;
       warp_find_digit(ms->ghist[l], ms->remaining[l], lane, d, nr);
       if (lane == 0) {
@@ -182,7 +187,7 @@ __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char*
     const uint32_t* kl = keys + (size_t)l * cap;
     int ngt = 0, neq = 0;
     uint32_t mx = 0u;
-    for (int i = tid; i < n; i += kThreads) {
+    for (int i = tid; i < n; i += nthr) {
       const uint32_t key = kl[i];
       ngt += key > kth;
       neq += key == kth;
@@ -233,7 +238,7 @@ __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char*
     const uint32_t* kl = keys + (size_t)l * cap;
     const int* il = idxs + (size_t)l * cap;
     const int off_gt = ms->off_gt[l], off_eq = ms->off_eq[l], take_eq = ms->take_eq[l];
-    for (int i = tid; i < n; i += kThreads) {
+    for (int i = tid; i < n; i += nthr) {
       const uint32_t key = kl[i];
       int p = -1;
       if (key > kth) {
@@ -263,13 +268,13 @@ __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char*
     if (A.sel_idx) {
       const size_t dst = ((size_t)ld.bq * A.hq_total + ld.hq) * A.list_pitch + A.list_off +
                          (size_t)crank * per;
-      for (int e = tid; e < n_l; e += kThreads) {
+      for (int e = tid; e < n_l; e += nthr) {
         A.sel_idx[dst + e] = si[e] + A.index_base;
         if (A.sel_score) A.sel_score[dst + e] = key_score(sk[e]);
       }
       // a part with fewer than k keys pads its slots with entries that can never win
       const int slots = max(0, min(per, k - crank * per));
-      for (int e = n_l + tid; e < slots; e += kThreads) {
+      for (int e = n_l + tid; e < slots; e += nthr) {
         A.sel_idx[dst + e] = -1;
         if (A.sel_score) A.sel_score[dst + e] = -INFINITY;
       }
@@ -284,16 +289,19 @@ __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char*
     for (int i = 0; i < 8; ++i) acc[i] = 0.f;
     float lsum = 0.f;
     constexpr int UN = 4;
-    for (int e0 = warp * 2 + (lane >> 4); e0 < n_l; e0 += 16 * UN) {
+    for (int e0 = warp * 2 + (lane >> 4); e0 < n_l; e0 += 2 * nwarps * UN) {
       uint4 vv[UN];
       float w[UN];
 #pragma unroll
       for (int u = 0; u < UN; ++u) {
-        const int e = e0 + 16 * u;
+        const int e = e0 + 2 * nwarps * u;
         const int id = (e < n_l) ? si[e] : -1;
-        if (id >= A.own_lo && id < A.own_hi) {
+        const int local = id - A.id_shift;
+        const bool mine = id >= A.own_lo && id < A.own_hi;
+        if (mine && (unsigned)local >= (unsigned)A.n_tokens) atomicOr(A.status, kStatusBadId);
+        if (mine && (unsigned)local < (unsigned)A.n_tokens) {
           w[u] = fast_exp2((key_score(sk[e]) - smax) * A.scale_log2e);
-          vv[u] = ldg128_nc(vb + (size_t)(id - A.id_shift) * A.v_token_stride);
+          vv[u] = ldg128_nc(vb + (size_t)local * A.v_token_stride);
         } else {
           w[u] = 0.f;
           vv[u] = make_uint4(0u, 0u, 0u, 0u);
@@ -322,13 +330,11 @@ __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char*
     __syncthreads();
     if (tid < kHeadDim) {
       float o = 0.f;
-#pragma unroll
-      for (int w = 0; w < kWarps; ++w) o += ms->red[w][tid];
+      for (int w = 0; w < nwarps; ++w) o += ms->red[w][tid];
       ms->o_part[l][tid] = o;
       if (tid == 0) {
         float ls = 0.f;
-#pragma unroll
-        for (int w = 0; w < kWarps; ++w) ls += ms->lred[w];
+        for (int w = 0; w < nwarps; ++w) ls += ms->lred[w];
         ms->l_part[l] = ls;
       }
     }
@@ -338,7 +344,7 @@ __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char*
   if (A.out_mode != kOutNone) {
     cluster.sync();
     const int dper = kHeadDim / C;  // the cluster size divides 128
-    for (int item = tid; item < NL * dper; item += kThreads) {
+    for (int item = tid; item < NL * dper; item += nthr) {
       const int l = item / dper, d = crank * dper + item % dper;
       const ListDest ld = dest(l);
       if (!ld.valid) continue;

@@ -10,8 +10,13 @@ namespace ra {
 
 constexpr int kHeadDim = 128;          // the reference's only head size
 constexpr int kRowBytes = kHeadDim * 2;
-constexpr int kThreads = 256;          // threads per CTA of the scan kernels
-constexpr int kWarps = kThreads / 32;
+constexpr int kConsumerGroups = 2;     // warp groups of the scan kernel, each on its own tile
+constexpr int kConsumerWarps = 8 * kConsumerGroups;
+constexpr int kConsumerThreads = 32 * kConsumerWarps;
+constexpr int kThreads = kConsumerThreads + 32;   // + one TMA producer warp
+constexpr int kMergeThreads = 256;     // threads per CTA of the candidate-merge kernel
+constexpr int kMaxWarps = 32;
+constexpr int kRendezvous = 4;         // scan iterations between list-overflow checks
 constexpr int kTileRows = 128;         // K rows (tokens x kv heads) per pipeline stage
 constexpr int kStageBytes = kTileRows * kRowBytes;   // 32 KiB
 constexpr int kMaxStages = 6;
@@ -20,6 +25,8 @@ constexpr unsigned kSpinLimit = 1u << 22;   // bounded mbarrier wait (try_wait r
 
 // status word bits written by kernels that abandon a bounded wait
 constexpr unsigned kStatusTimeout = 1u;
+constexpr unsigned kStatusBadId = 2u;      // a winner id outside the value cache was skipped
+constexpr unsigned kStatusOverflow = 4u;   // a candidate list overflowed its capacity
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -45,6 +52,9 @@ __device__ __forceinline__ void fence_barrier_init() {
 }
 __device__ __forceinline__ void fence_proxy_async() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),

@@ -9,7 +9,7 @@
 
 namespace ra {
 
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kMergeThreads, 1)
 merge_attend_kernel(const __grid_constant__ MergeParams P) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   unsigned char* smem =
@@ -31,7 +31,7 @@ merge_attend_kernel(const __grid_constant__ MergeParams P) {
   const int n = max(0, min(P.m_total, lo + chunk) - lo);
   const float* cs = P.cand_score + (size_t)row * P.m_total + lo;
   const int* ci = P.cand_idx + (size_t)row * P.m_total + lo;
-  for (int i = tid; i < n; i += kThreads) {
+  for (int i = tid; i < n; i += kMergeThreads) {
     keys[i] = score_key(cs[i]);
     idxs[i] = ci[i];
   }
@@ -65,7 +65,7 @@ cudaError_t launch_merge_attend(const MergeParams& P, int rows, size_t smem, cud
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(rows * P.m.cluster), 1, 1);
-  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.blockDim = dim3(kMergeThreads, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];

@@ -27,30 +27,36 @@ namespace ra {
 
 struct Ctrl {
   uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
   int cnt[kMaxLists];
   uint32_t thr[kMaxLists];
   int hist[256];
   int digit, remaining, wpos, eqc;
-  int need[2];  // lists to cut back after the next tile barrier (bit per list)
   int timeout;
 };
 
+// Barrier among the consumer warps only (the producer warp never joins it).
+__device__ __forceinline__ void consumer_sync() {
+  asm volatile("bar.sync 1, %0;" ::"r"(kConsumerThreads) : "memory");
+}
+
 // Raise the threshold of list `l` to its exact k-th largest key and keep only the k best.
-// Called by all threads of the CTA.
-__device__ void compact_list(uint32_t* keys, int* idxs, Ctrl* ctrl, int l, int k, int tid) {
-  const int n = ctrl->cnt[l];
+// Called by all consumer threads.
+__device__ void compact_list(uint32_t* keys, int* idxs, Ctrl* ctrl, int l, int k, int cap,
+                             int tid) {
+  const int n = min(ctrl->cnt[l], cap);
   const int lane = tid & 31;
   uint32_t prefix = 0, mask = 0;
   int remaining = k;
 #pragma unroll 1
   for (int shift = 24; shift >= 0; shift -= 8) {
-    ctrl->hist[tid] = 0;  // kThreads == 256 bins
-    __syncthreads();
-    for (int i = tid; i < n; i += kThreads) {
+    if (tid < 256) ctrl->hist[tid] = 0;
+    consumer_sync();
+    for (int i = tid; i < n; i += kConsumerThreads) {
       const uint32_t key = keys[i];
       if ((key & mask) == prefix) atomicAdd(&ctrl->hist[(key >> shift) & 255], 1);
     }
-    __syncthreads();
+    consumer_sync();
     if (tid < 32) {
       int d, nr;
       warp_find_digit(ctrl->hist, remaining, lane, d, nr);
@@ -59,7 +65,7 @@ __device__ void compact_list(uint32_t* keys, int* idxs, Ctrl* ctrl, int l, int k
         ctrl->remaining = nr;
       }
     }
-    __syncthreads();
+    consumer_sync();
     prefix |= (uint32_t)ctrl->digit << shift;
     mask |= 255u << shift;
     remaining = ctrl->remaining;
@@ -70,22 +76,22 @@ __device__ void compact_list(uint32_t* keys, int* idxs, Ctrl* ctrl, int l, int k
     ctrl->wpos = 0;
     ctrl->eqc = 0;
   }
-  __syncthreads();
-  constexpr int E = 8;
+  consumer_sync();
+  constexpr int E = 4;
 #pragma unroll 1
-  for (int base = 0; base < n; base += kThreads * E) {
+  for (int base = 0; base < n; base += kConsumerThreads * E) {
     uint32_t kk[E];
     int ii[E];
 #pragma unroll
     for (int e = 0; e < E; ++e) {
-      const int i = base + e * kThreads + tid;
+      const int i = base + e * kConsumerThreads + tid;
       kk[e] = (i < n) ? keys[i] : 0u;
       ii[e] = (i < n) ? idxs[i] : 0;
     }
-    __syncthreads();
+    consumer_sync();
 #pragma unroll
     for (int e = 0; e < E; ++e) {
-      const int i = base + e * kThreads + tid;
+      const int i = base + e * kConsumerThreads + tid;
       if (i < n) {
         bool keep = kk[e] > kth;
         if (!keep && kk[e] == kth) keep = atomicAdd(&ctrl->eqc, 1) < need_eq;
@@ -96,22 +102,43 @@ __device__ void compact_list(uint32_t* keys, int* idxs, Ctrl* ctrl, int l, int k
         }
       }
     }
-    __syncthreads();
+    consumer_sync();
   }
   if (tid == 0) {
     ctrl->cnt[l] = ctrl->wpos;
     ctrl->thr[l] = kth;
   }
-  __syncthreads();
+  consumer_sync();
 }
 
-template <int HG, int NQ>
+// acc0 += k.lo * q.lo, acc1 += k.hi * q.hi for one packed pair of fp16 values; products of
+// two fp16 numbers are exact in fp32, so both forms give the same sums.
+template <bool MIXED>
+__device__ __forceinline__ void fma_pair(float& acc0, float& acc1, uint32_t kw, uint32_t qw) {
+  if constexpr (MIXED) {
+    asm("{\n\t.reg .b16 kl, kh, ql, qh;\n\t"
+        "mov.b32 {kl, kh}, %2;\n\t"
+        "mov.b32 {ql, qh}, %3;\n\t"
+        "fma.rn.f32.f16 %0, kl, ql, %0;\n\t"
+        "fma.rn.f32.f16 %1, kh, qh, %1;\n\t}"
+        : "+f"(acc0), "+f"(acc1)
+        : "r"(kw), "r"(qw));
+  } else {
+    const float2 kf = h2f2(kw), qf = h2f2(qw);
+    acc0 = fmaf(kf.x, qf.x, acc0);
+    acc1 = fmaf(kf.y, qf.y, acc1);
+  }
+}
+
+template <int HG, int NQ, bool MIXED>
 __global__ void __launch_bounds__(kThreads, 1)
 scan_select_kernel(const __grid_constant__ ScanParams P) {
   constexpr int NL = HG * NQ;
   static_assert(NL <= kMaxLists, "too many candidate lists per CTA");
-  constexpr int T = kTileRows / HG;   // tokens per tile
-  constexpr int NV = (NQ + 1) / 2;    // scores a lane keeps per tile
+  constexpr int T = kTileRows / HG;     // tokens per tile
+  constexpr int NV = (NQ + 1) / 2;      // scores a lane keeps per tile
+  constexpr int G = kConsumerGroups;    // warp groups working on different tiles
+  constexpr int R = kRendezvous;        // iterations between overflow checks
   extern __shared__ __align__(128) unsigned char smem_raw[];
   unsigned char* smem =
       reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
@@ -143,13 +170,15 @@ scan_select_kernel(const __grid_constant__ ScanParams P) {
   const int tile_b = crank * tpc;
   const int my_ntiles = max(0, min(ntiles_part, tile_b + tpc) - tile_b);
   const int tok_begin = part_lo + tile_b * T;
+  const int S = P.nstages;
 
   if (tid == 0) {
     tma_prefetch_desc(&P.kmap);
-    for (int s = 0; s < kMaxStages; ++s) mbar_init(&ctrl->full[s], 1);
+    for (int s = 0; s < kMaxStages; ++s) {
+      mbar_init(&ctrl->full[s], 1);
+      mbar_init(&ctrl->empty[s], 8);  // the 8 warps of the group that consumed the stage
+    }
     ctrl->timeout = 0;
-    ctrl->need[0] = 0;
-    ctrl->need[1] = 0;
     fence_barrier_init();
   }
   if (tid < kMaxLists) {
@@ -158,152 +187,190 @@ scan_select_kernel(const __grid_constant__ ScanParams P) {
   }
   __syncthreads();
 
-  auto issue = [&](int it) {
-    const int s = it % P.nstages;
-    const int tok = tok_begin + it * T;
-    mbar_expect_tx(&ctrl->full[s], kStageBytes);
-    if (P.head_major)
-      tma_load_4d(stages + (size_t)s * kStageBytes, &P.kmap, &ctrl->full[s], 0, tok, h0, kv_b);
-    else
-      tma_load_4d(stages + (size_t)s * kStageBytes, &P.kmap, &ctrl->full[s], 0, h0, tok, kv_b);
-  };
-  if (tid == 0) {
-    const int pre = min(P.nstages, my_ntiles);
-    for (int it = 0; it < pre; ++it) issue(it);
-  }
-
-  // row ownership inside a tile: warp -> (kv head hh, 16 consecutive tokens), 4 passes of
-  // 4 rows, 8 lanes per row
-  const int hh = warp % HG;
-  const int tw = warp / HG;
-  const int r = lane >> 3, j = lane & 7;
-  const int my_p = j & 3;      // pass whose score this lane keeps
-  const int my_qpar = j >> 2;  // parity of the queries this lane keeps
-
-  // query fragments: dims [8j,8j+8) and [64+8j,64+8j+8) of each query, fp32
-  float qf[NQ][16];
-#pragma unroll
-  for (int qi = 0; qi < NQ; ++qi) {
-    if (qi < P.nq_valid) {
-      const int bq = b0 + qi / P.group;
-      const int hq = (h0 + hh) * P.group + qi % P.group;
-      const __half* qp = P.q + ((size_t)bq * P.hq + hq) * kHeadDim;
-      const uint4 a = *reinterpret_cast<const uint4*>(qp + 8 * j);
-      const uint4 b = *reinterpret_cast<const uint4*>(qp + 64 + 8 * j);
-      const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float2 f = h2f2(w[i]);
-        qf[qi][2 * i] = f.x;
-        qf[qi][2 * i + 1] = f.y;
-      }
-    } else {
-#pragma unroll
-      for (int i = 0; i < 16; ++i) qf[qi][i] = 0.f;
-    }
-  }
-
-  // the lists this lane appends to and their thresholds
-  int my_list[NV];
-  uint32_t my_thr[NV];
-  bool my_valid[NV];
-#pragma unroll
-  for (int v = 0; v < NV; ++v) {
-    const int qi = 2 * v + my_qpar;
-    my_valid[v] = (NQ == 1) ? (j < 4) : (qi < P.nq_valid && qi < NQ);
-    my_list[v] = hh * NQ + ((NQ == 1) ? 0 : min(qi, NQ - 1));
-    my_thr[v] = 0u;
-  }
-  const unsigned grp_mask = my_qpar ? 0xF0F0F0F0u : 0x0F0F0F0Fu;
-  const unsigned lt_mask = (1u << lane) - 1u;
-
-  const uint32_t stage0 = smem_u32(stages);
-  const uint32_t row_off = (uint32_t)(((tw * 16 + r) * HG + hh) * kRowBytes + j * 16);
-
-#pragma unroll 1
-  for (int it = 0; it < my_ntiles; ++it) {
-    const int s = it % P.nstages;
-    if (!mbar_wait(&ctrl->full[s], (unsigned)((it / P.nstages) & 1))) {
-      if (lane == 0) {
-        ctrl->timeout = 1;
-        atomicOr(P.status, kStatusTimeout);
-      }
-    }
-    const uint32_t base = stage0 + (uint32_t)s * kStageBytes + row_off;
-    float mine[NV];
-#pragma unroll
-    for (int v = 0; v < NV; ++v) mine[v] = 0.f;
-#pragma unroll
-    for (int p = 0; p < 4; ++p) {
-      const uint32_t addr = base + (uint32_t)(p * 4 * HG * kRowBytes);
-      const uint4 a = lds128(addr);
-      const uint4 b = lds128(addr + 128);
-      const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-      float kf[16];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float2 f = h2f2(w[i]);
-        kf[2 * i] = f.x;
-        kf[2 * i + 1] = f.y;
-      }
-#pragma unroll
-      for (int qi = 0; qi < NQ; ++qi) {
-        float a0 = 0.f, a1 = 0.f;
-#pragma unroll
-        for (int i = 0; i < 16; i += 2) {
-          a0 = fmaf(kf[i], qf[qi][i], a0);
-          a1 = fmaf(kf[i + 1], qf[qi][i + 1], a1);
+  if (warp == kConsumerWarps) {
+    // ------------------------------------------------------------ producer warp
+    if (lane == 0) {
+      // Every consumer group has its own ring of S/G stages, so a warp waits on every phase of
+      // the barriers it uses (a warp that skipped a phase could not tell parities apart).
+      const int SG = S / G;
+      for (int it = 0; it < my_ntiles; ++it) {
+        const int jt = it / G;
+        const int s = (jt % SG) * G + (it % G);
+        if (jt >= SG && !mbar_wait(&ctrl->empty[s], (unsigned)(((jt / SG) - 1) & 1))) {
+          ctrl->timeout = 1;
+          atomicOr(P.status, kStatusTimeout);
         }
-        float acc = a0 + a1;
-        acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-        acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-        acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-        if (p == my_p && (qi & 1) == my_qpar) mine[qi >> 1] = acc;
+        const int tok = tok_begin + it * T;
+        mbar_expect_tx(&ctrl->full[s], kStageBytes);
+        if (P.head_major)
+          tma_load_4d(stages + (size_t)s * kStageBytes, &P.kmap, &ctrl->full[s], 0, tok, h0, kv_b);
+        else
+          tma_load_4d(stages + (size_t)s * kStageBytes, &P.kmap, &ctrl->full[s], 0, h0, tok, kv_b);
       }
     }
-    // append the scores above the threshold
-    const int tok = tok_begin + it * T + tw * 16 + my_p * 4 + r;
-    const bool in_range = tok < part_hi;
+  } else {
+    // ------------------------------------------------------------ consumer warps
+    // Group g takes tiles g, g+G, ...; inside a tile a warp owns (kv head hh, 16 consecutive
+    // tokens): 4 passes of 4 rows, 8 lanes per 256-byte row.
+    const int grp = warp >> 3, w8 = warp & 7;
+    const int hh = w8 % HG;
+    const int tw = w8 / HG;
+    const int r = lane >> 3, j = lane & 7;
+    const int b2 = (j >> 2) & 1, b1 = (j >> 1) & 1, b0l = j & 1;
+    const int my_p = j >> 1;  // pass whose score this lane ends up with
+    const int my_qpar = b0l;  // parity of the queries it ends up with
+
+    // query fragments: dims [8j,8j+8) and [64+8j,64+8j+8) of each query, packed fp16
+    uint32_t qh[NQ][8];
+#pragma unroll
+    for (int qi = 0; qi < NQ; ++qi) {
+      if (qi < P.nq_valid) {
+        const int bq = b0 + qi / P.group;
+        const int hq = (h0 + hh) * P.group + qi % P.group;
+        const __half* qp = P.q + ((size_t)bq * P.hq + hq) * kHeadDim;
+        const uint4 a = *reinterpret_cast<const uint4*>(qp + 8 * j);
+        const uint4 b = *reinterpret_cast<const uint4*>(qp + 64 + 8 * j);
+        qh[qi][0] = a.x; qh[qi][1] = a.y; qh[qi][2] = a.z; qh[qi][3] = a.w;
+        qh[qi][4] = b.x; qh[qi][5] = b.y; qh[qi][6] = b.z; qh[qi][7] = b.w;
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) qh[qi][i] = 0u;
+      }
+    }
+
+    // the lists this lane appends to and their thresholds
+    int my_list[NV];
+    uint32_t my_thr[NV];
+    bool my_valid[NV];
 #pragma unroll
     for (int v = 0; v < NV; ++v) {
-      const uint32_t key = score_key(mine[v]);
-      const bool pass = my_valid[v] && in_range && key > my_thr[v];
-      const unsigned bal = __ballot_sync(0xffffffffu, pass);
-      if (bal) {
-        const unsigned mym = bal & grp_mask;
-        const int leader = mym ? (__ffs(mym) - 1) : 0;
-        int basepos = 0;
-        if (pass && lane == leader) basepos = atomicAdd(&ctrl->cnt[my_list[v]], __popc(mym));
-        basepos = __shfl_sync(0xffffffffu, basepos, leader);
-        if (pass) {
-          const int pos = basepos + __popc(mym & lt_mask);
-          if (pos < cap) {
-            keys[(size_t)my_list[v] * cap + pos] = key;
-            idxs[(size_t)my_list[v] * cap + pos] = tok;
+      const int qi = 2 * v + my_qpar;
+      my_valid[v] = (NQ == 1) ? (b0l == 0) : (qi < P.nq_valid && qi < NQ);
+      my_list[v] = hh * NQ + ((NQ == 1) ? 0 : min(qi, NQ - 1));
+      my_thr[v] = 0u;
+    }
+    const unsigned grp_mask = my_qpar ? 0xAAAAAAAAu : 0x55555555u;
+    const unsigned lt_mask = (1u << lane) - 1u;
+
+    const uint32_t stage0 = smem_u32(stages);
+    const uint32_t row_off = (uint32_t)(((tw * 16 + r) * HG + hh) * kRowBytes + j * 16);
+    const int iters = ceil_div(my_ntiles, G);
+    const int SG = S / G;  // stages in this group's ring
+
+#pragma unroll 1
+    for (int jt = 0; jt < iters; ++jt) {
+      const int it = jt * G + grp;
+      if (it < my_ntiles) {
+        const int s = (jt % SG) * G + grp;
+        if (!mbar_wait(&ctrl->full[s], (unsigned)((jt / SG) & 1))) {
+          if (lane == 0) {
+            ctrl->timeout = 1;
+            atomicOr(P.status, kStatusTimeout);
+          }
+        }
+        const uint32_t base = stage0 + (uint32_t)s * kStageBytes + row_off;
+        float part_sum[NQ][4];
+        if (!(P.debug & 1)) {
+#pragma unroll
+          for (int p = 0; p < 4; ++p) {
+            const uint32_t addr = base + (uint32_t)(p * 4 * HG * kRowBytes);
+            const uint4 a = lds128(addr);
+            const uint4 b = lds128(addr + 128);
+            const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int qi = 0; qi < NQ; ++qi) {
+              float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+              for (int i = 0; i < 8; i += 2) {
+                fma_pair<MIXED>(a0, a1, w[i], qh[qi][i]);
+                fma_pair<MIXED>(a2, a3, w[i + 1], qh[qi][i + 1]);
+              }
+              part_sum[qi][p] = (a0 + a1) + (a2 + a3);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int qi = 0; qi < NQ; ++qi)
+#pragma unroll
+            for (int p = 0; p < 4; ++p) part_sum[qi][p] = 0.f;
+        }
+        // the stage is free as soon as this warp's loads have returned
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ctrl->empty[s]);
+
+        // transposing butterfly over the 8 lanes of a row: after three exchange steps each lane
+        // holds the complete dot product of pass (j >> 1) for the queries of parity (j & 1)
+        float mine[NV];
+        float red2[NQ];
+#pragma unroll
+        for (int qi = 0; qi < NQ; ++qi) {
+          const float s0 = b2 ? part_sum[qi][0] : part_sum[qi][2];
+          const float s1 = b2 ? part_sum[qi][1] : part_sum[qi][3];
+          float k0 = b2 ? part_sum[qi][2] : part_sum[qi][0];
+          float k1 = b2 ? part_sum[qi][3] : part_sum[qi][1];
+          k0 += __shfl_xor_sync(0xffffffffu, s0, 4);
+          k1 += __shfl_xor_sync(0xffffffffu, s1, 4);
+          const float s2 = b1 ? k0 : k1;
+          float kk = b1 ? k1 : k0;
+          kk += __shfl_xor_sync(0xffffffffu, s2, 2);
+          red2[qi] = kk;
+        }
+        if constexpr (NQ == 1) {
+          mine[0] = red2[0] + __shfl_xor_sync(0xffffffffu, red2[0], 1);
+        } else {
+#pragma unroll
+          for (int v = 0; v < NV; ++v) {
+            const float snd = b0l ? red2[2 * v] : red2[2 * v + 1];
+            float kept = b0l ? red2[2 * v + 1] : red2[2 * v];
+            kept += __shfl_xor_sync(0xffffffffu, snd, 1);
+            mine[v] = kept;
+          }
+        }
+        // append the scores above the threshold
+        const int tok = tok_begin + it * T + tw * 16 + my_p * 4 + r;
+        const bool in_range = tok < part_hi;
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+          const uint32_t key = score_key(mine[v]);
+          const bool pass = my_valid[v] && in_range && key > my_thr[v];
+          const unsigned bal = __ballot_sync(0xffffffffu, pass);
+          if (bal) {
+            const unsigned mym = bal & grp_mask;
+            const int leader = mym ? (__ffs(mym) - 1) : 0;
+            int basepos = 0;
+            if (pass && lane == leader) basepos = atomicAdd(&ctrl->cnt[my_list[v]], __popc(mym));
+            basepos = __shfl_sync(0xffffffffu, basepos, leader);
+            if (pass) {
+              const int pos = basepos + __popc(mym & lt_mask);
+              if (pos < cap) {
+                keys[(size_t)my_list[v] * cap + pos] = key;
+                idxs[(size_t)my_list[v] * cap + pos] = tok;
+              } else {
+                atomicOr(P.status, kStatusOverflow);
+              }
+            }
           }
         }
       }
-    }
-    __syncthreads();  // everyone is done with this stage
-    if (tid == 0 && it + P.nstages < my_ntiles) issue(it + P.nstages);
-    // Lists that could overflow are cut back to their k best.  The decision was taken by
-    // thread 0 after the previous barrier, so every thread sees the same one; it leaves room
-    // for the two tiles that may be appended before the cut happens.
-    const int need = ctrl->need[it & 1];
-    if (need) {
+      // Every R iterations all consumer warps meet; a list that could overflow before the next
+      // meeting is cut back to its k best.  The counters are settled between the two barriers,
+      // so every thread takes the same decision.
+      if ((jt + 1) % R == 0) {
+        consumer_sync();
+        int need = 0;
 #pragma unroll
-      for (int l = 0; l < NL; ++l)
-        if ((need >> l) & 1)
-          compact_list(keys + (size_t)l * cap, idxs + (size_t)l * cap, ctrl, l, k, tid);
+        for (int l = 0; l < NL; ++l)
+          if (ctrl->cnt[l] > cap - R * G * T) need |= 1 << l;
+        consumer_sync();
+        if (need) {
 #pragma unroll
-      for (int v = 0; v < NV; ++v) my_thr[v] = ctrl->thr[my_list[v]];
-    }
-    if (tid == 0) {
-      int m = 0;
+          for (int l = 0; l < NL; ++l)
+            if ((need >> l) & 1)
+              compact_list(keys + (size_t)l * cap, idxs + (size_t)l * cap, ctrl, l, k, cap, tid);
 #pragma unroll
-      for (int l = 0; l < NL; ++l)
-        if (ctrl->cnt[l] > cap - 2 * T) m |= 1 << l;
-      ctrl->need[(it + 1) & 1] = m;
+          for (int v = 0; v < NV; ++v) my_thr[v] = ctrl->thr[my_list[v]];
+        }
+      }
     }
   }
   __syncthreads();
@@ -332,7 +399,7 @@ size_t merge_scratch_bytes(int nl, int per) { return sizeof(MergeScratch) + (siz
 // ---------------------------------------------------------------------------- launcher
 template <int HG, int NQ>
 static cudaError_t launch_one(const ScanParams& P, int grid, size_t smem, cudaStream_t stream) {
-  auto kern = scan_select_kernel<HG, NQ>;
+  auto kern = (P.debug & 2) ? scan_select_kernel<HG, NQ, false> : scan_select_kernel<HG, NQ, true>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   if (P.m.cluster > 8) {
@@ -372,7 +439,7 @@ namespace ra {
 
 template <int HG, int NQ>
 static int max_clusters_one(int cluster, size_t smem) {
-  auto kern = scan_select_kernel<HG, NQ>;
+  auto kern = scan_select_kernel<HG, NQ, true>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
     (void)cudaGetLastError();
     return 0;

@@ -19,6 +19,7 @@ struct ScanParams {
   int nparts;                // parts (segments x splits) per (batch row, head)
   int part_len;              // tokens per part
   int head_major;            // 1: table is [H, N, 128] (centroids); one head per CTA
+  int debug;                 // tuning aid: bit 0 = stream the tiles but skip the scoring
 };
 
 size_t scan_smem_bytes(int nl, int cap, int nstages);
