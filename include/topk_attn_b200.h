@@ -103,6 +103,41 @@ int ra_legacy_retrieval_attention(const void* q, const void* k, const void* v, v
                                   void* stream);
 size_t ra_legacy_workspace_bytes(int32_t batch, int32_t num_tokens, int32_t topk_per_chunk);
 
+/* ---- sequence-sharded decode (no counterpart in the reference, which is single-device) ----
+ * The token axis is cut over ranks.  Per step every rank (1) calls ra_gemv_topk on its shard
+ * with index_base = first global token id of the shard, (2) all-gathers the [B,Hq,k] score and
+ * id buffers of all ranks, (3) calls ra_merge_attend, which selects the global top-k out of the
+ * num_parts*k candidates and mixes only the V rows this rank holds into an un-normalised
+ * partial, (4) all-gathers the partials and (5) calls ra_lse_combine. */
+typedef struct ra_merge_params {
+  const float* cand_scores;    /* fp32 [num_parts, batch, num_q_heads, topk] */
+  const int32_t* cand_indices; /* int32, same shape, global token ids */
+  int32_t num_parts;
+  const void* v;               /* this rank's value cache */
+  void* out;                   /* optional fp16 [batch, num_q_heads, 128], normalised */
+  float* out_partial;          /* optional fp32 [batch, num_q_heads, 130]: 128 un-normalised
+                                  sums, their weight, the maximum of sm_scale*score */
+  int32_t batch, num_q_heads, num_kv_heads, head_dim;
+  int32_t num_tokens;          /* rows of v */
+  int64_t kv_batch_stride, kv_token_stride, kv_head_stride;
+  int32_t topk;
+  float sm_scale;
+  int32_t own_base;            /* global id of row 0 of v; ids outside
+                                  [own_base, own_base + num_tokens) are not mixed */
+  int32_t* out_indices;        /* optional int32 [batch, num_q_heads, topk]: the global winners */
+  float* out_scores;           /* optional fp32, same shape */
+  void* workspace;             /* >= 256 bytes, 256-byte aligned (status word only) */
+  size_t workspace_bytes;
+  void* stream;
+} ra_merge_params;
+
+int ra_merge_attend(const ra_merge_params* p);
+
+/* out[r,:] = sum_p w_p o_p / sum_p w_p l_p, w_p = exp(m_p - max_p m_p), over num_parts partials of
+ * the layout ra_merge_attend writes ([num_parts, rows, 130]); out is fp16 [rows, 128].  The
+ * log-sum-exp merge of baseline_1.cu:549-598 as a stand-alone step. */
+int ra_lse_combine(const float* partials, int32_t num_parts, int32_t rows, void* out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,92 @@
+"""Host logic of the sequence-sharded step on CPU: two gloo ranks, the compute steps replaced by
+oracle-based stand-ins (test code only), the exchange/merge/combine orchestration is the
+product's."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import topk_attn_oracle as O
+from topk_attn_b200.sharded import ShardedTopkAttention
+
+
+class OracleBackend:
+    """CPU stand-in for the three kernels, built from the oracle."""
+
+    def select(self, q, k, topk, index_base):
+        s = O.full_scores(q, k)
+        sc, idx = torch.topk(s, topk, dim=-1)
+        return (idx + index_base).int().contiguous(), sc.contiguous()
+
+    def merge_partial(self, cand_sc, cand_idx, v, topk, sm_scale, own_base):
+        G, B, Hq, k = cand_sc.shape
+        sc = cand_sc.permute(1, 2, 0, 3).reshape(B, Hq, G * k)
+        ix = cand_idx.permute(1, 2, 0, 3).reshape(B, Hq, G * k).long()
+        gs, pos = torch.topk(sc, topk, dim=-1)
+        gi = torch.gather(ix, -1, pos)
+        n = v.size(-3)
+        mine = (gi >= own_base) & (gi < own_base + n)
+        m = gs.max(-1).values * sm_scale
+        e = torch.where(mine, torch.exp(gs * sm_scale - m.unsqueeze(-1)), torch.zeros_like(gs))
+        loc = torch.where(mine, gi - own_base, torch.zeros_like(gi))
+        out = torch.zeros(B, Hq, 130)
+        for b in range(B):
+            vs = O._gather_rows(v, b, Hq, loc[b])
+            out[b, :, :128] = torch.einsum("hs,hsd->hd", e[b], vs)
+        out[..., 128] = e.sum(-1)
+        out[..., 129] = m
+        return out
+
+    def combine(self, partials):
+        o, l, m = partials[..., :128], partials[..., 128], partials[..., 129]
+        return O.lse_combine(o, m, l).half()
+
+
+def _worker(rank, world, port, q, k, v, topk, scale, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        n = k.size(0) // world
+        op = ShardedTopkAttention(topk, scale, backend=OracleBackend())
+        out = op.step(q, k[rank * n:(rank + 1) * n].contiguous(), v[rank * n:(rank + 1) * n].contiguous())
+        ret[rank] = out.float()
+    finally:
+        dist.destroy_process_group()
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+@pytest.mark.parametrize("topk,n", [(64, 2048), (300, 512)])
+def test_two_gloo_ranks_match_single_device(topk, n):
+    g = torch.Generator().manual_seed(5)
+    q = (torch.randn(2, 8, 128, generator=g) / 11.3).half()
+    k = torch.randn(n, 2, 128, generator=g).half()
+    v = torch.randn(n, 2, 128, generator=g).half()
+    ref, _, _ = O.topk_sparse_attention(q, k, v, topk, 0.7)
+    world = 2
+    ret = mp.Manager().dict()
+    mp.spawn(_worker, args=(world, _free_port(), q, k, v, topk, 0.7, ret), nprocs=world, join=True)
+    for r in range(world):
+        O.check_output(ref, ret[r])
+    assert torch.equal(ret[0], ret[1])        # every rank ends with the same output
+
+
+def test_short_shard_is_padded():
+    """A shard with fewer than k tokens proposes all of them and pads with (-inf, -1)."""
+    g = torch.Generator().manual_seed(6)
+    q = (torch.randn(1, 2, 128, generator=g) / 11.3).half()
+    k = torch.randn(40, 2, 128, generator=g).half()
+    op = ShardedTopkAttention(64, 1.0, backend=OracleBackend())
+    idx, sc = op.local_candidates(q, k, 1000)
+    assert idx.shape == (1, 2, 64) and (idx[..., 40:] == -1).all() and torch.isinf(sc[..., 40:]).all()
+    assert idx[..., :40].min().item() >= 1000

@@ -17,6 +17,7 @@ RA_ERR_UNSUPPORTED = 2
 RA_ERR_WORKSPACE = 3
 RA_ERR_CUDA = 4
 RA_ERR_DEVICE_TIMEOUT = 5
+RA_ERR_DEVICE_CHECK = 7
 
 
 class RaParams(C.Structure):
@@ -30,6 +31,21 @@ class RaParams(C.Structure):
         ("topk", C.c_int32), ("num_segments", C.c_int32), ("sm_scale", C.c_float),
         ("index_base", C.c_int32),
         ("out_indices", C.c_void_p), ("out_scores", C.c_void_p), ("out_lse", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("stream", C.c_void_p),
+    ]
+
+
+class RaMergeParams(C.Structure):
+    """Mirror of ``struct ra_merge_params``."""
+    _fields_ = [
+        ("cand_scores", C.c_void_p), ("cand_indices", C.c_void_p), ("num_parts", C.c_int32),
+        ("v", C.c_void_p), ("out", C.c_void_p), ("out_partial", C.c_void_p),
+        ("batch", C.c_int32), ("num_q_heads", C.c_int32), ("num_kv_heads", C.c_int32),
+        ("head_dim", C.c_int32), ("num_tokens", C.c_int32),
+        ("kv_batch_stride", C.c_int64), ("kv_token_stride", C.c_int64),
+        ("kv_head_stride", C.c_int64),
+        ("topk", C.c_int32), ("sm_scale", C.c_float), ("own_base", C.c_int32),
+        ("out_indices", C.c_void_p), ("out_scores", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("stream", C.c_void_p),
     ]
 
@@ -68,6 +84,8 @@ def _declare(l: C.CDLL) -> None:
         "ra_check_status": (C.c_int, [vp, vp]),
         "ra_legacy_retrieval_attention": (C.c_int, [vp, vp, vp, vp, i32, i32, i32, i32, vp, sz, vp]),
         "ra_legacy_workspace_bytes": (sz, [i32, i32, i32]),
+        "ra_merge_attend": (C.c_int, [C.POINTER(RaMergeParams)]),
+        "ra_lse_combine": (C.c_int, [vp, i32, i32, vp, vp]),
     }
     for name, (res, args) in sigs.items():
         if not hasattr(l, name):

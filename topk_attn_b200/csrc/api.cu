@@ -395,6 +395,7 @@ int run(const ra_params* p, bool attend) {
     mp.m.sel_idx = p->out_indices; mp.m.sel_score = p->out_scores;
   }
   mp.cand_score = sp.m.sel_score; mp.cand_idx = sp.m.sel_idx;
+  mp.part_len = s.topk; mp.part_stride = s.topk; mp.row_stride = (long long)parts * s.topk;
   mp.m_total = parts * s.topk; mp.cap = pl.cap2; mp.group = c.group;
   e = launch_merge_attend(mp, s.batch * s.hq, pl.smem2, stream);
   if (e != cudaSuccess) return cuda_fail(e, "merge_attend launch");
@@ -446,6 +447,59 @@ int ra_check_status(void* workspace, void* stream) {
                                           : "a candidate list overflowed";
     return RA_ERR_DEVICE_CHECK;
   }
+  return RA_OK;
+}
+
+int ra_merge_attend(const ra_merge_params* p) {
+  if (!p) return invalid("params is null");
+  if (!p->cand_scores || !p->cand_indices) return invalid("candidate buffers are null");
+  if (p->head_dim != kHeadDim) return unsupported("head_dim must be 128");
+  if (p->batch < 1 || p->num_q_heads < 1 || p->num_kv_heads < 1 || p->num_parts < 1 ||
+      p->topk < 1 || p->num_tokens < 0)
+    return invalid("sizes must be positive");
+  if (p->num_q_heads % p->num_kv_heads) return invalid("num_kv_heads must divide num_q_heads");
+  const bool attend = p->out || p->out_partial;
+  if (attend && !p->v) return invalid("v is null");
+  if (!attend && !p->out_indices) return invalid("nothing to compute");
+  if (!(p->sm_scale > 0.f)) return invalid("sm_scale must be positive");
+  if (!p->workspace || p->workspace_bytes < kStatusBytes) {
+    g_last_error = "workspace missing or too small";
+    return RA_ERR_WORKSPACE;
+  }
+  Plan pl;
+  const long long m_total = (long long)p->num_parts * p->topk;
+  if (m_total > (1 << 20) || !plan_merge((int)m_total, p->topk, pl))
+    return unsupported("too many candidates for the merge kernel");
+  MergeParams mp;
+  memset(&mp, 0, sizeof mp);
+  MergeArgs& m = mp.m;
+  m.topk = p->topk; m.per = pl.per2; m.cluster = pl.cluster2;
+  m.out_mode = p->out_partial ? kOutPartial : (p->out ? kOutFinal : kOutNone);
+  m.hq_total = p->num_q_heads; m.list_pitch = p->topk; m.list_off = 0; m.index_base = 0;
+  m.own_lo = p->own_base; m.own_hi = p->own_base + p->num_tokens; m.id_shift = p->own_base;
+  m.n_tokens = p->num_tokens; m.status = static_cast<unsigned*>(p->workspace);
+  m.sel_idx = p->out_indices; m.sel_score = p->out_scores;
+  m.v = static_cast<const __half*>(p->v);
+  m.v_batch_stride = p->kv_batch_stride; m.v_token_stride = p->kv_token_stride;
+  m.v_head_stride = p->kv_head_stride;
+  m.out = static_cast<__half*>(p->out); m.out_lse = nullptr; m.out_partial = p->out_partial;
+  m.scale_log2e = p->sm_scale * kLog2e; m.sm_scale = p->sm_scale;
+  mp.cand_score = p->cand_scores; mp.cand_idx = p->cand_indices;
+  mp.part_len = p->topk;
+  mp.part_stride = (long long)p->batch * p->num_q_heads * p->topk;
+  mp.row_stride = p->topk;
+  mp.m_total = (int)m_total; mp.cap = pl.cap2; mp.group = p->num_q_heads / p->num_kv_heads;
+  cudaError_t e = launch_merge_attend(mp, p->batch * p->num_q_heads, pl.smem2,
+                                      static_cast<cudaStream_t>(p->stream));
+  if (e != cudaSuccess) return cuda_fail(e, "merge_attend launch");
+  return RA_OK;
+}
+
+int ra_lse_combine(const float* partials, int32_t num_parts, int32_t rows, void* out, void* stream) {
+  if (!partials || !out || num_parts < 1 || rows < 1) return invalid("bad lse_combine arguments");
+  cudaError_t e = launch_lse_combine(partials, num_parts, rows, static_cast<__half*>(out),
+                                     static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "lse_combine launch");
   return RA_OK;
 }
 

@@ -29,11 +29,12 @@ merge_attend_kernel(const __grid_constant__ MergeParams P) {
   const int chunk = ceil_div(P.m_total, C);
   const int lo = crank * chunk;
   const int n = max(0, min(P.m_total, lo + chunk) - lo);
-  const float* cs = P.cand_score + (size_t)row * P.m_total + lo;
-  const int* ci = P.cand_idx + (size_t)row * P.m_total + lo;
   for (int i = tid; i < n; i += kMergeThreads) {
-    keys[i] = score_key(cs[i]);
-    idxs[i] = ci[i];
+    const int c = lo + i;
+    const int part = c / P.part_len, off = c - part * P.part_len;
+    const size_t src = (size_t)part * P.part_stride + (size_t)row * P.row_stride + off;
+    keys[i] = score_key(P.cand_score[src]);
+    idxs[i] = P.cand_idx[src];
   }
   if (tid == 0) cnt[0] = n;
   __syncthreads();
@@ -76,6 +77,29 @@ cudaError_t launch_merge_attend(const MergeParams& P, int rows, size_t smem, cud
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, kern, P);
+}
+
+__global__ void __launch_bounds__(kHeadDim)
+lse_combine_kernel(const float* __restrict__ partials, int parts, int rows, __half* __restrict__ out) {
+  const int row = blockIdx.x, d = threadIdx.x;
+  float m = -INFINITY;
+  for (int p = 0; p < parts; ++p)
+    m = fmaxf(m, partials[((size_t)p * rows + row) * (kHeadDim + 2) + kHeadDim + 1]);
+  float o = 0.f, l = 0.f;
+  for (int p = 0; p < parts; ++p) {
+    const float* src = partials + ((size_t)p * rows + row) * (kHeadDim + 2);
+    const float lp = src[kHeadDim];
+    const float w = (lp > 0.f) ? __expf(src[kHeadDim + 1] - m) : 0.f;
+    o = fmaf(w, src[d], o);
+    l = fmaf(w, lp, l);
+  }
+  out[(size_t)row * kHeadDim + d] = __float2half_rn(o / l);
+}
+
+cudaError_t launch_lse_combine(const float* partials, int parts, int rows, __half* out,
+                               cudaStream_t stream) {
+  lse_combine_kernel<<<rows, kHeadDim, 0, stream>>>(partials, parts, rows, out);
+  return cudaGetLastError();
 }
 
 }  // namespace ra

@@ -6,8 +6,10 @@ namespace ra {
 
 struct MergeParams {
   MergeArgs m;              // m.topk winners out of m_total candidates per (batch row, head)
-  const float* cand_score;  // [B*Hq, m_total]
-  const int* cand_idx;      // [B*Hq, m_total]
+  const float* cand_score;  // candidate c of row r: [ (c / part_len) * part_stride +
+  const int* cand_idx;      //                       r * row_stride + c % part_len ]
+  long long part_stride, row_stride;
+  int part_len;
   int m_total;
   int cap;                  // ceil(m_total / cluster)
   int group;                // query heads per kv head
@@ -15,5 +17,9 @@ struct MergeParams {
 
 size_t merge_attend_smem_bytes(int per, int cap);
 cudaError_t launch_merge_attend(const MergeParams& P, int rows, size_t smem, cudaStream_t stream);
+// out[r, :] = sum_p w_p o_p / sum_p w_p l_p with w_p = exp(m_p - max m); partials are
+// [parts][rows][130] = 128 un-normalised sums, their weight l, their maximum m.
+cudaError_t launch_lse_combine(const float* partials, int parts, int rows, __half* out,
+                               cudaStream_t stream);
 
 }  // namespace ra

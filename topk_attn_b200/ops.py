@@ -107,6 +107,55 @@ def gemv_topk(q: Tensor, k: Tensor, topk: int, num_segments: int = 1, index_base
     return idx, sc
 
 
+def merge_attend(cand_scores: Tensor, cand_indices: Tensor, v: Tensor, topk: int, sm_scale: float,
+                 own_base: int, partial: bool = True, return_indices: bool = False):
+    """Select the global top-k out of ``cand_* [parts,B,Hq,topk]`` (global ids) and mix the V rows
+    held in ``v`` (global ids own_base .. own_base+N).  Returns the fp32 partial [B,Hq,130]
+    (128 un-normalised sums, weight, maximum) or, with ``partial=False``, the fp16 output."""
+    parts, B, Hq, k = cand_scores.shape
+    if cand_scores.dtype != torch.float32 or cand_indices.dtype != torch.int32:
+        raise ValueError("candidates must be fp32 scores and int32 ids")
+    if not (cand_scores.is_contiguous() and cand_indices.is_contiguous() and v.is_contiguous()):
+        raise ValueError("tensors must be contiguous")
+    N, Hkv = v.size(-3), v.size(-2)
+    dev = cand_scores.device
+    p = capi.RaMergeParams()
+    p.cand_scores, p.cand_indices, p.num_parts = cand_scores.data_ptr(), cand_indices.data_ptr(), parts
+    p.v = v.data_ptr()
+    out = None
+    if partial:
+        out = torch.empty(B, Hq, 130, dtype=torch.float32, device=dev)
+        p.out_partial = out.data_ptr()
+    else:
+        out = torch.empty(B, Hq, 128, dtype=torch.float16, device=dev)
+        p.out = out.data_ptr()
+    p.batch, p.num_q_heads, p.num_kv_heads, p.head_dim, p.num_tokens = B, Hq, Hkv, 128, N
+    p.kv_batch_stride = N * Hkv * 128 if v.dim() == 4 else 0
+    p.kv_token_stride, p.kv_head_stride = Hkv * 128, 128
+    p.topk, p.sm_scale, p.own_base = topk, sm_scale, own_base
+    idx = sc = None
+    if return_indices:
+        idx = torch.empty(B, Hq, topk, dtype=torch.int32, device=dev)
+        sc = torch.empty(B, Hq, topk, dtype=torch.float32, device=dev)
+        p.out_indices, p.out_scores = idx.data_ptr(), sc.data_ptr()
+    ws = workspace(256, dev)
+    p.workspace, p.workspace_bytes, p.stream = ws.data_ptr(), ws.numel(), _stream_ptr()
+    capi.check(capi.lib().ra_merge_attend(C.byref(p)))
+    return (out, idx, sc) if return_indices else out
+
+
+def lse_combine(partials: Tensor, out: Optional[Tensor] = None) -> Tensor:
+    """partials fp32 [parts, B, Hq, 130] -> fp16 [B, Hq, 128]."""
+    parts, B, Hq, w = partials.shape
+    if w != 130 or partials.dtype != torch.float32 or not partials.is_contiguous():
+        raise ValueError("partials must be contiguous fp32 [parts, B, Hq, 130]")
+    if out is None:
+        out = torch.empty(B, Hq, 128, dtype=torch.float16, device=partials.device)
+    capi.check(capi.lib().ra_lse_combine(partials.data_ptr(), parts, B * Hq, out.data_ptr(),
+                                         _stream_ptr()))
+    return out
+
+
 def check_status(device: Optional[torch.device] = None) -> None:
     """Synchronise the current stream and raise if a kernel abandoned a bounded wait."""
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else device

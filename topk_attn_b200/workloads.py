@@ -139,6 +139,25 @@ def fused_topk_128k(seed: int = 2, device="cpu", batch: int = 4, n: int = 131072
     return Workload("cfg2_fused_topk", q, k, v, topk=topk)
 
 
+def fused_topk_128k_shard(rank: int, world: int, seed: int = 2, device="cpu", batch: int = 4,
+                          n_local: int = 131072, heads: int = 32, topk: int = 2048,
+                          frac: float = 0.02) -> Workload:
+    """One rank's token shard of the headline geometry stretched over ``world`` ranks (weak
+    scaling: the context is world * n_local).  The query depends on ``seed`` only, so it is
+    identical on every rank; the shard's cache is drawn from ``seed * 2**16 + rank``."""
+    g0 = _gen(device, seed)
+    q = (torch.randn(batch, heads, 128, generator=g0, device=device) / math.sqrt(128)).half()
+    qdir = q.float() / q.float().norm(dim=-1, keepdim=True)
+    g = _gen(device, seed * (1 << 16) + rank)
+    k = _randn16((batch, n_local, heads, 128), g, device)
+    v = _randn16((batch, n_local, heads, 128), g, device)
+    for b in range(batch):
+        _plant(k[b], qdir[b], frac, g)
+    w = Workload("cfg2_token_shard", q, k, v, topk=topk)
+    w.extra.update(index_base=rank * n_local, n_shards=world)
+    return w
+
+
 def centroid_retrieval(seed: int = 3, device="cpu", heads: int = 32, csz: int = 2048,
                        clen: int = 64, topc: int = 64, noise: float = 0.3) -> Workload:
     """Configuration 3: B=1, centroids [H,CSZ,D] ~ N(0,1); member keys
