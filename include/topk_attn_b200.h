@@ -103,6 +103,59 @@ int ra_legacy_retrieval_attention(const void* q, const void* k, const void* v, v
                                   void* stream);
 size_t ra_legacy_workspace_bytes(int32_t batch, int32_t num_tokens, int32_t topk_per_chunk);
 
+/* Attention over given key ids: softmax(sm_scale * q.K[id]) . V[id].  Replaces
+ * MHAFlashDecodeKernel (baseline_1.cu:324-610; prototype flash_decoding.cu:100-388), whose
+ * kv_indices are [H, S] global token ids shared by the batch (flash_decoding.cu:105); sm_scale is
+ * explicit (the reference applies rsqrt(D) inside, baseline_1.cu:369). */
+typedef struct ra_gather_params {
+  const void* q;            /* fp16 [batch, num_q_heads, 128] */
+  const void* k;            /* fp16 caches, strides below */
+  const void* v;
+  void* out;                /* fp16 [batch, num_q_heads, 128] */
+  int32_t batch, num_q_heads, num_kv_heads, head_dim, num_tokens;
+  int64_t kv_batch_stride, kv_token_stride, kv_head_stride;
+  const int32_t* indices;   /* int32 [batch or 1, num_q_heads, num_indices] */
+  int32_t num_indices;
+  int64_t indices_batch_stride; /* elements; 0 = one list per head shared by the batch */
+  float sm_scale;
+  float* out_lse;           /* optional fp32 [batch, num_q_heads, 2] */
+  void* workspace;          /* >= 256 bytes (status word) */
+  size_t workspace_bytes;
+  void* stream;
+} ra_gather_params;
+
+int ra_gathered_attention(const ra_gather_params* p);
+
+/* Centroid-only retrieval: score the num_centers centroids of every head, keep the
+ * top_clusters best, expand cluster c to its member tokens c*cluster_len .. +cluster_len-1 in
+ * descending order of the centroid scores, and (when k, v and out are given) attend over all
+ * member tokens.  Replaces gemv_topk_kernel / gemv_topk_cluster_kernel
+ * (center_only_topk/gemv_topk.cu:157-280, :283-457) and, with attention, the pipelines of
+ * center_only_topk/baselines.cu:546-973. */
+typedef struct ra_center_params {
+  const void* q;            /* fp16 [batch, num_heads, 128] */
+  const void* centers;      /* fp16 [num_heads, num_centers, 128] (center_only_topk/gemv_topk.cu:99) */
+  int32_t batch, num_heads, head_dim;
+  int32_t num_centers;      /* CSZ */
+  int32_t cluster_len;      /* CLEN */
+  int32_t top_clusters;     /* TOPC */
+  int32_t* out_cluster_ids; /* optional int32 [batch, num_heads, top_clusters], unordered */
+  int32_t* out_indices;     /* optional int32 [batch, num_heads, top_clusters*cluster_len] */
+  const void* k;            /* optional fp16 [num_tokens, num_heads, 128] (or per batch row) */
+  const void* v;
+  void* out;                /* optional fp16 [batch, num_heads, 128] */
+  int32_t num_tokens;
+  int64_t kv_batch_stride, kv_token_stride, kv_head_stride;
+  float sm_scale;
+  void* workspace;          /* ra_center_workspace_bytes() */
+  size_t workspace_bytes;
+  void* stream;
+} ra_center_params;
+
+int ra_center_only_topk(const ra_center_params* p);
+size_t ra_center_workspace_bytes(int32_t batch, int32_t num_heads, int32_t num_centers,
+                                 int32_t top_clusters);
+
 /* ---- sequence-sharded decode (no counterpart in the reference, which is single-device) ----
  * The token axis is cut over ranks.  Per step every rank (1) calls ra_gemv_topk on its shard
  * with index_base = first global token id of the shard, (2) all-gathers the [B,Hq,k] score and
@@ -113,6 +166,9 @@ typedef struct ra_merge_params {
   const float* cand_scores;    /* fp32 [num_parts, batch, num_q_heads, topk] */
   const int32_t* cand_indices; /* int32, same shape, global token ids */
   int32_t num_parts;
+  int64_t cand_part_stride;    /* elements between two parts in both buffers; 0 = dense
+                                  (batch*num_q_heads*topk).  Lets scores and ids travel as the two
+                                  halves of one all-gathered buffer. */
   const void* v;               /* this rank's value cache */
   void* out;                   /* optional fp16 [batch, num_q_heads, 128], normalised */
   float* out_partial;          /* optional fp32 [batch, num_q_heads, 130]: 128 un-normalised

@@ -16,13 +16,19 @@ from topk_attn_b200.sharded import ShardedTopkAttention
 class OracleBackend:
     """CPU stand-in for the three kernels, built from the oracle."""
 
-    def select(self, q, k, topk, index_base):
+    def select(self, q, k, topk, index_base, out=None):
         s = O.full_scores(q, k)
         sc, idx = torch.topk(s, topk, dim=-1)
-        return (idx + index_base).int().contiguous(), sc.contiguous()
+        idx, sc = (idx + index_base).int().contiguous(), sc.contiguous()
+        if out is not None:
+            out[0].copy_(idx)
+            out[1].copy_(sc)
+            return out
+        return idx, sc
 
     def merge_partial(self, cand_sc, cand_idx, v, topk, sm_scale, own_base):
         G, B, Hq, k = cand_sc.shape
+        assert cand_sc.stride()[1:] == (Hq * k, k, 1) and cand_idx.stride() == cand_sc.stride()
         sc = cand_sc.permute(1, 2, 0, 3).reshape(B, Hq, G * k)
         ix = cand_idx.permute(1, 2, 0, 3).reshape(B, Hq, G * k).long()
         gs, pos = torch.topk(sc, topk, dim=-1)

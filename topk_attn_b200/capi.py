@@ -39,13 +39,43 @@ class RaMergeParams(C.Structure):
     """Mirror of ``struct ra_merge_params``."""
     _fields_ = [
         ("cand_scores", C.c_void_p), ("cand_indices", C.c_void_p), ("num_parts", C.c_int32),
-        ("v", C.c_void_p), ("out", C.c_void_p), ("out_partial", C.c_void_p),
+        ("cand_part_stride", C.c_int64), ("v", C.c_void_p), ("out", C.c_void_p), ("out_partial", C.c_void_p),
         ("batch", C.c_int32), ("num_q_heads", C.c_int32), ("num_kv_heads", C.c_int32),
         ("head_dim", C.c_int32), ("num_tokens", C.c_int32),
         ("kv_batch_stride", C.c_int64), ("kv_token_stride", C.c_int64),
         ("kv_head_stride", C.c_int64),
         ("topk", C.c_int32), ("sm_scale", C.c_float), ("own_base", C.c_int32),
         ("out_indices", C.c_void_p), ("out_scores", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("stream", C.c_void_p),
+    ]
+
+
+class RaGatherParams(C.Structure):
+    """Mirror of ``struct ra_gather_params``."""
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("out", C.c_void_p),
+        ("batch", C.c_int32), ("num_q_heads", C.c_int32), ("num_kv_heads", C.c_int32),
+        ("head_dim", C.c_int32), ("num_tokens", C.c_int32),
+        ("kv_batch_stride", C.c_int64), ("kv_token_stride", C.c_int64),
+        ("kv_head_stride", C.c_int64),
+        ("indices", C.c_void_p), ("num_indices", C.c_int32), ("indices_batch_stride", C.c_int64),
+        ("sm_scale", C.c_float), ("out_lse", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("stream", C.c_void_p),
+    ]
+
+
+class RaCenterParams(C.Structure):
+    """Mirror of ``struct ra_center_params``."""
+    _fields_ = [
+        ("q", C.c_void_p), ("centers", C.c_void_p),
+        ("batch", C.c_int32), ("num_heads", C.c_int32), ("head_dim", C.c_int32),
+        ("num_centers", C.c_int32), ("cluster_len", C.c_int32), ("top_clusters", C.c_int32),
+        ("out_cluster_ids", C.c_void_p), ("out_indices", C.c_void_p),
+        ("k", C.c_void_p), ("v", C.c_void_p), ("out", C.c_void_p),
+        ("num_tokens", C.c_int32),
+        ("kv_batch_stride", C.c_int64), ("kv_token_stride", C.c_int64),
+        ("kv_head_stride", C.c_int64),
+        ("sm_scale", C.c_float),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("stream", C.c_void_p),
     ]
 
@@ -85,6 +115,9 @@ def _declare(l: C.CDLL) -> None:
         "ra_legacy_retrieval_attention": (C.c_int, [vp, vp, vp, vp, i32, i32, i32, i32, vp, sz, vp]),
         "ra_legacy_workspace_bytes": (sz, [i32, i32, i32]),
         "ra_merge_attend": (C.c_int, [C.POINTER(RaMergeParams)]),
+        "ra_gathered_attention": (C.c_int, [C.POINTER(RaGatherParams)]),
+        "ra_center_only_topk": (C.c_int, [C.POINTER(RaCenterParams)]),
+        "ra_center_workspace_bytes": (sz, [i32, i32, i32, i32]),
         "ra_lse_combine": (C.c_int, [vp, i32, i32, vp, vp]),
     }
     for name, (res, args) in sigs.items():

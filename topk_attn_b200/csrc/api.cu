@@ -11,6 +11,7 @@
 #include <string>
 #include <tuple>
 
+#include "gather_attend.cuh"
 #include "merge_attend.cuh"
 #include "scan_select.cuh"
 
@@ -275,7 +276,7 @@ int encode_kmap(CUtensorMap* map, const ra_params* p, const Shape& s, int hg) {
     return RA_ERR_CUDA;
   }
   const cuuint64_t nb = s.per_batch ? (cuuint64_t)p->batch : 1;
-  const cuuint64_t bstride =
+  cuuint64_t bstride =
       s.per_batch ? (cuuint64_t)p->kv_batch_stride * 2
                   : (cuuint64_t)16 * (((cuuint64_t)p->num_tokens * p->kv_token_stride * 2 + 15) / 16);
   cuuint64_t dims[4], strides[3];
@@ -285,6 +286,7 @@ int encode_kmap(CUtensorMap* map, const ra_params* p, const Shape& s, int hg) {
     dims[0] = kHeadDim; dims[1] = p->num_tokens; dims[2] = p->num_kv_heads; dims[3] = nb;
     strides[0] = (cuuint64_t)p->kv_token_stride * 2; strides[1] = (cuuint64_t)p->kv_head_stride * 2;
     box[0] = kHeadDim; box[1] = T; box[2] = 1; box[3] = 1;
+    if (!s.per_batch) bstride = (cuuint64_t)p->num_kv_heads * p->kv_head_stride * 2;
   } else {
     dims[0] = kHeadDim; dims[1] = p->num_kv_heads; dims[2] = p->num_tokens; dims[3] = nb;
     strides[0] = (cuuint64_t)p->kv_head_stride * 2; strides[1] = (cuuint64_t)p->kv_token_stride * 2;
@@ -450,6 +452,144 @@ int ra_check_status(void* workspace, void* stream) {
   return RA_OK;
 }
 
+// Launch geometry of the gathered-attention kernel for n_entries ids per row.
+static bool plan_gather(int n_entries, int n_src, int rows, int& cluster, int& cap, int& per,
+                        size_t& smem) {
+  // enough CTAs to fill the machine, not more than 16 rows of K per thread and CTA
+  int want = 1;
+  while (want < 8 && (rows * want < 148 || ceil_div(n_entries, want) > 4096)) want <<= 1;
+  for (int c = want; c <= 8; c <<= 1) {
+    cap = ceil_div(n_entries, c);
+    per = ceil_div(n_entries, c);
+    smem = gather_attend_smem_bytes(per, cap, n_src);
+    if (smem <= kSmemBudget) {
+      cluster = c;
+      return true;
+    }
+  }
+  return false;
+}
+
+static int run_gather(const __half* q, const __half* k, const __half* v, __half* out, float* out_lse,
+                      int batch, int hq, int hkv, int n_tokens, long long bs, long long ts,
+                      long long hs, const int* src_idx, const float* src_score,
+                      long long src_bstride, long long src_hstride, int n_src, int expand_clen,
+                      int* out_token_ids, float sm_scale, unsigned* status, bool attend,
+                      cudaStream_t stream) {
+  const long long n_entries_ll = (long long)n_src * (expand_clen > 0 ? expand_clen : 1);
+  if (n_entries_ll > (1 << 20)) return unsupported("more than 2^20 ids per head");
+  const int n_entries = (int)n_entries_ll;
+  int cluster = 1, cap = 0, per = 0;
+  size_t smem = 0;
+  if (!plan_gather(n_entries, n_src, batch * hq, cluster, cap, per, smem))
+    return unsupported("id list too long for the gathered-attention kernel");
+  GatherParams gp;
+  memset(&gp, 0, sizeof gp);
+  MergeArgs& m = gp.m;
+  m.topk = n_entries; m.per = per; m.cluster = cluster; m.select_all = 1;
+  m.out_mode = attend ? kOutFinal : kOutNone;
+  m.hq_total = hq; m.list_pitch = n_entries; m.list_off = 0; m.index_base = 0;
+  m.own_lo = 0; m.own_hi = 0x7fffffff; m.id_shift = 0; m.n_tokens = n_tokens; m.status = status;
+  m.sel_idx = nullptr; m.sel_score = nullptr;
+  m.v = v; m.v_batch_stride = bs; m.v_token_stride = ts; m.v_head_stride = hs;
+  m.out = out; m.out_lse = out_lse; m.out_partial = nullptr;
+  m.scale_log2e = sm_scale * kLog2e; m.sm_scale = sm_scale;
+  gp.q = q; gp.k = k; gp.src_idx = src_idx; gp.src_score = src_score;
+  gp.src_batch_stride = src_bstride; gp.src_head_stride = src_hstride;
+  gp.n_src = n_src; gp.expand_clen = expand_clen; gp.n_entries = n_entries;
+  gp.out_token_ids = out_token_ids; gp.cap = cap; gp.group = hq / hkv;
+  cudaError_t e = launch_gather_attend(gp, batch * hq, smem, stream);
+  if (e != cudaSuccess) return cuda_fail(e, "gather_attend launch");
+  return RA_OK;
+}
+
+int ra_gathered_attention(const ra_gather_params* p) {
+  if (!p) return invalid("params is null");
+  if (!p->q || !p->k || !p->v || !p->out || !p->indices) return invalid("a required pointer is null");
+  if (p->head_dim != kHeadDim) return unsupported("head_dim must be 128");
+  if (p->batch < 1 || p->num_q_heads < 1 || p->num_kv_heads < 1 || p->num_tokens < 1 ||
+      p->num_indices < 1)
+    return invalid("sizes must be positive");
+  if (p->num_q_heads % p->num_kv_heads) return invalid("num_kv_heads must divide num_q_heads");
+  if (!(p->sm_scale > 0.f)) return invalid("sm_scale must be positive");
+  if (p->kv_token_stride % 8 || p->kv_head_stride % 8 || p->kv_batch_stride % 8)
+    return invalid("kv strides must be multiples of 8 elements");
+  if (!p->workspace || p->workspace_bytes < kStatusBytes) {
+    g_last_error = "workspace missing or too small";
+    return RA_ERR_WORKSPACE;
+  }
+  return run_gather(static_cast<const __half*>(p->q), static_cast<const __half*>(p->k),
+                    static_cast<const __half*>(p->v), static_cast<__half*>(p->out), p->out_lse,
+                    p->batch, p->num_q_heads, p->num_kv_heads, p->num_tokens, p->kv_batch_stride,
+                    p->kv_token_stride, p->kv_head_stride, p->indices, nullptr,
+                    p->indices_batch_stride, p->num_indices, p->num_indices, 0, nullptr,
+                    p->sm_scale, static_cast<unsigned*>(p->workspace), true,
+                    static_cast<cudaStream_t>(p->stream));
+}
+
+size_t ra_center_workspace_bytes(int32_t batch, int32_t num_heads, int32_t num_centers,
+                                 int32_t top_clusters) {
+  if (batch < 1 || num_heads < 1 || num_centers < 1 || top_clusters < 1) return 0;
+  Shape s;
+  s.batch = batch; s.hq = num_heads; s.hkv = num_heads; s.n = num_centers; s.topk = top_clusters;
+  s.segments = 1; s.per_batch = 0; s.head_major = 1; s.fused_ok = 1;
+  // selection scratch, then the kept cluster ids and their scores
+  return workspace_bound(s) + (size_t)batch * num_heads * top_clusters * 8 + 256;
+}
+
+int ra_center_only_topk(const ra_center_params* p) {
+  if (!p) return invalid("params is null");
+  if (!p->q || !p->centers) return invalid("q or centers is null");
+  if (p->head_dim != kHeadDim) return unsupported("head_dim must be 128");
+  if (p->batch < 1 || p->num_heads < 1 || p->num_centers < 1 || p->cluster_len < 1 ||
+      p->top_clusters < 1 || p->top_clusters > p->num_centers)
+    return invalid("sizes must be positive and top_clusters <= num_centers");
+  const bool attend = p->out != nullptr;
+  if (attend && (!p->k || !p->v)) return invalid("k and v are required with out");
+  if (!attend && !p->out_indices && !p->out_cluster_ids) return invalid("nothing to compute");
+  const size_t need = ra_center_workspace_bytes(p->batch, p->num_heads, p->num_centers, p->top_clusters);
+  if (!p->workspace || p->workspace_bytes < need) {
+    g_last_error = "workspace smaller than ra_center_workspace_bytes()";
+    return RA_ERR_WORKSPACE;
+  }
+  const long long n_members = (long long)p->top_clusters * p->cluster_len;
+  if (attend && (long long)p->num_centers * p->cluster_len > p->num_tokens)
+    return invalid("num_centers * cluster_len exceeds num_tokens");
+  // 1) exact top-TOPC of the centroid scores (the scan kernel over the head-major table)
+  const size_t rows = (size_t)p->batch * p->num_heads;
+  char* ws = static_cast<char*>(p->workspace);
+  const size_t tail = (need - rows * p->top_clusters * 8 - 256 + 255) & ~size_t(255);
+  float* c_score = reinterpret_cast<float*>(ws + tail);
+  int* c_ids = reinterpret_cast<int*>(c_score + rows * p->top_clusters);
+  ra_params sp;
+  memset(&sp, 0, sizeof sp);
+  sp.q = p->q; sp.k = p->centers;
+  sp.batch = p->batch; sp.num_q_heads = p->num_heads; sp.num_kv_heads = p->num_heads;
+  sp.head_dim = kHeadDim; sp.num_tokens = p->num_centers;
+  sp.kv_batch_stride = 0; sp.kv_token_stride = kHeadDim;
+  sp.kv_head_stride = (int64_t)p->num_centers * kHeadDim;
+  sp.topk = p->top_clusters; sp.num_segments = 1; sp.sm_scale = 1.f;
+  sp.out_indices = p->out_cluster_ids ? p->out_cluster_ids : c_ids;
+  sp.out_scores = c_score;
+  sp.workspace = p->workspace; sp.workspace_bytes = tail; sp.stream = p->stream;
+  int st = ra_gemv_topk(&sp);
+  if (st != RA_OK) return st;
+  if (!attend && !p->out_indices) return RA_OK;
+  // 2) expansion in rank order (+ attention over every member token)
+  const long long ts = attend ? p->kv_token_stride : kHeadDim;
+  return run_gather(static_cast<const __half*>(p->q),
+                    static_cast<const __half*>(attend ? p->k : p->centers),
+                    static_cast<const __half*>(attend ? p->v : p->centers),
+                    static_cast<__half*>(p->out), nullptr, p->batch, p->num_heads, p->num_heads,
+                    attend ? p->num_tokens : 0x7fffffff, attend ? p->kv_batch_stride : 0, ts,
+                    attend ? p->kv_head_stride : 0, sp.out_indices, c_score,
+                    (long long)p->num_heads * p->top_clusters, p->top_clusters, p->top_clusters,
+                    p->cluster_len, p->out_indices, p->sm_scale > 0.f ? p->sm_scale : 1.f,
+                    static_cast<unsigned*>(p->workspace), attend,
+                    static_cast<cudaStream_t>(p->stream));
+  (void)n_members;
+}
+
 int ra_merge_attend(const ra_merge_params* p) {
   if (!p) return invalid("params is null");
   if (!p->cand_scores || !p->cand_indices) return invalid("candidate buffers are null");
@@ -458,6 +598,7 @@ int ra_merge_attend(const ra_merge_params* p) {
       p->topk < 1 || p->num_tokens < 0)
     return invalid("sizes must be positive");
   if (p->num_q_heads % p->num_kv_heads) return invalid("num_kv_heads must divide num_q_heads");
+  if (p->cand_part_stride < 0) return invalid("cand_part_stride must not be negative");
   const bool attend = p->out || p->out_partial;
   if (attend && !p->v) return invalid("v is null");
   if (!attend && !p->out_indices) return invalid("nothing to compute");
@@ -486,7 +627,8 @@ int ra_merge_attend(const ra_merge_params* p) {
   m.scale_log2e = p->sm_scale * kLog2e; m.sm_scale = p->sm_scale;
   mp.cand_score = p->cand_scores; mp.cand_idx = p->cand_indices;
   mp.part_len = p->topk;
-  mp.part_stride = (long long)p->batch * p->num_q_heads * p->topk;
+  mp.part_stride = p->cand_part_stride ? p->cand_part_stride
+                                       : (long long)p->batch * p->num_q_heads * p->topk;
   mp.row_stride = p->topk;
   mp.m_total = (int)m_total; mp.cap = pl.cap2; mp.group = p->num_q_heads / p->num_kv_heads;
   cudaError_t e = launch_merge_attend(mp, p->batch * p->num_q_heads, pl.smem2,

@@ -48,6 +48,7 @@ struct MergeArgs {
   int index_base;
   int own_lo, own_hi;  // only winners with own_lo <= id < own_hi are mixed (id before index_base)
   int id_shift;        // subtracted from an id to address V (ids of another shard's frame)
+  int select_all;      // 1: every candidate is a winner (topk == number of candidates)
   int n_tokens;        // rows of V; ids outside [0, n_tokens) after the shift are never read
   unsigned* status;    // device status word (bit kStatusBadId is set on such an id)
   int* sel_idx;        // optional
@@ -142,8 +143,12 @@ __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char*
   // radix select, most significant byte first; one cluster barrier per pass
   uint32_t mask = 0u;
   int buf = 0;
+  if (A.select_all) {
+    if (tid < kMaxLists) ms->remaining[tid] = 0;  // threshold key 0: everything is above it
+    __syncthreads();
+  }
 #pragma unroll 1
-  for (int shift = 24; shift >= 0; shift -= 8) {
+  for (int shift = A.select_all ? -1 : 24; shift >= 0; shift -= 8) {
 #pragma unroll
     for (int l = 0; l < NL; ++l) {
       const int n = min(cnt[l], cap);

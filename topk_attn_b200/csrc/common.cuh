@@ -21,7 +21,7 @@ constexpr int kTileRows = 128;         // K rows (tokens x kv heads) per pipelin
 constexpr int kStageBytes = kTileRows * kRowBytes;   // 32 KiB
 constexpr int kMaxStages = 6;
 constexpr int kMaxLists = 8;           // candidate lists (kv heads x queries) per CTA
-constexpr unsigned kSpinLimit = 1u << 22;   // bounded mbarrier wait (try_wait rounds)
+constexpr unsigned long long kWaitLimitNs = 1000000000ull;   // bounded mbarrier wait: 1 s
 
 // status word bits written by kernels that abandon a bounded wait
 constexpr unsigned kStatusTimeout = 1u;
@@ -61,22 +61,38 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
                "r"(bytes)
                : "memory");
 }
-// Bounded wait on an mbarrier phase.  Returns false when the limit ran out; the caller
-// records that in the status word and carries on so that every barrier stays matched.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity) {
-  uint32_t addr = smem_u32(bar);
-  for (unsigned it = 0; it < kSpinLimit; ++it) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(addr), "r"(parity)
-        : "memory");
-    if (ok) return true;
+__device__ __forceinline__ bool mbar_try_wait(uint32_t addr, unsigned parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(addr), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Wait on an mbarrier phase for at most kWaitLimitNs of wall time.  Returns false when the limit
+// ran out or when another thread of the CTA already gave up (*abort != 0); in both cases *abort is
+// set, the caller records that in the status word and carries on so that every barrier stays
+// matched and the kernel ends promptly.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, volatile int* abort) {
+  const uint32_t addr = smem_u32(bar);
+  if (mbar_try_wait(addr, parity)) return true;
+  const unsigned long long t0 = global_timer_ns();
+  for (;;) {
+    if (mbar_try_wait(addr, parity)) return true;
+    if (*abort) return false;
+    if (global_timer_ns() - t0 > kWaitLimitNs) {
+      *abort = 1;
+      return false;
+    }
   }
-  return false;
 }
 
 // Tiled TMA load of a 4-D box into shared memory, completion on an mbarrier.

@@ -196,10 +196,8 @@ scan_select_kernel(const __grid_constant__ ScanParams P) {
       for (int it = 0; it < my_ntiles; ++it) {
         const int jt = it / G;
         const int s = (jt % SG) * G + (it % G);
-        if (jt >= SG && !mbar_wait(&ctrl->empty[s], (unsigned)(((jt / SG) - 1) & 1))) {
-          ctrl->timeout = 1;
+        if (jt >= SG && !mbar_wait(&ctrl->empty[s], (unsigned)(((jt / SG) - 1) & 1), &ctrl->timeout))
           atomicOr(P.status, kStatusTimeout);
-        }
         const int tok = tok_begin + it * T;
         mbar_expect_tx(&ctrl->full[s], kStageBytes);
         if (P.head_major)
@@ -262,11 +260,8 @@ scan_select_kernel(const __grid_constant__ ScanParams P) {
       const int it = jt * G + grp;
       if (it < my_ntiles) {
         const int s = (jt % SG) * G + grp;
-        if (!mbar_wait(&ctrl->full[s], (unsigned)((jt / SG) & 1))) {
-          if (lane == 0) {
-            ctrl->timeout = 1;
-            atomicOr(P.status, kStatusTimeout);
-          }
+        if (!mbar_wait(&ctrl->full[s], (unsigned)((jt / SG) & 1), &ctrl->timeout)) {
+          if (lane == 0) atomicOr(P.status, kStatusTimeout);
         }
         const uint32_t base = stage0 + (uint32_t)s * kStageBytes + row_off;
         float part_sum[NQ][4];

@@ -96,15 +96,93 @@ def topk_attention(q: Tensor, k: Tensor, v: Tensor, topk: int, sm_scale: float =
     return res[0] if len(res) == 1 else res
 
 
-def gemv_topk(q: Tensor, k: Tensor, topk: int, num_segments: int = 1, index_base: int = 0
-              ) -> Tuple[Tensor, Tensor]:
-    """Selection only: (indices int32, scores fp32) [B,Hq,S*topk], unordered inside a segment."""
+def gemv_topk(q: Tensor, k: Tensor, topk: int, num_segments: int = 1, index_base: int = 0,
+              out: Optional[Tuple[Tensor, Tensor]] = None) -> Tuple[Tensor, Tensor]:
+    """Selection only: (indices int32, scores fp32) [B,Hq,S*topk], unordered inside a segment.
+    ``out`` may give the two (contiguous) destination tensors."""
     B, Hq, _ = q.shape
-    idx = torch.empty(B, Hq, num_segments * topk, dtype=torch.int32, device=q.device)
-    sc = torch.empty(B, Hq, num_segments * topk, dtype=torch.float32, device=q.device)
+    if out is not None:
+        idx, sc = out
+        if idx.dtype != torch.int32 or sc.dtype != torch.float32 or not idx.is_contiguous() \
+                or not sc.is_contiguous() or idx.shape != (B, Hq, num_segments * topk) \
+                or sc.shape != idx.shape:
+            raise ValueError("out must be contiguous (int32, fp32) [B,Hq,S*topk]")
+    else:
+        idx = torch.empty(B, Hq, num_segments * topk, dtype=torch.int32, device=q.device)
+        sc = torch.empty(B, Hq, num_segments * topk, dtype=torch.float32, device=q.device)
     p = _params(q, k, None, None, topk, 1.0, num_segments, index_base, idx, sc, None)
     capi.check(capi.lib().ra_gemv_topk(C.byref(p)))
     return idx, sc
+
+
+def gathered_attention(q: Tensor, k: Tensor, v: Tensor, indices: Tensor, sm_scale: float,
+                       out: Optional[Tensor] = None) -> Tensor:
+    """softmax(sm_scale * q.K[id]) . V[id] over ``indices`` int32 [Hq,S] (shared by the batch) or
+    [B,Hq,S].  Returns fp16 [B,Hq,128]."""
+    B, Hq, Hkv, N, bstride = _check_qkv(q, k, v)
+    if indices.dtype != torch.int32 or not indices.is_contiguous() or indices.device != q.device:
+        raise ValueError("indices must be a contiguous int32 tensor on the device of q")
+    if indices.dim() == 2:
+        ib, S = 0, indices.size(1)
+        ok = indices.size(0) == Hq
+    else:
+        ib, S = Hq * indices.size(2), indices.size(2)
+        ok = indices.shape[:2] == (B, Hq)
+    if not ok:
+        raise ValueError("indices must be [Hq,S] or [B,Hq,S]")
+    if out is None:
+        out = torch.empty_like(q)
+    p = capi.RaGatherParams()
+    p.q, p.k, p.v, p.out = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr()
+    p.batch, p.num_q_heads, p.num_kv_heads, p.head_dim, p.num_tokens = B, Hq, Hkv, 128, N
+    p.kv_batch_stride, p.kv_token_stride, p.kv_head_stride = bstride, Hkv * 128, 128
+    p.indices, p.num_indices, p.indices_batch_stride = indices.data_ptr(), S, ib
+    p.sm_scale = sm_scale
+    ws = workspace(256, q.device)
+    p.workspace, p.workspace_bytes, p.stream = ws.data_ptr(), ws.numel(), _stream_ptr()
+    capi.check(capi.lib().ra_gathered_attention(C.byref(p)))
+    return out
+
+
+def center_only_topk(q: Tensor, centers: Tensor, top_clusters: int, cluster_len: int,
+                     k: Optional[Tensor] = None, v: Optional[Tensor] = None, sm_scale: float = 1.0,
+                     return_indices: bool = True):
+    """Centroid-only retrieval.  q [B,H,128], centers [H,CSZ,128].  Returns
+    (cluster_ids int32 [B,H,TOPC] unordered, token_ids int32 [B,H,TOPC*CLEN] in descending order
+    of the centroid scores[, out fp16 [B,H,128] when k and v are given])."""
+    if q.dim() != 3 or centers.dim() != 3 or centers.size(0) != q.size(1) or centers.size(2) != 128:
+        raise ValueError("q must be [B,H,128] and centers [H,CSZ,128]")
+    for t in (q, centers):
+        if t.dtype != torch.float16 or not t.is_contiguous() or not t.is_cuda:
+            raise ValueError("q and centers must be contiguous fp16 CUDA tensors")
+    B, H, _ = q.shape
+    csz = centers.size(1)
+    dev = q.device
+    p = capi.RaCenterParams()
+    p.q, p.centers = q.data_ptr(), centers.data_ptr()
+    p.batch, p.num_heads, p.head_dim = B, H, 128
+    p.num_centers, p.cluster_len, p.top_clusters = csz, cluster_len, top_clusters
+    cids = torch.empty(B, H, top_clusters, dtype=torch.int32, device=dev)
+    p.out_cluster_ids = cids.data_ptr()
+    tids = None
+    if return_indices:
+        tids = torch.empty(B, H, top_clusters * cluster_len, dtype=torch.int32, device=dev)
+        p.out_indices = tids.data_ptr()
+    out = None
+    if k is not None:
+        _, _, Hkv, N, bstride = _check_qkv(q, k, v)
+        if Hkv != H:
+            raise ValueError("centroid retrieval needs one kv head per query head")
+        out = torch.empty_like(q)
+        p.k, p.v, p.out, p.num_tokens = k.data_ptr(), v.data_ptr(), out.data_ptr(), N
+        p.kv_batch_stride, p.kv_token_stride, p.kv_head_stride = bstride, Hkv * 128, 128
+    p.sm_scale = sm_scale
+    need = capi.lib().ra_center_workspace_bytes(B, H, csz, top_clusters)
+    ws = workspace(max(need, 256), dev)
+    p.workspace, p.workspace_bytes, p.stream = ws.data_ptr(), ws.numel(), _stream_ptr()
+    capi.check(capi.lib().ra_center_only_topk(C.byref(p)))
+    res = (cids, tids)
+    return res + (out,) if out is not None else res
 
 
 def merge_attend(cand_scores: Tensor, cand_indices: Tensor, v: Tensor, topk: int, sm_scale: float,
@@ -115,12 +193,15 @@ def merge_attend(cand_scores: Tensor, cand_indices: Tensor, v: Tensor, topk: int
     parts, B, Hq, k = cand_scores.shape
     if cand_scores.dtype != torch.float32 or cand_indices.dtype != torch.int32:
         raise ValueError("candidates must be fp32 scores and int32 ids")
-    if not (cand_scores.is_contiguous() and cand_indices.is_contiguous() and v.is_contiguous()):
-        raise ValueError("tensors must be contiguous")
+    dense = (B * Hq * k, Hq * k, k, 1)
+    st = cand_scores.stride()
+    if cand_indices.stride() != st or st[1:] != dense[1:] or not v.is_contiguous():
+        raise ValueError("candidates must be dense per part with equal strides; v contiguous")
     N, Hkv = v.size(-3), v.size(-2)
     dev = cand_scores.device
     p = capi.RaMergeParams()
     p.cand_scores, p.cand_indices, p.num_parts = cand_scores.data_ptr(), cand_indices.data_ptr(), parts
+    p.cand_part_stride = st[0]
     p.v = v.data_ptr()
     out = None
     if partial:

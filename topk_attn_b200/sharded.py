@@ -33,9 +33,9 @@ def _all_gather(out: Tensor, piece: Tensor, group=None) -> None:
 class CudaBackend:
     """The three compute steps on the local GPU through the C ABI."""
 
-    def select(self, q: Tensor, k: Tensor, topk: int, index_base: int):
+    def select(self, q: Tensor, k: Tensor, topk: int, index_base: int, out=None):
         from . import ops
-        return ops.gemv_topk(q, k, topk, index_base=index_base)
+        return ops.gemv_topk(q, k, topk, index_base=index_base, out=out)
 
     def merge_partial(self, cand_sc: Tensor, cand_idx: Tensor, v: Tensor, topk: int,
                       sm_scale: float, own_base: int) -> Tensor:
@@ -53,21 +53,29 @@ class ShardedTopkAttention:
         self.backend = backend if backend is not None else CudaBackend()
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
-        self._cand_sc = self._cand_idx = self._partials = None
+        self._recv = self._send = self._partials = None
 
     def _buffers(self, B: int, Hq: int, device):
-        shape = (self.world, B, Hq, self.topk)
-        if self._cand_sc is None or self._cand_sc.shape != shape or self._cand_sc.device != device:
-            self._cand_sc = torch.empty(shape, dtype=torch.float32, device=device)
-            self._cand_idx = torch.empty(shape, dtype=torch.int32, device=device)
+        """Scores and ids of one rank are the two halves of one int32 buffer, so that a single
+        all-gather moves both: recv [world, 2, B, Hq, k], send [2, B, Hq, k]."""
+        shape = (self.world, 2, B, Hq, self.topk)
+        if self._recv is None or self._recv.shape != shape or self._recv.device != device:
+            self._recv = torch.empty(shape, dtype=torch.int32, device=device)
+            self._send = torch.empty(shape[1:], dtype=torch.int32, device=device)
             self._partials = torch.empty(self.world, B, Hq, 130, dtype=torch.float32, device=device)
-        return self._cand_sc, self._cand_idx, self._partials
+        cand_sc = self._recv[:, 0].view(torch.float32)
+        cand_idx = self._recv[:, 1]
+        return cand_sc, cand_idx, self._partials
 
     def local_candidates(self, q: Tensor, k: Tensor, index_base: int):
         """Local top-k of this shard, padded with (-inf, -1) when the shard holds fewer than k
         tokens."""
         n = k.size(-3)
         kk = min(self.topk, n)
+        if kk == self.topk and self._send is not None and self._send.shape[1:3] == q.shape[:2]:
+            # write straight into the send halves
+            return self.backend.select(q, k, kk, index_base,
+                                       out=(self._send[1], self._send[0].view(torch.float32)))
         idx, sc = self.backend.select(q, k, kk, index_base)
         if kk < self.topk:
             pad = self.topk - kk
@@ -84,18 +92,27 @@ class ShardedTopkAttention:
             index_base = self.rank * n
         cand_sc, cand_idx, partials = self._buffers(B, Hq, q.device)
         idx, sc = self.local_candidates(q, k, index_base)
-        if self.world > 1:
-            _all_gather(cand_sc, sc, self.group)
-            _all_gather(cand_idx, idx, self.group)
-        else:
-            cand_sc[0].copy_(sc)
-            cand_idx[0].copy_(idx)
+        self.exchange_candidates(idx, sc)
         part = self.backend.merge_partial(cand_sc, cand_idx, v, self.topk, self.sm_scale, index_base)
         if self.world > 1:
             _all_gather(partials, part, self.group)
         else:
             partials[0].copy_(part)
         return self.backend.combine(partials)
+
+
+def _exchange(self, idx: Tensor, sc: Tensor) -> None:
+    """All ranks' (score, id) proposals into the receive buffer with one collective."""
+    if idx.data_ptr() != self._send[1].data_ptr():
+        self._send[1].copy_(idx)
+        self._send[0].view(torch.float32).copy_(sc)
+    if self.world > 1:
+        _all_gather(self._recv, self._send, self.group)
+    else:
+        self._recv[0].copy_(self._send)
+
+
+ShardedTopkAttention.exchange_candidates = _exchange
 
 
 def bench(args, rank: int, local: int, world: int, ClockSampler, measured_peak_gbs) -> None:
@@ -129,8 +146,7 @@ def bench(args, rank: int, local: int, world: int, ClockSampler, measured_peak_g
         sel[i][0].record()
         idx, sc = op.local_candidates(q, k, rank * n_local)
         sel[i][1].record()
-        _all_gather(cand_sc, sc)
-        _all_gather(cand_idx, idx)
+        op.exchange_candidates(idx, sc)
         part = op.backend.merge_partial(cand_sc, cand_idx, v, op.topk, op.sm_scale, rank * n_local)
         _all_gather(partials, part)
         op.backend.combine(partials)
@@ -178,7 +194,7 @@ def bench(args, rank: int, local: int, world: int, ClockSampler, measured_peak_g
             "config": {"workload": "cfg2 token-sharded", "batch": w.batch, "heads_q": q.size(1),
                        "heads_kv": k.size(-2), "head_dim": 128, "context": world * n_local,
                        "context_per_gpu": n_local, "topk": w.topk, "caches": w.bkv,
-                       "l2": "inputs_exceed_l2", "collectives": "nccl all_gather x3"},
+                       "l2": "inputs_exceed_l2", "collectives": "nccl all_gather x2"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_kind": kind + " (burst copy)",
                          "algorithmic_bytes": alg, "traffic": None,
