@@ -82,6 +82,28 @@ size_t ra_workspace_bytes(const ra_params* p);
  * topk_attn_fused_kernel (baseline_2.cu:583-1058). */
 int ra_topk_attention(const ra_params* p);
 
+/* Same decode step as ra_topk_attention for callers that have no device buffer to lend and
+ * must not allocate one: a plugin inside a server that reserved all of HBM for its own pools at
+ * start-up, code that runs after an "initialisation is over, no more cudaMalloc" point (a
+ * cudaMalloc there may also synchronise the whole device in the middle of a decode step), or a
+ * host language binding that can pass pointers it was given but cannot create new ones.
+ * It has no counterpart in the reference, whose runners cudaMalloc and cudaFree their scratch on
+ * every call.  p->workspace and p->workspace_bytes are ignored; the scratch is a fixed
+ * RA_NOALLOC_SCRATCH_BYTES array inside the library image, so every GPU that loads the library
+ * gives up that much memory until the process exits.  The call itself performs no cudaMalloc,
+ * cudaFree or other allocating call.
+ *   - Shapes whose ra_workspace_bytes() exceeds RA_NOALLOC_SCRATCH_BYTES are refused with
+ *     RA_ERR_UNSUPPORTED (ra_last_cuda_error() says so); nothing is launched.
+ *   - The first call on each device looks up the array's device address (with that device
+ *     current).  Make that first call during start-up, before any stream capture begins.
+ *   - All calls on one device share the array.  Its status block is cleared at the start of each
+ *     call, everything else is overwritten before it is read.  Two calls whose kernels may run at
+ *     the same time on one GPU (different streams, no dependency) race on it: order them.
+ *   - The device-side self-check word lives in the array too and is not reported back; callers
+ *     that want ra_check_status() use the workspace variant. */
+#define RA_NOALLOC_SCRATCH_BYTES (4u << 20)
+int ra_topk_attention_noalloc(const ra_params* p);
+
 /* Selection only: out_indices (and out_scores) must be given, out/v are ignored.  The role of
  * gemv_topk_kernel (gemv_topk.cu:173-380) with a global top-k over the N keys. */
 int ra_gemv_topk(const ra_params* p);

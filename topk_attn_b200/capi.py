@@ -111,6 +111,7 @@ def _declare(l: C.CDLL) -> None:
         "ra_workspace_bytes": (sz, [P]),
         "ra_topk_attention": (C.c_int, [P]),
         "ra_gemv_topk": (C.c_int, [P]),
+        "ra_topk_attention_noalloc": (C.c_int, [P]),
         "ra_check_status": (C.c_int, [vp, vp]),
         "ra_legacy_retrieval_attention": (C.c_int, [vp, vp, vp, vp, i32, i32, i32, i32, vp, sz, vp]),
         "ra_legacy_workspace_bytes": (sz, [i32, i32, i32]),

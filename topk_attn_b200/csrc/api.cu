@@ -436,6 +436,49 @@ int ra_topk_attention(const ra_params* p) { return run(p, true); }
 
 int ra_gemv_topk(const ra_params* p) { return run(p, false); }
 
+// ---- fused decode step for callers that cannot hand over a workspace ------------------------
+// Scratch of this entry point: a fixed array inside the library image.  The name below is only a
+// host-side handle; the address kernels may use comes from cudaGetSymbolAddress, once per device.
+static __device__ __align__(256) unsigned char g_static_scratch[RA_NOALLOC_SCRATCH_BYTES];
+
+int ra_topk_attention_noalloc(const ra_params* p) {
+  if (!p) return invalid("params is null");
+  Checked c;
+  int st = check_shape(p, c);
+  if (st != RA_OK) return st;
+  if (workspace_bound(c.shape) > (size_t)RA_NOALLOC_SCRATCH_BYTES) {
+    g_last_error = "this shape needs more scratch than the built-in RA_NOALLOC_SCRATCH_BYTES; "
+                   "use ra_topk_attention with a workspace";
+    return RA_ERR_UNSUPPORTED;
+  }
+  // set-up, once per device, with that device current
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static void* scratch_of[kMaxDevices] = {};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+  if (dev < 0 || dev >= kMaxDevices) return unsupported("device ordinal above 63");
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> g(mu);
+    if (!scratch_of[dev]) {
+      void* ptr = nullptr;
+      e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+      if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(static scratch)");
+      scratch_of[dev] = ptr;
+    }
+    scratch = scratch_of[dev];
+  }
+  // the array keeps the previous call's contents: the status block must start at zero
+  e = cudaMemsetAsync(scratch, 0, kStatusBytes, static_cast<cudaStream_t>(p->stream));
+  if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(static scratch)");
+  ra_params q = *p;
+  q.workspace = scratch;
+  q.workspace_bytes = RA_NOALLOC_SCRATCH_BYTES;
+  return run(&q, true);
+}
+
 int ra_check_status(void* workspace, void* stream) {
   if (!workspace) return RA_ERR_WORKSPACE;
   unsigned h = 0;
