@@ -178,6 +178,28 @@ int ra_center_only_topk(const ra_center_params* p);
 size_t ra_center_workspace_bytes(int32_t batch, int32_t num_heads, int32_t num_centers,
                                  int32_t top_clusters);
 
+/* Dense decode attention over the whole cache, split-KV with a log-sum-exp combine
+ * ("flash decoding"): the dense baseline of the path and the reference's
+ * baseline_attention_kernel (retrieval_attn/retrieval_attention.cu:51-168) /
+ * MHAFlashDecodeKernel (flash_decoding.cu:100-388) without the index gather. */
+typedef struct ra_dense_params {
+  const void* q;            /* fp16 [batch, num_q_heads, 128] */
+  const void* k;            /* fp16 caches, token-major */
+  const void* v;
+  void* out;                /* fp16 [batch, num_q_heads, 128] */
+  int32_t batch, num_q_heads, num_kv_heads, head_dim, num_tokens;
+  int64_t kv_batch_stride, kv_token_stride, kv_head_stride;
+  float sm_scale;
+  int32_t num_splits;       /* chunks of the token axis; 0 = chosen by the library */
+  void* workspace;          /* ra_flash_workspace_bytes() */
+  size_t workspace_bytes;
+  void* stream;
+} ra_dense_params;
+
+int ra_flash_decoding(const ra_dense_params* p);
+size_t ra_flash_workspace_bytes(int32_t batch, int32_t num_q_heads, int32_t num_kv_heads,
+                                int32_t num_tokens, int32_t num_splits);
+
 /* ---- sequence-sharded decode (no counterpart in the reference, which is single-device) ----
  * The token axis is cut over ranks.  Per step every rank (1) calls ra_gemv_topk on its shard
  * with index_base = first global token id of the shard, (2) all-gathers the [B,Hq,k] score and

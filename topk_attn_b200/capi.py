@@ -80,6 +80,19 @@ class RaCenterParams(C.Structure):
     ]
 
 
+class RaDenseParams(C.Structure):
+    """Mirror of ``struct ra_dense_params``."""
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("out", C.c_void_p),
+        ("batch", C.c_int32), ("num_q_heads", C.c_int32), ("num_kv_heads", C.c_int32),
+        ("head_dim", C.c_int32), ("num_tokens", C.c_int32),
+        ("kv_batch_stride", C.c_int64), ("kv_token_stride", C.c_int64),
+        ("kv_head_stride", C.c_int64),
+        ("sm_scale", C.c_float), ("num_splits", C.c_int32),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("stream", C.c_void_p),
+    ]
+
+
 class RaError(RuntimeError):
     def __init__(self, status: int, text: str, detail: str = ""):
         super().__init__(f"topk_attn_b200: {text} (status {status})" + (f": {detail}" if detail else ""))
@@ -117,6 +130,8 @@ def _declare(l: C.CDLL) -> None:
         "ra_legacy_workspace_bytes": (sz, [i32, i32, i32]),
         "ra_merge_attend": (C.c_int, [C.POINTER(RaMergeParams)]),
         "ra_gathered_attention": (C.c_int, [C.POINTER(RaGatherParams)]),
+        "ra_flash_decoding": (C.c_int, [C.POINTER(RaDenseParams)]),
+        "ra_flash_workspace_bytes": (sz, [i32, i32, i32, i32, i32]),
         "ra_center_only_topk": (C.c_int, [C.POINTER(RaCenterParams)]),
         "ra_center_workspace_bytes": (sz, [i32, i32, i32, i32]),
         "ra_lse_combine": (C.c_int, [vp, i32, i32, vp, vp]),

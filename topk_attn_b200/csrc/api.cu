@@ -11,6 +11,7 @@
 #include <string>
 #include <tuple>
 
+#include "flash_decode.cuh"
 #include "gather_attend.cuh"
 #include "merge_attend.cuh"
 #include "scan_select.cuh"
@@ -64,6 +65,7 @@ struct Plan {
   bool ok = false;
   int hg = 0, nq = 0, bshare = 1, nq_valid = 1;
   int cluster = 1, nsplit = 1, cap = 0, nstages = 0, per = 0, part_len = 0, grid = 0;
+  int groups = 2, rendezvous = 4;
   size_t smem = 0;
   // second stage (only when parts > 1)
   int cluster2 = 1, cap2 = 0, per2 = 0;
@@ -155,23 +157,28 @@ Plan make_plan(const Shape& s) {
         if (cluster > 1 && tiles < cluster) continue;
         const int per = ceil_div(s.topk, cluster);
         const size_t scratch = merge_scratch_bytes(nl, per);
-        // stages and list capacity within the shared-memory budget
-        int nstages = 0, cap = 0;
-        for (int st = kMaxStages; st >= 2 * kConsumerGroups; st -= kConsumerGroups) {
+        // stages, consumer groups, check interval and list capacity within the shared-memory
+        // budget: the deepest pipeline whose lists still hold k keys plus the keys that may arrive
+        // between two overflow checks
+        int nstages = 0, cap = 0, cgroups = 0, rdv = 0;
+        static const int kGeo[][2] = {{2, 6}, {2, 4}, {1, 3}, {1, 2}};
+        for (auto& ge : kGeo) {
+          const int g2 = ge[0], st = ge[1];
           if (f_stages && st != f_stages) continue;
-          if ((size_t)st * kStageBytes < scratch) break;
+          if ((size_t)st * kStageBytes < scratch) continue;
           const size_t fixed = scan_smem_bytes(nl, 0, st);
           if (fixed >= kSmemBudget) continue;
-          int c = (int)((kSmemBudget - fixed) / ((size_t)nl * 8));
-          // room for the keys that may arrive between two overflow checks
-          const int margin = kRendezvous * kConsumerGroups * T;
-          c = std::min(c, 2 * s.topk + margin);
-          const int want = (st > 4) ? (3 * s.topk) / 2 + margin : s.topk + margin + 64;
-          if (c >= std::min(want, 2 * s.topk + margin)) {
-            nstages = st;
-            cap = c;
-            break;
+          const int fit = (int)((kSmemBudget - fixed) / ((size_t)nl * 8));
+          for (int r : {4, 2, 1}) {
+            const int margin = r * g2 * T;
+            const int c = std::min(fit, 2 * s.topk + margin);
+            const int want = (st > 4) ? (3 * s.topk) / 2 + margin : s.topk + margin + 64;
+            if (c >= std::min(want, 2 * s.topk + margin)) {
+              nstages = st; cap = c; cgroups = g2; rdv = r;
+              break;
+            }
           }
+          if (nstages) break;
         }
         if (!nstages) continue;
         const size_t smem = scan_smem_bytes(nl, cap, nstages);
@@ -184,7 +191,7 @@ Plan make_plan(const Shape& s) {
         const double rate = std::min(per_sm, hbm / live);
         // every cut of a candidate list stalls the CTA's consumers for a few microseconds; the
         // seen-token count grows by (1 + room/k) between two cuts of one list
-        const int margin = kRendezvous * kConsumerGroups * T;
+        const int margin = rdv * cgroups * T;
         const double room = std::max(64, cap - s.topk - margin);
         const double slab = (double)ceil_div(tiles, cluster) * T;
         const double cuts = slab > cap ? std::log(slab / cap) / std::log1p(room / s.topk) + 1.0 : 0.0;
@@ -194,6 +201,7 @@ Plan make_plan(const Shape& s) {
         Plan pl;
         pl.hg = hg; pl.nq = nq; pl.bshare = bshare; pl.nq_valid = nq_valid;
         pl.cluster = cluster; pl.nsplit = nsplit; pl.cap = cap; pl.nstages = nstages;
+        pl.groups = cgroups; pl.rendezvous = rdv;
         pl.per = per; pl.part_len = part_len; pl.grid = nclusters * cluster; pl.smem = smem;
         pl.cost = cost;
         if (two_stage && !plan_merge(s.segments * nsplit * s.topk,
@@ -324,9 +332,10 @@ int run(const ra_params* p, bool attend) {
   if (show)
     fprintf(stderr,
             "[topk_attn_b200] plan: hg=%d nq=%d(valid %d) bshare=%d cluster=%d nsplit=%d cap=%d "
-            "stages=%d per=%d part_len=%d grid=%d smem=%zu | merge: cluster=%d cap=%d smem=%zu | "
+            "stages=%d groups=%d rdv=%d per=%d part_len=%d grid=%d smem=%zu | merge: cluster=%d cap=%d smem=%zu | "
             "model %.1f us\n",
-            pl.hg, pl.nq, pl.nq_valid, pl.bshare, pl.cluster, pl.nsplit, pl.cap, pl.nstages, pl.per,
+            pl.hg, pl.nq, pl.nq_valid, pl.bshare, pl.cluster, pl.nsplit, pl.cap, pl.nstages, pl.groups,
+            pl.rendezvous, pl.per,
             pl.part_len, pl.grid, pl.smem, pl.cluster2, pl.cap2, pl.smem2, pl.cost * 1e6);
   if (p->workspace_bytes < workspace_bound(s)) {
     g_last_error = "workspace smaller than ra_workspace_bytes()";
@@ -348,7 +357,7 @@ int run(const ra_params* p, bool attend) {
   sp.batch = s.batch; sp.hq = s.hq; sp.hkv = s.hkv; sp.n_tokens = s.n;
   sp.group = c.group; sp.bshare = pl.bshare; sp.nq_valid = pl.nq_valid;
   sp.kv_per_batch = s.per_batch;
-  sp.cap = pl.cap; sp.nstages = pl.nstages; sp.nparts = parts; sp.part_len = pl.part_len;
+  sp.cap = pl.cap; sp.nstages = pl.nstages; sp.groups = pl.groups; sp.rendezvous = pl.rendezvous; sp.nparts = parts; sp.part_len = pl.part_len;
   sp.head_major = s.head_major;
   if (const char* d = getenv("RA_DEBUG_FLAGS")) sp.debug = atoi(d);
   MergeArgs& m = sp.m;
@@ -631,6 +640,101 @@ int ra_center_only_topk(const ra_center_params* p) {
                     static_cast<unsigned*>(p->workspace), attend,
                     static_cast<cudaStream_t>(p->stream));
   (void)n_members;
+}
+
+// Effective split geometry: split_len is a multiple of the 128-token tile.
+static void flash_geometry(int batch, int hkv, int n, int asked, int& splits, int& split_len) {
+  int want = asked;
+  if (want <= 0) {
+    // about four work items per SM, never less than two tiles per item
+    want = std::max(1, ceil_div(4 * 148, batch * hkv));
+    want = std::min(want, std::max(1, n / (2 * kFdTile)));
+  }
+  want = std::max(1, std::min(want, ceil_div(n, kFdTile)));
+  split_len = ceil_div(ceil_div(n, want), kFdTile) * kFdTile;
+  splits = ceil_div(n, split_len);
+}
+
+size_t ra_flash_workspace_bytes(int32_t batch, int32_t num_q_heads, int32_t num_kv_heads,
+                                int32_t num_tokens, int32_t num_splits) {
+  if (batch < 1 || num_q_heads < 1 || num_kv_heads < 1 || num_tokens < 1) return 0;
+  int splits, split_len;
+  flash_geometry(batch, num_kv_heads, num_tokens, num_splits, splits, split_len);
+  return kStatusBytes + (size_t)splits * batch * num_q_heads * (kHeadDim + 2) * sizeof(float);
+}
+
+int ra_flash_decoding(const ra_dense_params* p) {
+  if (!p) return invalid("params is null");
+  if (!p->q || !p->k || !p->v || !p->out) return invalid("a required pointer is null");
+  if (p->head_dim != kHeadDim) return unsupported("head_dim must be 128");
+  if (p->batch < 1 || p->num_q_heads < 1 || p->num_kv_heads < 1 || p->num_tokens < 1)
+    return invalid("sizes must be positive");
+  if (p->num_q_heads % p->num_kv_heads) return invalid("num_kv_heads must divide num_q_heads");
+  const int group = p->num_q_heads / p->num_kv_heads;
+  if (group > kFdMaxGroup) return unsupported("more than 8 query heads per kv head");
+  if (!(p->sm_scale > 0.f)) return invalid("sm_scale must be positive");
+  if (p->kv_token_stride < kHeadDim || p->kv_head_stride < kHeadDim || p->kv_token_stride % 8 ||
+      p->kv_head_stride % 8 || p->kv_batch_stride % 8 || p->kv_batch_stride < 0 ||
+      p->kv_head_stride > p->kv_token_stride)
+    return invalid("kv strides must be token-major multiples of 8 elements");
+  auto mis = [](const void* x) { return (reinterpret_cast<uintptr_t>(x) & 15u) != 0; };
+  if (mis(p->q) || mis(p->k) || mis(p->v) || mis(p->out)) return invalid("pointers must be 16-byte aligned");
+  const size_t need = ra_flash_workspace_bytes(p->batch, p->num_q_heads, p->num_kv_heads,
+                                               p->num_tokens, p->num_splits);
+  if (!p->workspace || p->workspace_bytes < need || (reinterpret_cast<uintptr_t>(p->workspace) & 255u)) {
+    g_last_error = "workspace missing, misaligned or smaller than ra_flash_workspace_bytes()";
+    return RA_ERR_WORKSPACE;
+  }
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) {
+    g_last_error = "cuTensorMapEncodeTiled is not available from the driver";
+    return RA_ERR_CUDA;
+  }
+  FlashParams fp;
+  memset(&fp, 0, sizeof fp);
+  const bool per_batch = p->kv_batch_stride != 0;
+  const cuuint64_t nb = per_batch ? (cuuint64_t)p->batch : 1;
+  cuuint64_t dims[4] = {kHeadDim, (cuuint64_t)p->num_kv_heads, (cuuint64_t)p->num_tokens, nb};
+  cuuint64_t strides[3] = {(cuuint64_t)p->kv_head_stride * 2, (cuuint64_t)p->kv_token_stride * 2,
+                           per_batch ? (cuuint64_t)p->kv_batch_stride * 2
+                                     : (cuuint64_t)p->num_tokens * p->kv_token_stride * 2};
+  cuuint32_t box[4] = {64, 1, kFdTile, 1}, estr[4] = {1, 1, 1, 1};
+  for (int which = 0; which < 2; ++which) {
+    CUresult r = enc(which ? &fp.vmap : &fp.kmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                     const_cast<void*>(which ? p->v : p->k), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+      char buf[96];
+      snprintf(buf, sizeof buf, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+      g_last_error = buf;
+      return RA_ERR_CUDA;
+    }
+  }
+  int splits, split_len;
+  flash_geometry(p->batch, p->num_kv_heads, p->num_tokens, p->num_splits, splits, split_len);
+  fp.q = static_cast<const __half*>(p->q);
+  fp.partials = reinterpret_cast<float*>(static_cast<char*>(p->workspace) + kStatusBytes);
+  fp.status = static_cast<unsigned*>(p->workspace);
+  fp.batch = p->batch; fp.hq = p->num_q_heads; fp.hkv = p->num_kv_heads; fp.n_tokens = p->num_tokens;
+  fp.group = group; fp.kv_per_batch = per_batch;
+  fp.num_splits = splits; fp.split_len = split_len;
+  fp.nstages = kFdMaxStages;
+  fp.num_items = p->batch * p->num_kv_heads * splits;
+  fp.scale_log2e = p->sm_scale * kLog2e;
+  static int sms = [] {
+    int dev = 0, v = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+    return v;
+  }();
+  const int grid = std::min(fp.num_items, sms);
+  cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
+  cudaError_t e = launch_flash_decode(fp, grid, flash_decode_smem_bytes(fp.nstages), stream);
+  if (e != cudaSuccess) return cuda_fail(e, "flash_decode launch");
+  e = launch_lse_combine(fp.partials, splits, p->batch * p->num_q_heads, static_cast<__half*>(p->out),
+                         stream);
+  if (e != cudaSuccess) return cuda_fail(e, "lse_combine launch");
+  return RA_OK;
 }
 
 int ra_merge_attend(const ra_merge_params* p) {

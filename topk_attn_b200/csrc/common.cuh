@@ -10,13 +10,13 @@ namespace ra {
 
 constexpr int kHeadDim = 128;          // the reference's only head size
 constexpr int kRowBytes = kHeadDim * 2;
-constexpr int kConsumerGroups = 2;     // warp groups of the scan kernel, each on its own tile
+constexpr int kConsumerGroups = 2;     // most warp groups of the scan kernel (each on its own tile)
 constexpr int kConsumerWarps = 8 * kConsumerGroups;
 constexpr int kConsumerThreads = 32 * kConsumerWarps;
 constexpr int kThreads = kConsumerThreads + 32;   // + one TMA producer warp
 constexpr int kMergeThreads = 256;     // threads per CTA of the candidate-merge kernel
 constexpr int kMaxWarps = 32;
-constexpr int kRendezvous = 4;         // scan iterations between list-overflow checks
+constexpr int kRendezvous = 4;         // most scan iterations between list-overflow checks
 constexpr int kTileRows = 128;         // K rows (tokens x kv heads) per pipeline stage
 constexpr int kStageBytes = kTileRows * kRowBytes;   // 32 KiB
 constexpr int kMaxStages = 6;

@@ -36,14 +36,14 @@ struct Ctrl {
 };
 
 // Barrier among the consumer warps only (the producer warp never joins it).
-__device__ __forceinline__ void consumer_sync() {
-  asm volatile("bar.sync 1, %0;" ::"r"(kConsumerThreads) : "memory");
+__device__ __forceinline__ void consumer_sync(int nct) {
+  asm volatile("bar.sync 1, %0;" ::"r"(nct) : "memory");
 }
 
 // Raise the threshold of list `l` to its exact k-th largest key and keep only the k best.
 // Called by all consumer threads.
 __device__ void compact_list(uint32_t* keys, int* idxs, Ctrl* ctrl, int l, int k, int cap,
-                             int tid) {
+                             int tid, int nct) {
   const int n = min(ctrl->cnt[l], cap);
   const int lane = tid & 31;
   uint32_t prefix = 0, mask = 0;
@@ -51,12 +51,12 @@ __device__ void compact_list(uint32_t* keys, int* idxs, Ctrl* ctrl, int l, int k
 #pragma unroll 1
   for (int shift = 24; shift >= 0; shift -= 8) {
     if (tid < 256) ctrl->hist[tid] = 0;
-    consumer_sync();
-    for (int i = tid; i < n; i += kConsumerThreads) {
+    consumer_sync(nct);
+    for (int i = tid; i < n; i += nct) {
       const uint32_t key = keys[i];
       if ((key & mask) == prefix) atomicAdd(&ctrl->hist[(key >> shift) & 255], 1);
     }
-    consumer_sync();
+    consumer_sync(nct);
     if (tid < 32) {
       int d, nr;
       warp_find_digit(ctrl->hist, remaining, lane, d, nr);
@@ -65,7 +65,7 @@ __device__ void compact_list(uint32_t* keys, int* idxs, Ctrl* ctrl, int l, int k
         ctrl->remaining = nr;
       }
     }
-    consumer_sync();
+    consumer_sync(nct);
     prefix |= (uint32_t)ctrl->digit << shift;
     mask |= 255u << shift;
     remaining = ctrl->remaining;
@@ -76,22 +76,22 @@ __device__ void compact_list(uint32_t* keys, int* idxs, Ctrl* ctrl, int l, int k
     ctrl->wpos = 0;
     ctrl->eqc = 0;
   }
-  consumer_sync();
+  consumer_sync(nct);
   constexpr int E = 4;
 #pragma unroll 1
-  for (int base = 0; base < n; base += kConsumerThreads * E) {
+  for (int base = 0; base < n; base += nct * E) {
     uint32_t kk[E];
     int ii[E];
 #pragma unroll
     for (int e = 0; e < E; ++e) {
-      const int i = base + e * kConsumerThreads + tid;
+      const int i = base + e * nct + tid;
       kk[e] = (i < n) ? keys[i] : 0u;
       ii[e] = (i < n) ? idxs[i] : 0;
     }
-    consumer_sync();
+    consumer_sync(nct);
 #pragma unroll
     for (int e = 0; e < E; ++e) {
-      const int i = base + e * kConsumerThreads + tid;
+      const int i = base + e * nct + tid;
       if (i < n) {
         bool keep = kk[e] > kth;
         if (!keep && kk[e] == kth) keep = atomicAdd(&ctrl->eqc, 1) < need_eq;
@@ -102,13 +102,13 @@ __device__ void compact_list(uint32_t* keys, int* idxs, Ctrl* ctrl, int l, int k
         }
       }
     }
-    consumer_sync();
+    consumer_sync(nct);
   }
   if (tid == 0) {
     ctrl->cnt[l] = ctrl->wpos;
     ctrl->thr[l] = kth;
   }
-  consumer_sync();
+  consumer_sync(nct);
 }
 
 // acc0 += k.lo * q.lo, acc1 += k.hi * q.hi for one packed pair of fp16 values; products of
@@ -137,8 +137,9 @@ scan_select_kernel(const __grid_constant__ ScanParams P) {
   static_assert(NL <= kMaxLists, "too many candidate lists per CTA");
   constexpr int T = kTileRows / HG;     // tokens per tile
   constexpr int NV = (NQ + 1) / 2;      // scores a lane keeps per tile
-  constexpr int G = kConsumerGroups;    // warp groups working on different tiles
-  constexpr int R = kRendezvous;        // iterations between overflow checks
+  const int G = P.groups;      // consumer warp groups (1 or 2), each on its own tile
+  const int R = P.rendezvous;  // iterations between overflow checks
+  const int nct = 256 * G;     // consumer threads
   extern __shared__ __align__(128) unsigned char smem_raw[];
   unsigned char* smem =
       reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
@@ -187,7 +188,7 @@ scan_select_kernel(const __grid_constant__ ScanParams P) {
   }
   __syncthreads();
 
-  if (warp == kConsumerWarps) {
+  if (warp == 8 * G) {
     // ------------------------------------------------------------ producer warp
     if (lane == 0) {
       // Every consumer group has its own ring of S/G stages, so a warp waits on every phase of
@@ -351,17 +352,17 @@ scan_select_kernel(const __grid_constant__ ScanParams P) {
       // meeting is cut back to its k best.  The counters are settled between the two barriers,
       // so every thread takes the same decision.
       if ((jt + 1) % R == 0) {
-        consumer_sync();
+        consumer_sync(nct);
         int need = 0;
 #pragma unroll
         for (int l = 0; l < NL; ++l)
           if (ctrl->cnt[l] > cap - R * G * T) need |= 1 << l;
-        consumer_sync();
+        consumer_sync(nct);
         if (need) {
 #pragma unroll
           for (int l = 0; l < NL; ++l)
             if ((need >> l) & 1)
-              compact_list(keys + (size_t)l * cap, idxs + (size_t)l * cap, ctrl, l, k, cap, tid);
+              compact_list(keys + (size_t)l * cap, idxs + (size_t)l * cap, ctrl, l, k, cap, tid, nct);
 #pragma unroll
           for (int v = 0; v < NV; ++v) my_thr[v] = ctrl->thr[my_list[v]];
         }
@@ -403,7 +404,7 @@ static cudaError_t launch_one(const ScanParams& P, int grid, size_t smem, cudaSt
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid, 1, 1);
-  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.blockDim = dim3(32 * (8 * P.groups + 1), 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];

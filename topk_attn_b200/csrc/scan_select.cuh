@@ -15,7 +15,9 @@ struct ScanParams {
   int nq_valid;              // bshare * group, queries scored per K row (<= NQ)
   int kv_per_batch;          // 1: every batch row has its own cache
   int cap;                   // capacity of a candidate list (>= topk + 2 tiles)
-  int nstages;               // TMA pipeline depth
+  int nstages;               // TMA pipeline depth (a multiple of groups)
+  int groups;                // consumer warp groups: 1 or 2
+  int rendezvous;            // scan iterations between list-overflow checks
   int nparts;                // parts (segments x splits) per (batch row, head)
   int part_len;              // tokens per part
   int head_major;            // 1: table is [H, N, 128] (centroids); one head per CTA

@@ -115,6 +115,24 @@ def gemv_topk(q: Tensor, k: Tensor, topk: int, num_segments: int = 1, index_base
     return idx, sc
 
 
+def flash_decoding(q: Tensor, k: Tensor, v: Tensor, sm_scale: float, num_splits: int = 0,
+                   out: Optional[Tensor] = None) -> Tensor:
+    """Dense decode attention over the whole cache (split-KV + log-sum-exp combine)."""
+    B, Hq, Hkv, N, bstride = _check_qkv(q, k, v)
+    if out is None:
+        out = torch.empty_like(q)
+    p = capi.RaDenseParams()
+    p.q, p.k, p.v, p.out = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr()
+    p.batch, p.num_q_heads, p.num_kv_heads, p.head_dim, p.num_tokens = B, Hq, Hkv, 128, N
+    p.kv_batch_stride, p.kv_token_stride, p.kv_head_stride = bstride, Hkv * 128, 128
+    p.sm_scale, p.num_splits = sm_scale, num_splits
+    need = capi.lib().ra_flash_workspace_bytes(B, Hq, Hkv, N, num_splits)
+    ws = workspace(max(need, 256), q.device)
+    p.workspace, p.workspace_bytes, p.stream = ws.data_ptr(), ws.numel(), _stream_ptr()
+    capi.check(capi.lib().ra_flash_decoding(C.byref(p)))
+    return out
+
+
 def gathered_attention(q: Tensor, k: Tensor, v: Tensor, indices: Tensor, sm_scale: float,
                        out: Optional[Tensor] = None) -> Tensor:
     """softmax(sm_scale * q.K[id]) . V[id] over ``indices`` int32 [Hq,S] (shared by the batch) or
