@@ -1,0 +1,100 @@
+"""CPU checks of the boundary: the C-ABI library loads without a GPU, exports every function the
+header declares, the ctypes mirrors match the header's structs field by field, and argument
+validation that needs no device works."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "topk_attn_b200.h")
+
+
+def header_text():
+    return open(HEADER).read()
+
+
+def declared_functions():
+    txt = re.sub(r"/\*.*?\*/", "", header_text(), flags=re.S)
+    return sorted(set(re.findall(r"\b(ra_[a-z_0-9]+)\s*\(", txt)))
+
+
+def test_library_exports_every_declared_symbol():
+    from topk_attn_b200 import capi
+    lib = capi.lib()
+    names = declared_functions()
+    assert len(names) >= 15
+    for n in names:
+        assert hasattr(lib, n), f"{n} is declared in the header but not exported"
+
+
+def struct_fields(name):
+    txt = re.sub(r"/\*.*?\*/", "", header_text(), flags=re.S)
+    body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (name, name), txt, flags=re.S).group(1)
+    fields = []
+    for decl in body.split(";"):
+        decl = decl.strip()
+        if not decl:
+            continue
+        names = [x.strip().lstrip("*").strip() for x in decl.split(",")]
+        first = names[0].split()[-1].lstrip("*")
+        fields.append(first)
+        fields.extend(names[1:])
+    return fields
+
+
+@pytest.mark.parametrize("cname,pyname", [
+    ("ra_params", "RaParams"), ("ra_merge_params", "RaMergeParams"),
+    ("ra_gather_params", "RaGatherParams"), ("ra_center_params", "RaCenterParams"),
+    ("ra_dense_params", "RaDenseParams"),
+])
+def test_ctypes_mirrors_match_header(cname, pyname):
+    from topk_attn_b200 import capi
+    py = [f[0] for f in getattr(capi, pyname)._fields_]
+    assert py == struct_fields(cname)
+
+
+def test_strerror_and_version():
+    from topk_attn_b200 import capi
+    lib = capi.lib()
+    assert lib.ra_version() >= 100
+    assert lib.ra_strerror(0) == b"ok"
+    for code in range(1, 8):
+        assert lib.ra_strerror(code) not in (b"ok", b"unknown status")
+
+
+def test_shape_validation_without_a_device():
+    from topk_attn_b200 import capi
+    lib = capi.lib()
+    p = capi.RaParams()
+    assert lib.ra_workspace_bytes(C.byref(p)) == 0           # empty shape
+    p.batch, p.num_q_heads, p.num_kv_heads, p.head_dim, p.num_tokens = 4, 32, 32, 128, 131072
+    p.kv_token_stride, p.kv_head_stride, p.topk, p.num_segments, p.sm_scale = 4096, 128, 2048, 1, 1.0
+    need = lib.ra_workspace_bytes(C.byref(p))
+    assert need >= 256 + 4 * 32 * 2048 * 8
+    p.head_dim = 64
+    assert lib.ra_workspace_bytes(C.byref(p)) == 0
+    assert lib.ra_topk_attention(C.byref(p)) == capi.RA_ERR_UNSUPPORTED
+    p.head_dim, p.topk = 128, 0
+    assert lib.ra_topk_attention(C.byref(p)) == capi.RA_ERR_INVALID_ARGUMENT
+    assert lib.ra_legacy_workspace_bytes(4, 8192, 128) > 0
+    assert lib.ra_flash_workspace_bytes(8, 32, 8, 32768, 64) == 256 + 64 * 8 * 32 * 130 * 4
+    assert lib.ra_center_workspace_bytes(1, 32, 2048, 64) > 0
+
+
+def test_missing_library_fails_loudly(monkeypatch):
+    from topk_attn_b200 import capi
+    monkeypatch.setattr(capi, "_lib", None)
+    monkeypatch.setattr(capi, "LIB_PATH", "/nonexistent/libtopk_attn_b200.so")
+    with pytest.raises(ImportError):
+        capi.lib()
+
+
+def test_extension_module_is_built_with_the_reference_names():
+    import topk_attn_b200
+    mod = topk_attn_b200.load_extension()
+    names = [f"retrieval_attention{v}_{k}" for v in
+             ("", "_global", "_pipelined", "_pipelined_global", "_two_kernels", "_gather_baseline")
+             for k in (32, 128, 256, 512, 1024)]
+    assert all(hasattr(mod, n) for n in names)

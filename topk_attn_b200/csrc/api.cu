@@ -142,6 +142,8 @@ Plan make_plan(const Shape& s) {
     if (s.hkv % hg || !combo_built(hg, nq)) continue;
     if (s.head_major && hg != 1) continue;
     if (f_hg && hg != f_hg) continue;
+    // several queries per K row are scored on the tensor cores, one kv head per CTA
+    if (nq > 1 && hg != 1 && !getenv("RA_NO_MMA")) continue;
     const int nl = hg * nq, T = kTileRows / hg;
     const int groups = (s.batch / bshare) * (s.hkv / hg) * s.segments;
     for (int cluster : {1, 2, 4, 8, 16}) {
@@ -277,7 +279,7 @@ size_t workspace_bound(const Shape& s) {
   return (w + 255) & ~size_t(255);
 }
 
-int encode_kmap(CUtensorMap* map, const ra_params* p, const Shape& s, int hg) {
+int encode_kmap(CUtensorMap* map, const ra_params* p, const Shape& s, int hg, bool swizzled) {
   EncodeTiledFn enc = encode_fn();
   if (!enc) {
     g_last_error = "cuTensorMapEncodeTiled is not available from the driver";
@@ -301,8 +303,10 @@ int encode_kmap(CUtensorMap* map, const ra_params* p, const Shape& s, int hg) {
     box[0] = kHeadDim; box[1] = hg; box[2] = T; box[3] = 1;
   }
   strides[2] = bstride;
+  if (swizzled) box[0] = 64;
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(p->k), dims, strides,
-                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   swizzled ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     char buf[96];
@@ -350,7 +354,10 @@ int run(const ra_params* p, bool attend) {
 
   ScanParams sp;
   memset(&sp, 0, sizeof sp);
-  st = encode_kmap(&sp.kmap, p, s, pl.hg);
+  // several queries per K row (GQA group, batch rows on one cache): score on the tensor cores
+  const bool swizzled = pl.hg == 1 && pl.nq > 1 && !getenv("RA_NO_MMA");
+  st = encode_kmap(&sp.kmap, p, s, pl.hg, swizzled);
+  sp.swizzled = swizzled;
   if (st != RA_OK) return st;
   sp.q = static_cast<const __half*>(p->q);
   sp.status = status;

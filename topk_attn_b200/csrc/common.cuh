@@ -124,6 +124,31 @@ __device__ __forceinline__ uint4 ldg128_nc(const void* p) {
                : "l"(p));
   return r;
 }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+// d += a(16x16, row) * b(16x8, col), fp16 inputs, fp32 accumulate
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
+                                          uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// A 128-token x 128-dim fp16 tile loaded by TMA as two [128 tokens][64 dims] halves of 16 KiB with
+// the 128-byte swizzle: byte offset of (token row, 16-byte chunk c8 in 0..15 of the 256-byte row).
+constexpr int kSwzHalfBytes = 128 * 128;
+__device__ __forceinline__ uint32_t swz128(int token, int c8) {
+  return (uint32_t)((c8 >> 3) * kSwzHalfBytes + token * 128 + (((c8 & 7) ^ (token & 7)) << 4));
+}
 __device__ __forceinline__ float2 h2f2(uint32_t u) {
   __half2 h = *reinterpret_cast<__half2*>(&u);
   return __half22float2(h);

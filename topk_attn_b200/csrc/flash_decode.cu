@@ -27,34 +27,11 @@ struct FdCtrl {
 __device__ __forceinline__ void fd_consumer_sync() {
   asm volatile("bar.sync 1, %0;" ::"r"(32 * kFdConsumerWarps) : "memory");
 }
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-               : "r"(addr));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-               : "r"(addr));
-}
-// d += a(16x16, row) * b(16x8, col), fp16 inputs, fp32 accumulate
-__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
-                                          uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-      "{%0,%1,%2,%3};"
-      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
   __half2 h = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&h);
 }
-// byte offset of (token row, 16-byte chunk c8 in 0..15 of the 256-byte row) inside one stage
-// half pair: rows are 128 bytes, chunk index xor-ed with the row (TMA 128-byte swizzle)
-__device__ __forceinline__ uint32_t fd_swz(int token, int c8) {
-  return (uint32_t)((c8 >> 3) * kFdHalfBytes + token * 128 + (((c8 & 7) ^ (token & 7)) << 4));
-}
+__device__ __forceinline__ uint32_t fd_swz(int token, int c8) { return swz128(token, c8); }
 
 __global__ void __launch_bounds__(kFdThreads, 1)
 flash_decode_kernel(const __grid_constant__ FlashParams P) {

@@ -130,11 +130,13 @@ __device__ __forceinline__ void fma_pair(float& acc0, float& acc1, uint32_t kw, 
   }
 }
 
-template <int HG, int NQ, bool MIXED>
+template <int HG, int NQ, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 scan_select_kernel(const __grid_constant__ ScanParams P) {
   constexpr int NL = HG * NQ;
+  constexpr bool MIXED = (MODE == 1);
   static_assert(NL <= kMaxLists, "too many candidate lists per CTA");
+  static_assert(MODE != 2 || HG == 1, "tensor-core scoring takes one kv head per CTA");
   constexpr int T = kTileRows / HG;     // tokens per tile
   constexpr int NV = (NQ + 1) / 2;      // scores a lane keeps per tile
   const int G = P.groups;      // consumer warp groups (1 or 2), each on its own tile
@@ -200,11 +202,23 @@ scan_select_kernel(const __grid_constant__ ScanParams P) {
         if (jt >= SG && !mbar_wait(&ctrl->empty[s], (unsigned)(((jt / SG) - 1) & 1), &ctrl->timeout))
           atomicOr(P.status, kStatusTimeout);
         const int tok = tok_begin + it * T;
+        unsigned char* dst = stages + (size_t)s * kStageBytes;
         mbar_expect_tx(&ctrl->full[s], kStageBytes);
-        if (P.head_major)
-          tma_load_4d(stages + (size_t)s * kStageBytes, &P.kmap, &ctrl->full[s], 0, tok, h0, kv_b);
-        else
-          tma_load_4d(stages + (size_t)s * kStageBytes, &P.kmap, &ctrl->full[s], 0, h0, tok, kv_b);
+        if constexpr (MODE == 2) {
+          // two 64-dim halves with the 128-byte swizzle (operands of ldmatrix)
+          if (P.head_major) {
+            tma_load_4d(dst, &P.kmap, &ctrl->full[s], 0, tok, h0, kv_b);
+            tma_load_4d(dst + kSwzHalfBytes, &P.kmap, &ctrl->full[s], 64, tok, h0, kv_b);
+          } else {
+            tma_load_4d(dst, &P.kmap, &ctrl->full[s], 0, h0, tok, kv_b);
+            tma_load_4d(dst + kSwzHalfBytes, &P.kmap, &ctrl->full[s], 64, h0, tok, kv_b);
+          }
+        } else {
+          if (P.head_major)
+            tma_load_4d(dst, &P.kmap, &ctrl->full[s], 0, tok, h0, kv_b);
+          else
+            tma_load_4d(dst, &P.kmap, &ctrl->full[s], 0, h0, tok, kv_b);
+        }
       }
     }
   } else {
@@ -253,6 +267,31 @@ scan_select_kernel(const __grid_constant__ ScanParams P) {
 
     const uint32_t stage0 = smem_u32(stages);
     const uint32_t row_off = (uint32_t)(((tw * 16 + r) * HG + hh) * kRowBytes + j * 16);
+
+    // Tensor-core scoring (MODE 2): the queries that share a K row (GQA group and/or batch rows
+    // on one cache, <= 8) are the N dimension of an m16n8k16 product whose M dimension is this
+    // warp's 16 tokens.  Lane (g, t) holds B fragments of query g and ends up with the scores
+    // of tokens g, g+8 for queries 2t, 2t+1.
+    const int mg = lane >> 2, mt = lane & 3;
+    uint32_t qb[8][2];
+    uint32_t thr2[2] = {0u, 0u};
+    const int a_tok = w8 * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+    const int a_c8 = lane >> 4;
+    if constexpr (MODE == 2) {
+      if (mg < P.nq_valid) {
+        const int bq = b0 + mg / P.group;
+        const int hq = h0 * P.group + mg % P.group;
+        const __half* qp = P.q + ((size_t)bq * P.hq + hq) * kHeadDim;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          qb[kk][0] = *reinterpret_cast<const uint32_t*>(qp + 16 * kk + 2 * mt);
+          qb[kk][1] = *reinterpret_cast<const uint32_t*>(qp + 16 * kk + 8 + 2 * mt);
+        }
+      } else {
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) qb[kk][0] = qb[kk][1] = 0u;
+      }
+    }
     const int iters = ceil_div(my_ntiles, G);
     const int SG = S / G;  // stages in this group's ring
 
@@ -264,6 +303,46 @@ scan_select_kernel(const __grid_constant__ ScanParams P) {
         if (!mbar_wait(&ctrl->full[s], (unsigned)((jt / SG) & 1), &ctrl->timeout)) {
           if (lane == 0) atomicOr(P.status, kStatusTimeout);
         }
+        if constexpr (MODE == 2) {
+          const uint32_t tbase = stage0 + (uint32_t)s * kStageBytes;
+          float c[4] = {0.f, 0.f, 0.f, 0.f};
+          if (!(P.debug & 1)) {
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk) {
+              uint32_t a[4];
+              ldmatrix_x4(a, tbase + swz128(a_tok, 2 * kk + a_c8));
+              mma_16816(c, a, qb[kk][0], qb[kk][1]);
+            }
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&ctrl->empty[s]);
+          const int tok_lo = tok_begin + it * T + w8 * 16 + mg;
+          const unsigned tmask = 0x11111111u << mt;  // the lanes that share my two queries
+#pragma unroll
+          for (int jv = 0; jv < 4; ++jv) {
+            const int qi = 2 * mt + (jv & 1);
+            const int tok = tok_lo + 8 * (jv >> 1);
+            const uint32_t key = score_key(c[jv]);
+            const bool pass = qi < P.nq_valid && tok < part_hi && key > thr2[jv & 1];
+            const unsigned bal = __ballot_sync(0xffffffffu, pass);
+            if (bal) {
+              const unsigned mym = bal & tmask;
+              const int leader = mym ? (__ffs(mym) - 1) : 0;
+              int basepos = 0;
+              if (pass && lane == leader) basepos = atomicAdd(&ctrl->cnt[qi], __popc(mym));
+              basepos = __shfl_sync(0xffffffffu, basepos, leader);
+              if (pass) {
+                const int pos = basepos + __popc(mym & lt_mask);
+                if (pos < cap) {
+                  keys[(size_t)qi * cap + pos] = key;
+                  idxs[(size_t)qi * cap + pos] = tok;
+                } else {
+                  atomicOr(P.status, kStatusOverflow);
+                }
+              }
+            }
+          }
+        } else {
         const uint32_t base = stage0 + (uint32_t)s * kStageBytes + row_off;
         float part_sum[NQ][4];
         if (!(P.debug & 1)) {
@@ -347,6 +426,7 @@ scan_select_kernel(const __grid_constant__ ScanParams P) {
             }
           }
         }
+        }  // scoring on the CUDA cores
       }
       // Every R iterations all consumer warps meet; a list that could overflow before the next
       // meeting is cut back to its k best.  The counters are settled between the two barriers,
@@ -365,6 +445,10 @@ scan_select_kernel(const __grid_constant__ ScanParams P) {
               compact_list(keys + (size_t)l * cap, idxs + (size_t)l * cap, ctrl, l, k, cap, tid, nct);
 #pragma unroll
           for (int v = 0; v < NV; ++v) my_thr[v] = ctrl->thr[my_list[v]];
+          if constexpr (MODE == 2) {
+            thr2[0] = ctrl->thr[min(2 * mt, NL - 1)];
+            thr2[1] = ctrl->thr[min(2 * mt + 1, NL - 1)];
+          }
         }
       }
     }
@@ -395,7 +479,11 @@ size_t merge_scratch_bytes(int nl, int per) { return sizeof(MergeScratch) + (siz
 // ---------------------------------------------------------------------------- launcher
 template <int HG, int NQ>
 static cudaError_t launch_one(const ScanParams& P, int grid, size_t smem, cudaStream_t stream) {
-  auto kern = (P.debug & 2) ? scan_select_kernel<HG, NQ, false> : scan_select_kernel<HG, NQ, true>;
+  auto kern = scan_select_kernel<HG, NQ, 1>;
+  if (P.debug & 2) kern = scan_select_kernel<HG, NQ, 0>;
+  if constexpr (HG == 1 && NQ > 1) {
+    if (P.swizzled) kern = scan_select_kernel<1, NQ, 2>;
+  }
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   if (P.m.cluster > 8) {
@@ -435,7 +523,7 @@ namespace ra {
 
 template <int HG, int NQ>
 static int max_clusters_one(int cluster, size_t smem) {
-  auto kern = scan_select_kernel<HG, NQ, true>;
+  auto kern = scan_select_kernel<HG, NQ, 1>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
     (void)cudaGetLastError();
     return 0;

@@ -21,6 +21,7 @@ struct ScanParams {
   int nparts;                // parts (segments x splits) per (batch row, head)
   int part_len;              // tokens per part
   int head_major;            // 1: table is [H, N, 128] (centroids); one head per CTA
+  int swizzled;              // 1: tiles are two 64-dim halves with the 128-byte swizzle (tensor-core scoring)
   int debug;                 // tuning aid: bit 0 = stream the tiles but skip the scoring
 };
 

@@ -164,7 +164,7 @@ def gathered_attention(q: Tensor, k: Tensor, v: Tensor, indices: Tensor, sm_scal
 
 def center_only_topk(q: Tensor, centers: Tensor, top_clusters: int, cluster_len: int,
                      k: Optional[Tensor] = None, v: Optional[Tensor] = None, sm_scale: float = 1.0,
-                     return_indices: bool = True):
+                     return_indices: bool = True, out: Optional[Tensor] = None):
     """Centroid-only retrieval.  q [B,H,128], centers [H,CSZ,128].  Returns
     (cluster_ids int32 [B,H,TOPC] unordered, token_ids int32 [B,H,TOPC*CLEN] in descending order
     of the centroid scores[, out fp16 [B,H,128] when k and v are given])."""
@@ -183,15 +183,17 @@ def center_only_topk(q: Tensor, centers: Tensor, top_clusters: int, cluster_len:
     cids = torch.empty(B, H, top_clusters, dtype=torch.int32, device=dev)
     p.out_cluster_ids = cids.data_ptr()
     tids = None
+    out_given = out
     if return_indices:
         tids = torch.empty(B, H, top_clusters * cluster_len, dtype=torch.int32, device=dev)
         p.out_indices = tids.data_ptr()
-    out = None
+    out = out_given if k is not None else None
     if k is not None:
         _, _, Hkv, N, bstride = _check_qkv(q, k, v)
         if Hkv != H:
             raise ValueError("centroid retrieval needs one kv head per query head")
-        out = torch.empty_like(q)
+        if out is None:
+            out = torch.empty_like(q)
         p.k, p.v, p.out, p.num_tokens = k.data_ptr(), v.data_ptr(), out.data_ptr(), N
         p.kv_batch_stride, p.kv_token_stride, p.kv_head_stride = bstride, Hkv * 128, 128
     p.sm_scale = sm_scale
