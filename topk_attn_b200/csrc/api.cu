@@ -63,7 +63,7 @@ constexpr int kMaxSplit = 16;  // parts one head's context may be cut into
 
 struct Plan {
   bool ok = false;
-  int hg = 0, nq = 0, bshare = 1, nq_valid = 1;
+  int hg = 0, nq = 0, bshare = 1, nq_valid = 1, qsplit = 1, nq_cta = 1;
   int cluster = 1, nsplit = 1, cap = 0, nstages = 0, per = 0, part_len = 0, grid = 0;
   int groups = 2, rendezvous = 4;
   size_t smem = 0;
@@ -135,17 +135,23 @@ Plan make_plan(const Shape& s) {
       if (s.batch % b == 0 && b * group <= 8) bshare = b;
   }
   const int nq_valid = bshare * group;
-  const int nq = next_pow2(nq_valid);
   const int seg_len = s.n / s.segments;
   const double hbm = 6.5e12, per_sm = 75e9;
+  int f_qsplit = 0;
+  if (const char* f = getenv("RA_FORCE_QSPLIT")) f_qsplit = atoi(f);
+  for (int qsplit : {1, 2, 4, 8})
   for (int hg : {8, 4, 2, 1}) {
+    if (nq_valid % qsplit || (f_qsplit && qsplit != f_qsplit)) continue;
+    const int nq_cta = nq_valid / qsplit;
+    const int nq = next_pow2(nq_cta);
+    if (qsplit > 1 && hg != 1) continue;
     if (s.hkv % hg || !combo_built(hg, nq)) continue;
     if (s.head_major && hg != 1) continue;
     if (f_hg && hg != f_hg) continue;
     // several queries per K row are scored on the tensor cores, one kv head per CTA
     if (nq > 1 && hg != 1 && !getenv("RA_NO_MMA")) continue;
     const int nl = hg * nq, T = kTileRows / hg;
-    const int groups = (s.batch / bshare) * (s.hkv / hg) * s.segments;
+    const int groups = (s.batch / bshare) * (s.hkv / hg) * s.segments * qsplit;
     for (int cluster : {1, 2, 4, 8, 16}) {
       if (f_cluster && cluster != f_cluster) continue;
       for (int nsplit = 1; nsplit <= kMaxSplit; ++nsplit) {
@@ -163,8 +169,13 @@ Plan make_plan(const Shape& s) {
         // budget: the deepest pipeline whose lists still hold k keys plus the keys that may arrive
         // between two overflow checks
         int nstages = 0, cap = 0, cgroups = 0, rdv = 0;
-        static const int kGeo[][2] = {{2, 6}, {2, 4}, {1, 3}, {1, 2}};
-        for (auto& ge : kGeo) {
+        // one query per K row: scoring is latency-bound, two warp groups and deep rings help;
+        // several queries per row (tensor-core scoring): one group and roomier lists win
+        static const int kGeo1[4][2] = {{2, 6}, {2, 4}, {1, 3}, {1, 2}};
+        static const int kGeoN[4][2] = {{2, 4}, {1, 3}, {1, 2}, {1, 2}};
+        const int (*kGeo)[2] = (nq > 1) ? kGeoN : kGeo1;
+        for (int gi = 0; gi < 4; ++gi) {
+          const int* ge = kGeo[gi];
           const int g2 = ge[0], st = ge[1];
           if (f_stages && st != f_stages) continue;
           if ((size_t)st * kStageBytes < scratch) continue;
@@ -190,7 +201,8 @@ Plan make_plan(const Shape& s) {
         const int waves = ceil_div(nclusters, active);
         const int live = std::min(nclusters, active) * cluster;
         const double bytes_cta = (double)ceil_div(tiles, cluster) * kStageBytes;
-        const double rate = std::min(per_sm, hbm / live);
+        // clusters that share a K row stream it once from HBM and qsplit - 1 times from L2
+        const double rate = std::min(per_sm, hbm * qsplit / live);
         // every cut of a candidate list stalls the CTA's consumers for a few microseconds; the
         // seen-token count grows by (1 + room/k) between two cuts of one list
         const int margin = rdv * cgroups * T;
@@ -198,10 +210,11 @@ Plan make_plan(const Shape& s) {
         const double slab = (double)ceil_div(tiles, cluster) * T;
         const double cuts = slab > cap ? std::log(slab / cap) / std::log1p(room / s.topk) + 1.0 : 0.0;
         const bool two_stage = nsplit > 1 || s.segments > 1 || !s.fused_ok;
-        double cost = waves * (bytes_cta / rate + cuts * nl * 4e-6 + 6e-6 + 1.5e-6 * cluster) +
+        double cost = waves * (bytes_cta / rate + cuts * nl * 2e-6 + 6e-6 + 1.5e-6 * cluster) +
                       (two_stage ? 8e-6 : 0.0);
         Plan pl;
         pl.hg = hg; pl.nq = nq; pl.bshare = bshare; pl.nq_valid = nq_valid;
+        pl.qsplit = qsplit; pl.nq_cta = nq_cta;
         pl.cluster = cluster; pl.nsplit = nsplit; pl.cap = cap; pl.nstages = nstages;
         pl.groups = cgroups; pl.rendezvous = rdv;
         pl.per = per; pl.part_len = part_len; pl.grid = nclusters * cluster; pl.smem = smem;
@@ -335,10 +348,10 @@ int run(const ra_params* p, bool attend) {
   if (show) last_shown = s;
   if (show)
     fprintf(stderr,
-            "[topk_attn_b200] plan: hg=%d nq=%d(valid %d) bshare=%d cluster=%d nsplit=%d cap=%d "
+            "[topk_attn_b200] plan: hg=%d nq=%d(valid %d, qsplit %d) bshare=%d cluster=%d nsplit=%d cap=%d "
             "stages=%d groups=%d rdv=%d per=%d part_len=%d grid=%d smem=%zu | merge: cluster=%d cap=%d smem=%zu | "
             "model %.1f us\n",
-            pl.hg, pl.nq, pl.nq_valid, pl.bshare, pl.cluster, pl.nsplit, pl.cap, pl.nstages, pl.groups,
+            pl.hg, pl.nq, pl.nq_valid, pl.qsplit, pl.bshare, pl.cluster, pl.nsplit, pl.cap, pl.nstages, pl.groups,
             pl.rendezvous, pl.per,
             pl.part_len, pl.grid, pl.smem, pl.cluster2, pl.cap2, pl.smem2, pl.cost * 1e6);
   if (p->workspace_bytes < workspace_bound(s)) {
@@ -363,6 +376,7 @@ int run(const ra_params* p, bool attend) {
   sp.status = status;
   sp.batch = s.batch; sp.hq = s.hq; sp.hkv = s.hkv; sp.n_tokens = s.n;
   sp.group = c.group; sp.bshare = pl.bshare; sp.nq_valid = pl.nq_valid;
+  sp.qsplit = pl.qsplit; sp.nq_cta = pl.nq_cta;
   sp.kv_per_batch = s.per_batch;
   sp.cap = pl.cap; sp.nstages = pl.nstages; sp.groups = pl.groups; sp.rendezvous = pl.rendezvous; sp.nparts = parts; sp.part_len = pl.part_len;
   sp.head_major = s.head_major;

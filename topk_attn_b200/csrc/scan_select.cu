@@ -31,7 +31,8 @@ struct Ctrl {
   int cnt[kMaxLists];
   uint32_t thr[kMaxLists];
   int hist[256];
-  int digit, remaining, wpos, eqc;
+  int digit, remaining, wpos, eqc, binpop;
+  uint32_t kmax;
   int timeout;
 };
 
@@ -40,21 +41,38 @@ __device__ __forceinline__ void consumer_sync(int nct) {
   asm volatile("bar.sync 1, %0;" ::"r"(nct) : "memory");
 }
 
-// Raise the threshold of list `l` to its exact k-th largest key and keep only the k best.
-// Called by all consumer threads.
+// Cut list `l` back: raise its threshold so that at least k and at most `accept` candidates stay.
+// All candidates lie above the old threshold, so the radix select works on (key - old threshold)
+// and starts at the highest bit that actually differs; it stops as soon as keeping the whole
+// current bin leaves few enough candidates, and only runs down to an exact k-th key (with ties
+// taken one by one) when it has to.  Called by all consumer threads.
 __device__ void compact_list(uint32_t* keys, int* idxs, Ctrl* ctrl, int l, int k, int cap,
-                             int tid, int nct) {
+                             int accept, int tid, int nct) {
   const int n = min(ctrl->cnt[l], cap);
   const int lane = tid & 31;
-  uint32_t prefix = 0, mask = 0;
+  const uint32_t base = ctrl->thr[l] + 1u;  // smallest key the list can hold
+  if (tid == 0) ctrl->kmax = 0u;
+  consumer_sync(nct);
+  {
+    uint32_t mx = 0u;
+    for (int i = tid; i < n; i += nct) mx = max(mx, keys[i]);
+#pragma unroll
+    for (int off = 16; off; off >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    if (lane == 0) atomicMax(&ctrl->kmax, mx);
+  }
+  consumer_sync(nct);
+  const uint32_t range = ctrl->kmax - base;
+  int shift = max(0, 32 - __clz((int)(range | 1u)) - 8);
+  uint32_t prefix = 0u, mask = 0u;
   int remaining = k;
+  bool inclusive = false;
 #pragma unroll 1
-  for (int shift = 24; shift >= 0; shift -= 8) {
+  for (;;) {
     if (tid < 256) ctrl->hist[tid] = 0;
     consumer_sync(nct);
     for (int i = tid; i < n; i += nct) {
-      const uint32_t key = keys[i];
-      if ((key & mask) == prefix) atomicAdd(&ctrl->hist[(key >> shift) & 255], 1);
+      const uint32_t rel = keys[i] - base;
+      if ((rel & mask) == prefix) atomicAdd(&ctrl->hist[(rel >> shift) & 255], 1);
     }
     consumer_sync(nct);
     if (tid < 32) {
@@ -63,38 +81,48 @@ __device__ void compact_list(uint32_t* keys, int* idxs, Ctrl* ctrl, int l, int k
       if (lane == 0) {
         ctrl->digit = d;
         ctrl->remaining = nr;
+        ctrl->binpop = ctrl->hist[d];
       }
     }
     consumer_sync(nct);
     prefix |= (uint32_t)ctrl->digit << shift;
-    mask |= 255u << shift;
+    mask = 0xffffffffu << shift;
     remaining = ctrl->remaining;
+    // candidates at or above the start of the chosen bin
+    const int kept = (k - remaining) + ctrl->binpop;
+    if (kept <= accept) {
+      inclusive = true;
+      break;
+    }
+    if (shift == 0) break;
+    shift = max(0, shift - 8);
   }
-  const uint32_t kth = prefix;
+  // inclusive: keep every key >= base + prefix; exact: keep keys above the k-th and need_eq ties
+  const uint32_t kth = base + prefix;
   const int need_eq = remaining;
   if (tid == 0) {
     ctrl->wpos = 0;
     ctrl->eqc = 0;
   }
   consumer_sync(nct);
-  constexpr int E = 4;
+  constexpr int E = 8;
 #pragma unroll 1
-  for (int base = 0; base < n; base += nct * E) {
+  for (int cb = 0; cb < n; cb += nct * E) {
     uint32_t kk[E];
     int ii[E];
 #pragma unroll
     for (int e = 0; e < E; ++e) {
-      const int i = base + e * nct + tid;
+      const int i = cb + e * nct + tid;
       kk[e] = (i < n) ? keys[i] : 0u;
       ii[e] = (i < n) ? idxs[i] : 0;
     }
     consumer_sync(nct);
 #pragma unroll
     for (int e = 0; e < E; ++e) {
-      const int i = base + e * nct + tid;
+      const int i = cb + e * nct + tid;
       if (i < n) {
-        bool keep = kk[e] > kth;
-        if (!keep && kk[e] == kth) keep = atomicAdd(&ctrl->eqc, 1) < need_eq;
+        bool keep = inclusive ? (kk[e] >= kth) : (kk[e] > kth);
+        if (!inclusive && kk[e] == kth) keep = atomicAdd(&ctrl->eqc, 1) < need_eq;
         if (keep) {
           const int p = atomicAdd(&ctrl->wpos, 1);
           keys[p] = kk[e];
@@ -106,7 +134,7 @@ __device__ void compact_list(uint32_t* keys, int* idxs, Ctrl* ctrl, int l, int k
   }
   if (tid == 0) {
     ctrl->cnt[l] = ctrl->wpos;
-    ctrl->thr[l] = kth;
+    ctrl->thr[l] = inclusive ? kth - 1u : kth;
   }
   consumer_sync(nct);
 }
@@ -142,6 +170,8 @@ scan_select_kernel(const __grid_constant__ ScanParams P) {
   const int G = P.groups;      // consumer warp groups (1 or 2), each on its own tile
   const int R = P.rendezvous;  // iterations between overflow checks
   const int nct = 256 * G;     // consumer threads
+  // a cut may leave up to half of the free room occupied
+  const int accept = P.m.topk + max(0, (P.cap - R * G * (kTileRows / HG) - P.m.topk) / 2);
   extern __shared__ __align__(128) unsigned char smem_raw[];
   unsigned char* smem =
       reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
@@ -161,6 +191,10 @@ scan_select_kernel(const __grid_constant__ ScanParams P) {
   int cid = blockIdx.x / C;
   const int part = cid % P.nparts;
   cid /= P.nparts;
+  // the queries that share a K row may be dealt over several clusters (each re-reads the rows,
+  // mostly from L2, and keeps fewer candidate lists): this cluster scores queries q0 .. q0+nq_cta-1
+  const int q0 = (cid % P.qsplit) * P.nq_cta;
+  cid /= P.qsplit;
   const int hgroups = P.hkv / HG;
   const int h0 = (cid % hgroups) * HG;
   const int b0 = (cid / hgroups) * P.bshare;
@@ -237,9 +271,9 @@ scan_select_kernel(const __grid_constant__ ScanParams P) {
     uint32_t qh[NQ][8];
 #pragma unroll
     for (int qi = 0; qi < NQ; ++qi) {
-      if (qi < P.nq_valid) {
-        const int bq = b0 + qi / P.group;
-        const int hq = (h0 + hh) * P.group + qi % P.group;
+      if (qi < P.nq_cta && q0 + qi < P.nq_valid) {
+        const int bq = b0 + (q0 + qi) / P.group;
+        const int hq = (h0 + hh) * P.group + (q0 + qi) % P.group;
         const __half* qp = P.q + ((size_t)bq * P.hq + hq) * kHeadDim;
         const uint4 a = *reinterpret_cast<const uint4*>(qp + 8 * j);
         const uint4 b = *reinterpret_cast<const uint4*>(qp + 64 + 8 * j);
@@ -258,7 +292,7 @@ scan_select_kernel(const __grid_constant__ ScanParams P) {
 #pragma unroll
     for (int v = 0; v < NV; ++v) {
       const int qi = 2 * v + my_qpar;
-      my_valid[v] = (NQ == 1) ? (b0l == 0) : (qi < P.nq_valid && qi < NQ);
+      my_valid[v] = (NQ == 1) ? (b0l == 0) : (qi < P.nq_cta && q0 + qi < P.nq_valid && qi < NQ);
       my_list[v] = hh * NQ + ((NQ == 1) ? 0 : min(qi, NQ - 1));
       my_thr[v] = 0u;
     }
@@ -278,9 +312,9 @@ scan_select_kernel(const __grid_constant__ ScanParams P) {
     const int a_tok = w8 * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
     const int a_c8 = lane >> 4;
     if constexpr (MODE == 2) {
-      if (mg < P.nq_valid) {
-        const int bq = b0 + mg / P.group;
-        const int hq = h0 * P.group + mg % P.group;
+      if (mg < P.nq_cta && q0 + mg < P.nq_valid) {
+        const int bq = b0 + (q0 + mg) / P.group;
+        const int hq = h0 * P.group + (q0 + mg) % P.group;
         const __half* qp = P.q + ((size_t)bq * P.hq + hq) * kHeadDim;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
@@ -323,7 +357,8 @@ scan_select_kernel(const __grid_constant__ ScanParams P) {
             const int qi = 2 * mt + (jv & 1);
             const int tok = tok_lo + 8 * (jv >> 1);
             const uint32_t key = score_key(c[jv]);
-            const bool pass = qi < P.nq_valid && tok < part_hi && key > thr2[jv & 1];
+            const bool pass = qi < P.nq_cta && q0 + qi < P.nq_valid && tok < part_hi &&
+                              key > thr2[jv & 1];
             const unsigned bal = __ballot_sync(0xffffffffu, pass);
             if (bal) {
               const unsigned mym = bal & tmask;
@@ -442,7 +477,7 @@ scan_select_kernel(const __grid_constant__ ScanParams P) {
 #pragma unroll
           for (int l = 0; l < NL; ++l)
             if ((need >> l) & 1)
-              compact_list(keys + (size_t)l * cap, idxs + (size_t)l * cap, ctrl, l, k, cap, tid, nct);
+              compact_list(keys + (size_t)l * cap, idxs + (size_t)l * cap, ctrl, l, k, cap, accept, tid, nct);
 #pragma unroll
           for (int v = 0; v < NV; ++v) my_thr[v] = ctrl->thr[my_list[v]];
           if constexpr (MODE == 2) {
@@ -462,10 +497,10 @@ scan_select_kernel(const __grid_constant__ ScanParams P) {
   auto dest = [&](int l) {
     ListDest d;
     const int lh = l / NQ, qi = l % NQ;
-    d.valid = qi < P.nq_valid;
-    d.bq = b0 + qi / P.group;
+    d.valid = qi < P.nq_cta && q0 + qi < P.nq_valid;
+    d.bq = b0 + (q0 + qi) / P.group;
     d.hkv = h0 + lh;
-    d.hq = (h0 + lh) * P.group + qi % P.group;
+    d.hq = (h0 + lh) * P.group + (q0 + qi) % P.group;
     return d;
   };
   cluster_select_attend<NL>(cluster, stages, keys, idxs, ctrl->cnt, cap, A, dest);

@@ -12,7 +12,9 @@ struct ScanParams {
   int batch, hq, hkv, n_tokens;
   int group;                 // hq / hkv
   int bshare;                // batch rows that share one cache and are scored together
-  int nq_valid;              // bshare * group, queries scored per K row (<= NQ)
+  int nq_valid;              // bshare * group, queries that share a K row
+  int qsplit;                // clusters the queries of a row are dealt over
+  int nq_cta;                // nq_valid / qsplit, queries scored per K row by one cluster (<= NQ)
   int kv_per_batch;          // 1: every batch row has its own cache
   int cap;                   // capacity of a candidate list (>= topk + 2 tiles)
   int nstages;               // TMA pipeline depth (a multiple of groups)
