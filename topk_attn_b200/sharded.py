@@ -120,7 +120,13 @@ def bench(args, rank: int, local: int, world: int, ClockSampler, measured_peak_g
     of the 4 sequences (32 heads, k = 2048).  Timed on the device, max over ranks."""
     from . import ops, workloads as W
     dev = torch.device("cuda", local)
-    w = W.fused_topk_128k_shard(rank, world, device=dev)
+    strong = args.workload == "cfg4"
+    if strong:
+        # configuration 4: 1 048 576 tokens in total (32 query / 8 kv heads, k = 4096) cut over the
+        # ranks, so the work per rank shrinks as ranks are added
+        w = W.sharded_long_context_shard(rank, world, device=dev)
+    else:
+        w = W.fused_topk_128k_shard(rank, world, device=dev)
     q, k, v = w.q, w.k, w.v
     op = ShardedTopkAttention(w.topk, w.sm_scale)
     n_local = w.n_tokens
@@ -189,9 +195,10 @@ def bench(args, rank: int, local: int, world: int, ClockSampler, measured_peak_g
             "metric": "tokens_scanned_per_s", "value": tokens / (per_ms * 1e-3), "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": per_ms, "us_per_step": per_ms * 1e3, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f16 inputs, f32 accumulate",
+            "scaling": "strong" if strong else "weak", "vs_baseline": None,
+            "dtype": "f16 inputs, f32 accumulate",
             "data": "synthetic",
-            "config": {"workload": "cfg2 token-sharded", "batch": w.batch, "heads_q": q.size(1),
+            "config": {"workload": "cfg4 token-sharded" if strong else "cfg2 token-sharded", "batch": w.batch, "heads_q": q.size(1),
                        "heads_kv": k.size(-2), "head_dim": 128, "context": world * n_local,
                        "context_per_gpu": n_local, "topk": w.topk, "caches": w.bkv,
                        "l2": "inputs_exceed_l2", "collectives": "nccl all_gather x2"},
