@@ -178,6 +178,35 @@ int ra_center_only_topk(const ra_center_params* p);
 size_t ra_center_workspace_bytes(int32_t batch, int32_t num_heads, int32_t num_centers,
                                  int32_t top_clusters);
 
+/* Two-level retrieval: keep the top_clusters best centroids of every head, then inside each
+ * kept cluster (cluster_len contiguous tokens) the topk_per_cluster best keys; optionally attend
+ * over all kept keys.  out_indices is [batch, num_heads, top_clusters * topk_per_cluster] with
+ * one slice per cluster in descending order of the centroid scores, unordered inside a slice —
+ * the layout of gemv_topk_kernel (gemv_topk.cu:173-380, baseline_1.cu:103-319); with out it
+ * is the pipeline of baseline_1.cu / baseline_2.cu (selection + gathered decode). */
+typedef struct ra_two_level_params {
+  const void* q;            /* fp16 [batch, num_heads, 128] */
+  const void* centers;      /* fp16 [num_heads, num_centers, 128] */
+  const void* k;            /* fp16 [num_tokens, num_heads, 128] or one cache per batch row */
+  const void* v;            /* needed with out */
+  void* out;                /* optional fp16 [batch, num_heads, 128] */
+  int32_t batch, num_heads, head_dim;
+  int32_t num_centers, cluster_len, top_clusters, topk_per_cluster;
+  int32_t num_tokens;       /* >= num_centers * cluster_len */
+  int64_t kv_batch_stride, kv_token_stride, kv_head_stride;
+  float sm_scale;
+  int32_t* out_cluster_ids; /* optional int32 [batch, num_heads, top_clusters], rank order */
+  int32_t* out_indices;     /* optional int32, see above */
+  float* out_scores;        /* optional fp32, same shape as out_indices */
+  void* workspace;          /* ra_two_level_workspace_bytes() */
+  size_t workspace_bytes;
+  void* stream;
+} ra_two_level_params;
+
+int ra_two_level_topk(const ra_two_level_params* p);
+size_t ra_two_level_workspace_bytes(int32_t batch, int32_t num_heads, int32_t num_centers,
+                                    int32_t top_clusters, int32_t topk_per_cluster);
+
 /* Dense decode attention over the whole cache, split-KV with a log-sum-exp combine
  * ("flash decoding"): the dense baseline of the path and the reference's
  * baseline_attention_kernel (retrieval_attn/retrieval_attention.cu:51-168) /

@@ -47,7 +47,7 @@ def struct_fields(name):
 @pytest.mark.parametrize("cname,pyname", [
     ("ra_params", "RaParams"), ("ra_merge_params", "RaMergeParams"),
     ("ra_gather_params", "RaGatherParams"), ("ra_center_params", "RaCenterParams"),
-    ("ra_dense_params", "RaDenseParams"),
+    ("ra_dense_params", "RaDenseParams"), ("ra_two_level_params", "RaTwoLevelParams"),
 ])
 def test_ctypes_mirrors_match_header(cname, pyname):
     from topk_attn_b200 import capi

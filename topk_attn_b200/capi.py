@@ -93,6 +93,22 @@ class RaDenseParams(C.Structure):
     ]
 
 
+class RaTwoLevelParams(C.Structure):
+    """Mirror of ``struct ra_two_level_params``."""
+    _fields_ = [
+        ("q", C.c_void_p), ("centers", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p),
+        ("out", C.c_void_p),
+        ("batch", C.c_int32), ("num_heads", C.c_int32), ("head_dim", C.c_int32),
+        ("num_centers", C.c_int32), ("cluster_len", C.c_int32), ("top_clusters", C.c_int32),
+        ("topk_per_cluster", C.c_int32), ("num_tokens", C.c_int32),
+        ("kv_batch_stride", C.c_int64), ("kv_token_stride", C.c_int64),
+        ("kv_head_stride", C.c_int64),
+        ("sm_scale", C.c_float),
+        ("out_cluster_ids", C.c_void_p), ("out_indices", C.c_void_p), ("out_scores", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("stream", C.c_void_p),
+    ]
+
+
 class RaError(RuntimeError):
     def __init__(self, status: int, text: str, detail: str = ""):
         super().__init__(f"topk_attn_b200: {text} (status {status})" + (f": {detail}" if detail else ""))
@@ -131,6 +147,8 @@ def _declare(l: C.CDLL) -> None:
         "ra_merge_attend": (C.c_int, [C.POINTER(RaMergeParams)]),
         "ra_gathered_attention": (C.c_int, [C.POINTER(RaGatherParams)]),
         "ra_flash_decoding": (C.c_int, [C.POINTER(RaDenseParams)]),
+        "ra_two_level_topk": (C.c_int, [C.POINTER(RaTwoLevelParams)]),
+        "ra_two_level_workspace_bytes": (sz, [i32, i32, i32, i32, i32]),
         "ra_flash_workspace_bytes": (sz, [i32, i32, i32, i32, i32]),
         "ra_center_only_topk": (C.c_int, [C.POINTER(RaCenterParams)]),
         "ra_center_workspace_bytes": (sz, [i32, i32, i32, i32]),

@@ -130,7 +130,8 @@ Plan make_plan(const Shape& s) {
     sscanf(f, "%d,%d,%d,%d", &f_hg, &f_cluster, &f_nsplit, &f_stages);
   const int group = s.hq / s.hkv;
   int bshare = 1;
-  if (!s.per_batch) {
+  const bool own_parts = (s.fused_ok & 2) != 0;
+  if (!s.per_batch && !own_parts) {
     for (int b = 1; b <= s.batch; ++b)
       if (s.batch % b == 0 && b * group <= 8) bshare = b;
   }
@@ -145,6 +146,7 @@ Plan make_plan(const Shape& s) {
     const int nq_cta = nq_valid / qsplit;
     const int nq = next_pow2(nq_cta);
     if (qsplit > 1 && hg != 1) continue;
+    if (own_parts && hg != 1) continue;
     if (s.hkv % hg || !combo_built(hg, nq)) continue;
     if (s.head_major && hg != 1) continue;
     if (f_hg && hg != f_hg) continue;
@@ -209,7 +211,7 @@ Plan make_plan(const Shape& s) {
         const double room = std::max(64, cap - s.topk - margin);
         const double slab = (double)ceil_div(tiles, cluster) * T;
         const double cuts = slab > cap ? std::log(slab / cap) / std::log1p(room / s.topk) + 1.0 : 0.0;
-        const bool two_stage = nsplit > 1 || s.segments > 1 || !s.fused_ok;
+        const bool two_stage = nsplit > 1 || s.segments > 1;
         double cost = waves * (bytes_cta / rate + cuts * nl * 2e-6 + 6e-6 + 1.5e-6 * cluster) +
                       (two_stage ? 8e-6 : 0.0);
         Plan pl;
@@ -292,7 +294,8 @@ size_t workspace_bound(const Shape& s) {
   return (w + 255) & ~size_t(255);
 }
 
-int encode_kmap(CUtensorMap* map, const ra_params* p, const Shape& s, int hg, bool swizzled) {
+int encode_kmap(CUtensorMap* map, const ra_params* p, const Shape& s, int hg, bool swizzled,
+                int n_tokens) {
   EncodeTiledFn enc = encode_fn();
   if (!enc) {
     g_last_error = "cuTensorMapEncodeTiled is not available from the driver";
@@ -301,17 +304,17 @@ int encode_kmap(CUtensorMap* map, const ra_params* p, const Shape& s, int hg, bo
   const cuuint64_t nb = s.per_batch ? (cuuint64_t)p->batch : 1;
   cuuint64_t bstride =
       s.per_batch ? (cuuint64_t)p->kv_batch_stride * 2
-                  : (cuuint64_t)16 * (((cuuint64_t)p->num_tokens * p->kv_token_stride * 2 + 15) / 16);
+                  : (cuuint64_t)16 * (((cuuint64_t)n_tokens * p->kv_token_stride * 2 + 15) / 16);
   cuuint64_t dims[4], strides[3];
   cuuint32_t box[4], estr[4] = {1, 1, 1, 1};
   const int T = kTileRows / hg;
   if (s.head_major) {
-    dims[0] = kHeadDim; dims[1] = p->num_tokens; dims[2] = p->num_kv_heads; dims[3] = nb;
+    dims[0] = kHeadDim; dims[1] = n_tokens; dims[2] = p->num_kv_heads; dims[3] = nb;
     strides[0] = (cuuint64_t)p->kv_token_stride * 2; strides[1] = (cuuint64_t)p->kv_head_stride * 2;
     box[0] = kHeadDim; box[1] = T; box[2] = 1; box[3] = 1;
     if (!s.per_batch) bstride = (cuuint64_t)p->num_kv_heads * p->kv_head_stride * 2;
   } else {
-    dims[0] = kHeadDim; dims[1] = p->num_kv_heads; dims[2] = p->num_tokens; dims[3] = nb;
+    dims[0] = kHeadDim; dims[1] = p->num_kv_heads; dims[2] = n_tokens; dims[3] = nb;
     strides[0] = (cuuint64_t)p->kv_head_stride * 2; strides[1] = (cuuint64_t)p->kv_token_stride * 2;
     box[0] = kHeadDim; box[1] = hg; box[2] = T; box[3] = 1;
   }
@@ -333,13 +336,21 @@ int encode_kmap(CUtensorMap* map, const ra_params* p, const Shape& s, int hg, bo
 constexpr float kLog2e = 1.4426950408889634f;
 
 // attend == false: selection only (indices/scores out).
-int run(const ra_params* p, bool attend) {
+// Two-level retrieval: part i of a (batch row, head) is the cluster ids[row][i] of cluster_len
+// tokens instead of the i-th slice of the token axis; p->num_tokens is then parts * cluster_len.
+struct PartIds {
+  const int* ids;
+  int real_tokens;
+};
+
+int run(const ra_params* p, bool attend, const PartIds* ext = nullptr) {
   Checked c;
   int st = check_params(p, attend, attend, c);
   if (st != RA_OK) return st;
   if (!attend && !p->out_indices) return invalid("out_indices is required");
   Shape s = c.shape;
-  s.fused_ok = 1;
+  s.fused_ok = ext ? 3 : 1;  // bit 1: every (row, head) scans its own parts — nothing is shared
+  const int real_tokens = ext ? ext->real_tokens : s.n;
   const Plan pl = make_plan(s);
   if (!pl.ok) return unsupported("no launch geometry fits these sizes");
   static const bool verbose = getenv("RA_VERBOSE") != nullptr;
@@ -369,12 +380,13 @@ int run(const ra_params* p, bool attend) {
   memset(&sp, 0, sizeof sp);
   // several queries per K row (GQA group, batch rows on one cache): score on the tensor cores
   const bool swizzled = pl.hg == 1 && pl.nq > 1 && !getenv("RA_NO_MMA");
-  st = encode_kmap(&sp.kmap, p, s, pl.hg, swizzled);
+  st = encode_kmap(&sp.kmap, p, s, pl.hg, swizzled, real_tokens);
   sp.swizzled = swizzled;
   if (st != RA_OK) return st;
   sp.q = static_cast<const __half*>(p->q);
   sp.status = status;
-  sp.batch = s.batch; sp.hq = s.hq; sp.hkv = s.hkv; sp.n_tokens = s.n;
+  sp.batch = s.batch; sp.hq = s.hq; sp.hkv = s.hkv; sp.n_tokens = real_tokens;
+  sp.part_ids = ext ? ext->ids : nullptr;
   sp.group = c.group; sp.bshare = pl.bshare; sp.nq_valid = pl.nq_valid;
   sp.qsplit = pl.qsplit; sp.nq_cta = pl.nq_cta;
   sp.kv_per_batch = s.per_batch;
@@ -386,7 +398,7 @@ int run(const ra_params* p, bool attend) {
   m.hq_total = s.hq; m.list_pitch = parts * s.topk; m.list_off = 0;
   m.index_base = two_stage ? 0 : p->index_base;
   m.own_lo = 0; m.own_hi = 0x7fffffff; m.id_shift = 0;
-  m.n_tokens = s.n; m.status = status;
+  m.n_tokens = real_tokens; m.status = status;
   m.v = static_cast<const __half*>(p->v);
   m.v_batch_stride = p->kv_batch_stride; m.v_token_stride = p->kv_token_stride;
   m.v_head_stride = p->kv_head_stride;
@@ -661,6 +673,79 @@ int ra_center_only_topk(const ra_center_params* p) {
                     static_cast<unsigned*>(p->workspace), attend,
                     static_cast<cudaStream_t>(p->stream));
   (void)n_members;
+}
+
+size_t ra_two_level_workspace_bytes(int32_t batch, int32_t num_heads, int32_t num_centers,
+                                    int32_t top_clusters, int32_t topk_per_cluster) {
+  if (batch < 1 || num_heads < 1 || num_centers < 1 || top_clusters < 1 || topk_per_cluster < 1)
+    return 0;
+  const size_t rows = (size_t)batch * num_heads;
+  // [centroid selection scratch][fine selection scratch][cluster ids + scores, twice]
+  const size_t coarse = ra_center_workspace_bytes(batch, num_heads, num_centers, top_clusters);
+  // a single cluster may be scanned in up to kMaxSplit parts
+  const size_t fine = kStatusBytes + rows * top_clusters * topk_per_cluster * 8 * (top_clusters == 1 ? kMaxSplit : 1) + 256;
+  return coarse + fine + rows * top_clusters * 16 + 512;
+}
+
+int ra_two_level_topk(const ra_two_level_params* p) {
+  if (!p) return invalid("params is null");
+  if (!p->q || !p->centers || !p->k) return invalid("q, centers or k is null");
+  if (p->head_dim != kHeadDim) return unsupported("head_dim must be 128");
+  if (p->batch < 1 || p->num_heads < 1 || p->num_centers < 1 || p->cluster_len < 1 ||
+      p->top_clusters < 1 || p->top_clusters > p->num_centers || p->topk_per_cluster < 1 ||
+      p->topk_per_cluster > p->cluster_len || p->top_clusters > 1024)
+    return invalid("bad two-level sizes");
+  if ((long long)p->num_centers * p->cluster_len > p->num_tokens)
+    return invalid("num_centers * cluster_len exceeds num_tokens");
+  const bool attend = p->out != nullptr;
+  if (attend && !p->v) return invalid("v is required with out");
+  if (!attend && !p->out_indices) return invalid("nothing to compute");
+  const size_t need = ra_two_level_workspace_bytes(p->batch, p->num_heads, p->num_centers,
+                                                   p->top_clusters, p->topk_per_cluster);
+  if (!p->workspace || p->workspace_bytes < need || (reinterpret_cast<uintptr_t>(p->workspace) & 255u)) {
+    g_last_error = "workspace missing, misaligned or smaller than ra_two_level_workspace_bytes()";
+    return RA_ERR_WORKSPACE;
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
+  const size_t rows = (size_t)p->batch * p->num_heads;
+  char* ws = static_cast<char*>(p->workspace);
+  const size_t coarse = (ra_center_workspace_bytes(p->batch, p->num_heads, p->num_centers,
+                                                   p->top_clusters) + 255) & ~size_t(255);
+  const size_t fine = (kStatusBytes + rows * p->top_clusters * p->topk_per_cluster * 8 * (p->top_clusters == 1 ? kMaxSplit : 1) + 511) & ~size_t(255);
+  float* c_score = reinterpret_cast<float*>(ws + coarse + fine);
+  int* c_ids = reinterpret_cast<int*>(c_score + rows * p->top_clusters);
+  int* c_sorted = c_ids + rows * p->top_clusters;
+  // 1) top clusters by centroid score
+  ra_params sp;
+  memset(&sp, 0, sizeof sp);
+  sp.q = p->q; sp.k = p->centers;
+  sp.batch = p->batch; sp.num_q_heads = p->num_heads; sp.num_kv_heads = p->num_heads;
+  sp.head_dim = kHeadDim; sp.num_tokens = p->num_centers;
+  sp.kv_token_stride = kHeadDim; sp.kv_head_stride = (int64_t)p->num_centers * kHeadDim;
+  sp.topk = p->top_clusters; sp.num_segments = 1; sp.sm_scale = 1.f;
+  sp.out_indices = c_ids; sp.out_scores = c_score;
+  sp.workspace = ws; sp.workspace_bytes = coarse; sp.stream = p->stream;
+  int st = run(&sp, false);
+  if (st != RA_OK) return st;
+  // 2) rank order
+  int* sorted = p->out_cluster_ids ? p->out_cluster_ids : c_sorted;
+  cudaError_t e = launch_rank_sort(c_score, c_ids, (int)rows, p->top_clusters, sorted, nullptr, stream);
+  if (e != cudaSuccess) return cuda_fail(e, "rank_sort launch");
+  // 3) per-cluster top-k over the chosen clusters (+ attention over all kept keys)
+  ra_params fp;
+  memset(&fp, 0, sizeof fp);
+  fp.q = p->q; fp.k = p->k; fp.v = p->v; fp.out = p->out;
+  fp.batch = p->batch; fp.num_q_heads = p->num_heads; fp.num_kv_heads = p->num_heads;
+  fp.head_dim = kHeadDim;
+  fp.num_tokens = p->top_clusters * p->cluster_len;  // the tokens actually scanned per head
+  fp.kv_batch_stride = p->kv_batch_stride; fp.kv_token_stride = p->kv_token_stride;
+  fp.kv_head_stride = p->kv_head_stride;
+  fp.topk = p->topk_per_cluster; fp.num_segments = p->top_clusters;
+  fp.sm_scale = p->sm_scale > 0.f ? p->sm_scale : 1.f;
+  fp.out_indices = p->out_indices; fp.out_scores = p->out_scores;
+  fp.workspace = ws + coarse; fp.workspace_bytes = fine; fp.stream = p->stream;
+  PartIds ext = {sorted, p->num_tokens};
+  return run(&fp, attend, &ext);
 }
 
 // Effective split geometry: split_len is a multiple of the 128-token tile.

@@ -131,6 +131,36 @@ gather_attend_kernel(const __grid_constant__ GatherParams P) {
   cluster_select_attend<1>(cluster, smem, keys, idxs, cnt, P.cap, A, dest);
 }
 
+// Orders the n (score, id) pairs of every row by descending score (ties: ascending id), the rank
+// order in which the reference lists its chosen clusters (gemv_topk.cu:103-104, partial_sort).
+__global__ void __launch_bounds__(256)
+rank_sort_kernel(const float* __restrict__ score, const int* __restrict__ idx, int n,
+                 int* __restrict__ out_idx, float* __restrict__ out_score) {
+  extern __shared__ float sh[];
+  float* ss = sh;
+  int* si = reinterpret_cast<int*>(sh + n);
+  const size_t row = blockIdx.x;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    ss[i] = score[row * n + i];
+    si[i] = idx[row * n + i];
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float a = ss[i];
+    const int ia = si[i];
+    int rank = 0;
+    for (int j = 0; j < n; ++j) rank += (ss[j] > a) || (ss[j] == a && si[j] < ia);
+    out_idx[row * n + rank] = ia;
+    if (out_score) out_score[row * n + rank] = a;
+  }
+}
+
+cudaError_t launch_rank_sort(const float* score, const int* idx, int rows, int n, int* out_idx,
+                             float* out_score, cudaStream_t stream) {
+  rank_sort_kernel<<<rows, 256, (size_t)n * 8, stream>>>(score, idx, n, out_idx, out_score);
+  return cudaGetLastError();
+}
+
 size_t gather_attend_smem_bytes(int per, int cap, int n_src) {
   return ((sizeof(MergeScratch) + (size_t)per * 8 + 127) & ~size_t(127)) + (size_t)cap * 8 + 16 +
          (size_t)n_src * 4 + 128;

@@ -200,7 +200,11 @@ scan_select_kernel(const __grid_constant__ ScanParams P) {
   const int b0 = (cid / hgroups) * P.bshare;
   const int kv_b = P.kv_per_batch ? b0 : 0;
 
-  const int part_lo = part * P.part_len;
+  // a part is normally the part-th slice of the token axis; with part_ids it is the cluster whose
+  // id the (batch row, head) chose at that rank (two-level retrieval, one head and query per CTA)
+  const int part_lo =
+      (P.part_ids ? P.part_ids[((size_t)b0 * P.hq + (size_t)h0 * P.group) * P.nparts + part] : part) *
+      P.part_len;
   const int part_hi = min(P.n_tokens, part_lo + P.part_len);
   const int ntiles_part = ceil_div(max(part_hi - part_lo, 0), T);
   const int tpc = ceil_div(ntiles_part, C);

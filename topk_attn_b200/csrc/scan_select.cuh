@@ -9,6 +9,7 @@ struct ScanParams {
   MergeArgs m;               // selection / output arguments (list_off is set per cluster)
   const __half* q;           // [B,Hq,128]
   unsigned* status;          // one word, bit 0 = a bounded wait gave up
+  const int* part_ids;       // optional [B,Hq,nparts]: which slice of length part_len each part is
   int batch, hq, hkv, n_tokens;
   int group;                 // hq / hkv
   int bshare;                // batch rows that share one cache and are scored together

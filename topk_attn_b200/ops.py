@@ -205,6 +205,39 @@ def center_only_topk(q: Tensor, centers: Tensor, top_clusters: int, cluster_len:
     return res + (out,) if out is not None else res
 
 
+def two_level_topk(q: Tensor, centers: Tensor, k: Tensor, top_clusters: int, cluster_len: int,
+                   topk_per_cluster: int, v: Optional[Tensor] = None, sm_scale: float = 1.0):
+    """Two-level retrieval.  Returns (cluster_ids int32 [B,H,TOPC] in rank order, indices int32
+    [B,H,TOPC*K] one slice per cluster rank, scores fp32 of the same shape[, out fp16 [B,H,128]
+    when ``v`` is given])."""
+    B, H, Hkv, N, bstride = _check_qkv(q, k, v)
+    if Hkv != H or centers.dim() != 3 or centers.size(0) != H or centers.size(2) != 128 \
+            or centers.dtype != torch.float16 or not centers.is_contiguous():
+        raise ValueError("two-level retrieval needs MHA caches and fp16 centers [H,CSZ,128]")
+    dev = q.device
+    p = capi.RaTwoLevelParams()
+    p.q, p.centers, p.k = q.data_ptr(), centers.data_ptr(), k.data_ptr()
+    p.batch, p.num_heads, p.head_dim = B, H, 128
+    p.num_centers, p.cluster_len = centers.size(1), cluster_len
+    p.top_clusters, p.topk_per_cluster, p.num_tokens = top_clusters, topk_per_cluster, N
+    p.kv_batch_stride, p.kv_token_stride, p.kv_head_stride = bstride, H * 128, 128
+    p.sm_scale = sm_scale
+    cids = torch.empty(B, H, top_clusters, dtype=torch.int32, device=dev)
+    idx = torch.empty(B, H, top_clusters * topk_per_cluster, dtype=torch.int32, device=dev)
+    sc = torch.empty(B, H, top_clusters * topk_per_cluster, dtype=torch.float32, device=dev)
+    p.out_cluster_ids, p.out_indices, p.out_scores = cids.data_ptr(), idx.data_ptr(), sc.data_ptr()
+    out = None
+    if v is not None:
+        out = torch.empty_like(q)
+        p.v, p.out = v.data_ptr(), out.data_ptr()
+    need = capi.lib().ra_two_level_workspace_bytes(B, H, centers.size(1), top_clusters,
+                                                  topk_per_cluster)
+    ws = workspace(max(need, 256), dev)
+    p.workspace, p.workspace_bytes, p.stream = ws.data_ptr(), ws.numel(), _stream_ptr()
+    capi.check(capi.lib().ra_two_level_topk(C.byref(p)))
+    return (cids, idx, sc) + ((out,) if out is not None else ())
+
+
 def merge_attend(cand_scores: Tensor, cand_indices: Tensor, v: Tensor, topk: int, sm_scale: float,
                  own_base: int, partial: bool = True, return_indices: bool = False):
     """Select the global top-k out of ``cand_* [parts,B,Hq,topk]`` (global ids) and mix the V rows
