@@ -571,7 +571,7 @@ static int run_gather(const __half* q, const __half* k, const __half* v, __half*
   GatherParams gp;
   memset(&gp, 0, sizeof gp);
   MergeArgs& m = gp.m;
-  m.topk = n_entries; m.per = per; m.cluster = cluster; m.select_all = 1;
+  m.topk = n_entries; m.per = per; m.cluster = cluster; m.select_all = 1; m.local_deal = 1;
   m.out_mode = attend ? kOutFinal : kOutNone;
   m.hq_total = hq; m.list_pitch = n_entries; m.list_off = 0; m.index_base = 0;
   m.own_lo = 0; m.own_hi = 0x7fffffff; m.id_shift = 0; m.n_tokens = n_tokens; m.status = status;
@@ -583,7 +583,9 @@ static int run_gather(const __half* q, const __half* k, const __half* v, __half*
   gp.src_batch_stride = src_bstride; gp.src_head_stride = src_hstride;
   gp.n_src = n_src; gp.expand_clen = expand_clen; gp.n_entries = n_entries;
   gp.out_token_ids = out_token_ids; gp.cap = cap; gp.group = hq / hkv;
-  cudaError_t e = launch_gather_attend(gp, batch * hq, smem, stream);
+  // attention: one pass over K and V with an online softmax; expansion only: the id writer
+  cudaError_t e = attend ? launch_gather_flash(gp, batch * hq, gather_flash_smem_bytes(n_src), stream)
+                         : launch_gather_attend(gp, batch * hq, smem, stream);
   if (e != cudaSuccess) return cuda_fail(e, "gather_attend launch");
   return RA_OK;
 }

@@ -49,6 +49,7 @@ struct MergeArgs {
   int own_lo, own_hi;  // only winners with own_lo <= id < own_hi are mixed (id before index_base)
   int id_shift;        // subtracted from an id to address V (ids of another shard's frame)
   int select_all;      // 1: every candidate is a winner (topk == number of candidates)
+  int local_deal;      // with select_all: CTA c already holds winners c*per .. c*per+cnt-1, keep them
   int n_tokens;        // rows of V; ids outside [0, n_tokens) after the shift are never read
   unsigned* status;    // device status word (bit kStatusBadId is set on such an id)
   int* sel_idx;        // optional
@@ -235,6 +236,18 @@ __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char*
     ms->maxkey[l] = mx;
   }
   __syncthreads();
+  if (A.select_all && A.local_deal) {
+    // nothing to deal: the lists were filled evenly and every entry wins
+#pragma unroll
+    for (int l = 0; l < NL; ++l) {
+      const int n = min(min(cnt[l], cap), per);
+      for (int i = tid; i < n; i += nthr) {
+        sel_key[(size_t)l * per + i] = keys[(size_t)l * cap + i];
+        sel_idx[(size_t)l * per + i] = idxs[(size_t)l * cap + i];
+      }
+    }
+    __syncthreads();
+  } else {
   // deal the winners evenly: global position p goes to CTA p / per, slot p % per
 #pragma unroll
   for (int l = 0; l < NL; ++l) {
@@ -262,6 +275,7 @@ __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char*
     }
   }
   cluster.sync();
+  }
 
 #pragma unroll 1
   for (int l = 0; l < NL; ++l) {

@@ -20,6 +20,8 @@ struct GatherParams {
 };
 
 size_t gather_attend_smem_bytes(int per, int cap, int n_src);
+size_t gather_flash_smem_bytes(int n_src);
+cudaError_t launch_gather_flash(const GatherParams& P, int rows, size_t smem, cudaStream_t stream);
 cudaError_t launch_rank_sort(const float* score, const int* idx, int rows, int n, int* out_idx,
                              float* out_score, cudaStream_t stream);
 cudaError_t launch_gather_attend(const GatherParams& P, int rows, size_t smem, cudaStream_t stream);
