@@ -97,12 +97,15 @@ bool combo_built(int hg, int nq) {
 
 // Second-stage geometry for m_total candidates per row with `topk` winners.
 bool plan_merge(int m_total, int topk, Plan& pl) {
+  int f_c2 = 0;
+  if (const char* f = getenv("RA_FORCE_MERGE_CLUSTER")) f_c2 = atoi(f);
   for (int c2 : {1, 2, 4, 8}) {
+    if (f_c2 && c2 != f_c2) continue;
     const int cap2 = ceil_div(m_total, c2), per2 = ceil_div(topk, c2);
     const size_t smem2 = merge_attend_smem_bytes(per2, cap2);
     if (smem2 > kSmemBudget) continue;
-    // prefer enough CTAs per row to keep the gather short, but never more than needed
-    if (cap2 > 4096 && c2 < 8) continue;
+    // enough CTAs per row to keep the V gather of a CTA short (<= 512 rows) and its list small
+    if (!f_c2 && (cap2 > 4096 || per2 > 512) && c2 < 8) continue;
     pl.cluster2 = c2;
     pl.cap2 = cap2;
     pl.per2 = per2;
@@ -110,6 +113,17 @@ bool plan_merge(int m_total, int topk, Plan& pl) {
     return true;
   }
   return false;
+}
+
+// The single-CTA merge when the row's candidates fit in one CTA's shared memory, else the cluster
+// form.
+cudaError_t dispatch_merge(MergeParams& mp, int rows, const Plan& pl, cudaStream_t stream) {
+  const size_t one = merge_attend_cta_smem_bytes(mp.m_total, mp.m.topk);
+  if (one <= kSmemBudget && !getenv("RA_FORCE_MERGE_CLUSTER")) {
+    mp.m.cluster = 1;
+    return launch_merge_attend_cta(mp, rows, one, stream);
+  }
+  return launch_merge_attend(mp, rows, pl.smem2, stream);
 }
 
 // Pick the launch geometry with the lowest modelled time.  The model: every CTA streams its
@@ -441,7 +455,7 @@ int run(const ra_params* p, bool attend, const PartIds* ext = nullptr) {
   mp.cand_score = sp.m.sel_score; mp.cand_idx = sp.m.sel_idx;
   mp.part_len = s.topk; mp.part_stride = s.topk; mp.row_stride = (long long)parts * s.topk;
   mp.m_total = parts * s.topk; mp.cap = pl.cap2; mp.group = c.group;
-  e = launch_merge_attend(mp, s.batch * s.hq, pl.smem2, stream);
+  e = dispatch_merge(mp, s.batch * s.hq, pl, stream);
   if (e != cudaSuccess) return cuda_fail(e, "merge_attend launch");
   return RA_OK;
 }
@@ -886,8 +900,7 @@ int ra_merge_attend(const ra_merge_params* p) {
                                        : (long long)p->batch * p->num_q_heads * p->topk;
   mp.row_stride = p->topk;
   mp.m_total = (int)m_total; mp.cap = pl.cap2; mp.group = p->num_q_heads / p->num_kv_heads;
-  cudaError_t e = launch_merge_attend(mp, p->batch * p->num_q_heads, pl.smem2,
-                                      static_cast<cudaStream_t>(p->stream));
+  cudaError_t e = dispatch_merge(mp, p->batch * p->num_q_heads, pl, static_cast<cudaStream_t>(p->stream));
   if (e != cudaSuccess) return cuda_fail(e, "merge_attend launch");
   return RA_OK;
 }

@@ -307,7 +307,7 @@ __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char*
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = 0.f;
     float lsum = 0.f;
-    constexpr int UN = 4;
+    constexpr int UN = 8;
     for (int e0 = warp * 2 + (lane >> 4); e0 < n_l; e0 += 2 * nwarps * UN) {
       uint4 vv[UN];
       float w[UN];

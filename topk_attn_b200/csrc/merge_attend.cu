@@ -103,3 +103,202 @@ cudaError_t launch_lse_combine(const float* partials, int parts, int rows, __hal
 }
 
 }  // namespace ra
+
+namespace ra {
+
+// Single-CTA form of the candidate merge for lists that fit in one CTA's shared memory (up to
+// about 22 000 candidates per row): no cluster barriers, 1024 threads.  The exact k-th key is
+// found by a radix select over (key - smallest key), which starts at the highest bit that differs
+// and spreads the histogram atomics over the bins; winners are compacted, written out if asked for,
+// and their V rows mixed by all 32 warps.
+constexpr int kMergeCtaThreads = 1024;
+
+struct MergeCtaCtrl {
+  int hist[256];
+  uint32_t kmin, kmax;
+  int digit, remaining, wpos, eqc;
+  float lred[32];
+};
+
+__global__ void __launch_bounds__(kMergeCtaThreads, 1)
+merge_attend_cta_kernel(const __grid_constant__ MergeParams P) {
+  extern __shared__ __align__(16) unsigned char smem_m[];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int row = blockIdx.x;
+  const int bq = row / P.m.hq_total, hq = row % P.m.hq_total;
+  const int hkv = hq / P.group;
+  const int n = P.m_total, k = P.m.topk;
+  uint32_t* keys = reinterpret_cast<uint32_t*>(smem_m);
+  int* idxs = reinterpret_cast<int*>(keys + n);
+  uint32_t* wkey = reinterpret_cast<uint32_t*>(idxs + n);  // winners
+  int* widx = reinterpret_cast<int*>(wkey + k);
+  float* red = reinterpret_cast<float*>(widx + k);         // [32][128]
+  MergeCtaCtrl* ctrl = reinterpret_cast<MergeCtaCtrl*>(red + 32 * kHeadDim);
+
+  if (tid == 0) {
+    ctrl->kmin = 0xffffffffu;
+    ctrl->kmax = 0u;
+    ctrl->wpos = 0;
+    ctrl->eqc = 0;
+  }
+  __syncthreads();
+  uint32_t mn = 0xffffffffu, mx = 0u;
+  for (int c = tid; c < n; c += kMergeCtaThreads) {
+    const int part = c / P.part_len, off = c - part * P.part_len;
+    const size_t src = (size_t)part * P.part_stride + (size_t)row * P.row_stride + off;
+    const uint32_t key = score_key(P.cand_score[src]);
+    keys[c] = key;
+    idxs[c] = P.cand_idx[src];
+    mn = min(mn, key);
+    mx = max(mx, key);
+  }
+#pragma unroll
+  for (int off = 16; off; off >>= 1) {
+    mn = min(mn, __shfl_xor_sync(0xffffffffu, mn, off));
+    mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+  }
+  if (lane == 0) {
+    atomicMin(&ctrl->kmin, mn);
+    atomicMax(&ctrl->kmax, mx);
+  }
+  __syncthreads();
+  const uint32_t base = ctrl->kmin, maxkey = ctrl->kmax;
+  int shift = max(0, 32 - __clz((int)((maxkey - base) | 1u)) - 8);
+  uint32_t prefix = 0u, mask = 0u;
+  int remaining = min(k, n);
+#pragma unroll 1
+  for (;;) {
+    if (tid < 256) ctrl->hist[tid] = 0;
+    __syncthreads();
+    for (int i = tid; i < n; i += kMergeCtaThreads) {
+      const uint32_t rel = keys[i] - base;
+      if ((rel & mask) == prefix) atomicAdd(&ctrl->hist[(rel >> shift) & 255], 1);
+    }
+    __syncthreads();
+    if (tid < 32) {
+      int d, nr;
+      warp_find_digit(ctrl->hist, remaining, lane, d, nr);
+      if (lane == 0) {
+        ctrl->digit = d;
+        ctrl->remaining = nr;
+      }
+    }
+    __syncthreads();
+    prefix |= (uint32_t)ctrl->digit << shift;
+    mask = 0xffffffffu << shift;
+    remaining = ctrl->remaining;
+    if (shift == 0) break;
+    shift = max(0, shift - 8);
+  }
+  const uint32_t kth = base + prefix;
+  const int need_eq = remaining;
+  // winners: keys above the k-th, and need_eq of its ties
+  for (int i = tid; i < n; i += kMergeCtaThreads) {
+    const uint32_t key = keys[i];
+    bool keep = key > kth;
+    if (!keep && key == kth) keep = atomicAdd(&ctrl->eqc, 1) < need_eq;
+    if (keep) {
+      const int p = atomicAdd(&ctrl->wpos, 1);
+      if (p < k) {
+        wkey[p] = key;
+        widx[p] = idxs[i];
+      }
+    }
+  }
+  __syncthreads();
+  const int nw = min(ctrl->wpos, k);
+  if (P.m.sel_idx) {
+    const size_t dst = (size_t)row * P.m.list_pitch + P.m.list_off;
+    for (int e = tid; e < k; e += kMergeCtaThreads) {
+      P.m.sel_idx[dst + e] = (e < nw) ? widx[e] + P.m.index_base : -1;
+      if (P.m.sel_score) P.m.sel_score[dst + e] = (e < nw) ? key_score(wkey[e]) : -INFINITY;
+    }
+  }
+  if (P.m.out_mode == kOutNone) return;
+
+  const float smax = key_score(maxkey);
+  const __half* vb = P.m.v + (size_t)bq * P.m.v_batch_stride + (size_t)hkv * P.m.v_head_stride +
+                     (lane & 15) * 8;
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  float lsum = 0.f;
+  constexpr int UN = 8;
+  constexpr int kRows = 2 * (kMergeCtaThreads / 32);
+  for (int e0 = warp * 2 + (lane >> 4); e0 < nw; e0 += kRows * UN) {
+    uint4 vv[UN];
+    float w[UN];
+#pragma unroll
+    for (int u = 0; u < UN; ++u) {
+      const int e = e0 + kRows * u;
+      const int id = (e < nw) ? widx[e] : -1;
+      const int local = id - P.m.id_shift;
+      const bool mine = id >= P.m.own_lo && id < P.m.own_hi;
+      if (mine && (unsigned)local >= (unsigned)P.m.n_tokens) atomicOr(P.m.status, kStatusBadId);
+      if (mine && (unsigned)local < (unsigned)P.m.n_tokens) {
+        w[u] = fast_exp2((key_score(wkey[e]) - smax) * P.m.scale_log2e);
+        vv[u] = ldg128_nc(vb + (size_t)local * P.m.v_token_stride);
+      } else {
+        w[u] = 0.f;
+        vv[u] = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UN; ++u) {
+      const uint32_t ww[4] = {vv[u].x, vv[u].y, vv[u].z, vv[u].w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = h2f2(ww[i]);
+        acc[2 * i] = fmaf(w[u], f.x, acc[2 * i]);
+        acc[2 * i + 1] = fmaf(w[u], f.y, acc[2 * i + 1]);
+      }
+      lsum += w[u];
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], 16);
+  lsum += __shfl_xor_sync(0xffffffffu, lsum, 16);
+  if (lane < 16) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) red[warp * kHeadDim + lane * 8 + i] = acc[i];
+  }
+  if (lane == 0) ctrl->lred[warp] = lsum;
+  __syncthreads();
+  if (tid < kHeadDim) {
+    float o = 0.f, lt = 0.f;
+#pragma unroll
+    for (int w = 0; w < 32; ++w) {
+      o += red[w * kHeadDim + tid];
+      lt += ctrl->lred[w];
+    }
+    const float mscaled = smax * P.m.sm_scale;
+    if (P.m.out_mode == kOutFinal) {
+      P.m.out[(size_t)row * kHeadDim + tid] = __float2half_rn(o / lt);
+      if (P.m.out_lse && tid == 0) {
+        P.m.out_lse[(size_t)row * 2 + 0] = mscaled;
+        P.m.out_lse[(size_t)row * 2 + 1] = lt;
+      }
+    } else {
+      float* dstp = P.m.out_partial + (size_t)row * (kHeadDim + 2);
+      dstp[tid] = o;
+      if (tid == 0) {
+        dstp[kHeadDim] = lt;
+        dstp[kHeadDim + 1] = mscaled;
+      }
+    }
+  }
+}
+
+size_t merge_attend_cta_smem_bytes(int m_total, int topk) {
+  return (size_t)m_total * 8 + (size_t)topk * 8 + 32 * kHeadDim * 4 + sizeof(MergeCtaCtrl) + 64;
+}
+
+cudaError_t launch_merge_attend_cta(const MergeParams& P, int rows, size_t smem, cudaStream_t stream) {
+  auto kern = merge_attend_cta_kernel;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  kern<<<rows, kMergeCtaThreads, smem, stream>>>(P);
+  return cudaGetLastError();
+}
+
+}  // namespace ra

@@ -17,6 +17,9 @@ struct MergeParams {
 
 size_t merge_attend_smem_bytes(int per, int cap);
 cudaError_t launch_merge_attend(const MergeParams& P, int rows, size_t smem, cudaStream_t stream);
+// one CTA per row, for candidate lists that fit in its shared memory
+size_t merge_attend_cta_smem_bytes(int m_total, int topk);
+cudaError_t launch_merge_attend_cta(const MergeParams& P, int rows, size_t smem, cudaStream_t stream);
 // out[r, :] = sum_p w_p o_p / sum_p w_p l_p with w_p = exp(m_p - max m); partials are
 // [parts][rows][130] = 128 un-normalised sums, their weight l, their maximum m.
 cudaError_t launch_lse_combine(const float* partials, int parts, int rows, __half* out,
