@@ -61,11 +61,16 @@ constexpr size_t kSmemBudget = 227 * 1024;
 constexpr size_t kStatusBytes = 256;
 constexpr int kMaxSplit = 16;  // parts one head's context may be cut into
 
+// Candidate lists of nl queries x k keys that may not fit in shared memory next to the pipeline.
+constexpr int kMaxSpillGrid = 304;
+static bool lists_may_spill(int nl, int topk) { return (size_t)nl * topk * 16 > 96 * 1024; }
+
 struct Plan {
   bool ok = false;
   int hg = 0, nq = 0, bshare = 1, nq_valid = 1, qsplit = 1, nq_cta = 1;
   int cluster = 1, nsplit = 1, cap = 0, nstages = 0, per = 0, part_len = 0, grid = 0;
   int groups = 2, rendezvous = 4;
+  bool global_lists = false;  // candidate lists live in the workspace instead of shared memory
   size_t smem = 0;
   // second stage (only when parts > 1)
   int cluster2 = 1, cap2 = 0, per2 = 0;
@@ -185,6 +190,7 @@ Plan make_plan(const Shape& s) {
         // budget: the deepest pipeline whose lists still hold k keys plus the keys that may arrive
         // between two overflow checks
         int nstages = 0, cap = 0, cgroups = 0, rdv = 0;
+        bool glists = false;
         // one query per K row: scoring is latency-bound, two warp groups and deep rings help;
         // several queries per row (tensor-core scoring): one group and roomier lists win
         static const int kGeo1[4][2] = {{2, 6}, {2, 4}, {1, 3}, {1, 2}};
@@ -209,8 +215,15 @@ Plan make_plan(const Shape& s) {
           }
           if (nstages) break;
         }
+        // Lists that leave no room next to a 4-stage pipeline move to global memory: deep
+        // pipeline, capacity 4k, few cuts.
+        if (nq > 1 && lists_may_spill(nl, s.topk) && !getenv("RA_NO_GLOBAL_LISTS") &&
+            (!nstages || nstages < 4 || cap < s.topk + s.topk / 2) &&
+            groups * nsplit * cluster <= kMaxSpillGrid && (size_t)kMaxStages * kStageBytes >= scratch) {
+          nstages = kMaxStages; cgroups = 2; rdv = 4; cap = 4 * s.topk; glists = true;
+        }
         if (!nstages) continue;
-        const size_t smem = scan_smem_bytes(nl, cap, nstages);
+        const size_t smem = scan_smem_bytes(glists ? 0 : nl, cap, nstages);
         const int nclusters = groups * nsplit;
         const int active = scan_max_active_clusters(hg, nq, cluster, smem);
         if (active <= 0) continue;
@@ -232,7 +245,7 @@ Plan make_plan(const Shape& s) {
         pl.hg = hg; pl.nq = nq; pl.bshare = bshare; pl.nq_valid = nq_valid;
         pl.qsplit = qsplit; pl.nq_cta = nq_cta;
         pl.cluster = cluster; pl.nsplit = nsplit; pl.cap = cap; pl.nstages = nstages;
-        pl.groups = cgroups; pl.rendezvous = rdv;
+        pl.groups = cgroups; pl.rendezvous = rdv; pl.global_lists = glists;
         pl.per = per; pl.part_len = part_len; pl.grid = nclusters * cluster; pl.smem = smem;
         pl.cost = cost;
         if (two_stage && !plan_merge(s.segments * nsplit * s.topk,
@@ -305,7 +318,17 @@ size_t workspace_bound(const Shape& s) {
   int maxsplit = 1;
   if (s.segments == 1) maxsplit = std::max(1, std::min(kMaxSplit, seg_len / std::max(s.topk, 128)));
   size_t w = kStatusBytes + (size_t)s.batch * s.hq * s.segments * maxsplit * s.topk * 8;
-  return (w + 255) & ~size_t(255);
+  w = (w + 255) & ~size_t(255);
+  // global candidate lists are only used when several queries share a K row
+  const int group = s.hq / s.hkv;
+  int bshare = 1;
+  if (!s.per_batch && !(s.fused_ok & 2))
+    for (int b = 1; b <= s.batch; ++b)
+      if (s.batch % b == 0 && b * group <= 8) bshare = b;
+  const int nq_valid = bshare * group;
+  if (nq_valid > 1 && lists_may_spill(next_pow2(nq_valid), s.topk))
+    w += (size_t)kMaxSpillGrid * next_pow2(nq_valid) * 4 * s.topk * 8;
+  return w;
 }
 
 int encode_kmap(CUtensorMap* map, const ra_params* p, const Shape& s, int hg, bool swizzled,
@@ -374,10 +397,10 @@ int run(const ra_params* p, bool attend, const PartIds* ext = nullptr) {
   if (show)
     fprintf(stderr,
             "[topk_attn_b200] plan: hg=%d nq=%d(valid %d, qsplit %d) bshare=%d cluster=%d nsplit=%d cap=%d "
-            "stages=%d groups=%d rdv=%d per=%d part_len=%d grid=%d smem=%zu | merge: cluster=%d cap=%d smem=%zu | "
+            "stages=%d groups=%d rdv=%d glists=%d per=%d part_len=%d grid=%d smem=%zu | merge: cluster=%d cap=%d smem=%zu | "
             "model %.1f us\n",
             pl.hg, pl.nq, pl.nq_valid, pl.qsplit, pl.bshare, pl.cluster, pl.nsplit, pl.cap, pl.nstages, pl.groups,
-            pl.rendezvous, pl.per,
+            pl.rendezvous, (int)pl.global_lists, pl.per,
             pl.part_len, pl.grid, pl.smem, pl.cluster2, pl.cap2, pl.smem2, pl.cost * 1e6);
   if (p->workspace_bytes < workspace_bound(s)) {
     g_last_error = "workspace smaller than ra_workspace_bytes()";
@@ -401,6 +424,10 @@ int run(const ra_params* p, bool attend, const PartIds* ext = nullptr) {
   sp.status = status;
   sp.batch = s.batch; sp.hq = s.hq; sp.hkv = s.hkv; sp.n_tokens = real_tokens;
   sp.part_ids = ext ? ext->ids : nullptr;
+  if (pl.global_lists) {
+    const size_t cand_bytes = ((size_t)kStatusBytes + (size_t)s.batch * s.hq * parts * s.topk * 8 + 255) & ~size_t(255);
+    sp.list_ws = static_cast<unsigned char*>(p->workspace) + cand_bytes;
+  }
   sp.group = c.group; sp.bshare = pl.bshare; sp.nq_valid = pl.nq_valid;
   sp.qsplit = pl.qsplit; sp.nq_cta = pl.nq_cta;
   sp.kv_per_batch = s.per_batch;

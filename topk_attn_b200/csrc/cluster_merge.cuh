@@ -62,6 +62,25 @@ struct MergeArgs {
   float scale_log2e, sm_scale;
 };
 
+// Visit keys[0..n) with all threads of the CTA, eight independent loads in flight per thread (the
+// lists may live in global memory, where one load at a time would cost a full L2 round trip each).
+template <typename F>
+__device__ __forceinline__ void for_each_key(const uint32_t* keys, int n, int tid, int nthr, F f) {
+  for (int base = 0; base < n; base += nthr * 8) {
+    uint32_t kk[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int i = base + e * nthr + tid;
+      kk[e] = (i < n) ? keys[i] : 0u;
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int i = base + e * nthr + tid;
+      if (i < n) f(kk[e], i);
+    }
+  }
+}
+
 // One list's destination: batch row, query head, kv head, and whether it is in use.
 struct ListDest {
   int bq, hq, hkv;
@@ -155,10 +174,9 @@ __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char*
       const int n = min(cnt[l], cap);
       const uint32_t pre = ms->prefix[l];
       const uint32_t* kl = keys + (size_t)l * cap;
-      for (int i = tid; i < n; i += nthr) {
-        const uint32_t key = kl[i];
+      for_each_key(kl, n, tid, nthr, [&](uint32_t key, int) {
         if ((key & mask) == pre) atomicAdd(&ms->hist[buf][l][(key >> shift) & 255], 1);
-      }
+      });
     }
     cluster.sync();
     for (int item = tid; item < NL * 256; item += nthr) {
@@ -193,12 +211,11 @@ __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char*
     const uint32_t* kl = keys + (size_t)l * cap;
     int ngt = 0, neq = 0;
     uint32_t mx = 0u;
-    for (int i = tid; i < n; i += nthr) {
-      const uint32_t key = kl[i];
+    for_each_key(kl, n, tid, nthr, [&](uint32_t key, int) {
       ngt += key > kth;
       neq += key == kth;
       mx = max(mx, key);
-    }
+    });
 #pragma unroll
     for (int off = 16; off; off >>= 1) {
       ngt += __shfl_xor_sync(0xffffffffu, ngt, off);
@@ -256,8 +273,7 @@ __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char*
     const uint32_t* kl = keys + (size_t)l * cap;
     const int* il = idxs + (size_t)l * cap;
     const int off_gt = ms->off_gt[l], off_eq = ms->off_eq[l], take_eq = ms->take_eq[l];
-    for (int i = tid; i < n; i += nthr) {
-      const uint32_t key = kl[i];
+    for_each_key(kl, n, tid, nthr, [&](uint32_t key, int i) {
       int p = -1;
       if (key > kth) {
         p = off_gt + atomicAdd(&ms->ctr_gt[l], 1);
@@ -272,7 +288,7 @@ __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char*
         rk[(size_t)l * per + slot] = key;
         ri[(size_t)l * per + slot] = il[i];
       }
-    }
+    });
   }
   cluster.sync();
   }

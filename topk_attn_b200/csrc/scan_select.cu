@@ -55,7 +55,7 @@ __device__ void compact_list(uint32_t* keys, int* idxs, Ctrl* ctrl, int l, int k
   consumer_sync(nct);
   {
     uint32_t mx = 0u;
-    for (int i = tid; i < n; i += nct) mx = max(mx, keys[i]);
+    for_each_key(keys, n, tid, nct, [&](uint32_t key, int) { mx = max(mx, key); });
 #pragma unroll
     for (int off = 16; off; off >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, off));
     if (lane == 0) atomicMax(&ctrl->kmax, mx);
@@ -70,10 +70,10 @@ __device__ void compact_list(uint32_t* keys, int* idxs, Ctrl* ctrl, int l, int k
   for (;;) {
     if (tid < 256) ctrl->hist[tid] = 0;
     consumer_sync(nct);
-    for (int i = tid; i < n; i += nct) {
-      const uint32_t rel = keys[i] - base;
+    for_each_key(keys, n, tid, nct, [&](uint32_t key, int) {
+      const uint32_t rel = key - base;
       if ((rel & mask) == prefix) atomicAdd(&ctrl->hist[(rel >> shift) & 255], 1);
-    }
+    });
     consumer_sync(nct);
     if (tid < 32) {
       int d, nr;
@@ -183,9 +183,15 @@ scan_select_kernel(const __grid_constant__ ScanParams P) {
   const int cap = P.cap, k = P.m.topk;
 
   unsigned char* stages = smem;
-  uint32_t* keys = reinterpret_cast<uint32_t*>(smem + (size_t)P.nstages * kStageBytes);
+  // Candidate lists: in shared memory behind the stages, or — when k times the queries per row is
+  // too large for that — in this CTA's slice of the workspace (they are written rarely once the
+  // thresholds have risen and stay in L2).
+  unsigned char* after_stages = smem + (size_t)P.nstages * kStageBytes;
+  uint32_t* keys = P.list_ws ? reinterpret_cast<uint32_t*>(P.list_ws + (size_t)blockIdx.x * NL * cap * 8)
+                             : reinterpret_cast<uint32_t*>(after_stages);
   int* idxs = reinterpret_cast<int*>(keys + (size_t)NL * cap);
-  Ctrl* ctrl = reinterpret_cast<Ctrl*>(idxs + (size_t)NL * cap);
+  Ctrl* ctrl = P.list_ws ? reinterpret_cast<Ctrl*>(after_stages)
+                         : reinterpret_cast<Ctrl*>(idxs + (size_t)NL * cap);
 
   // which part of which (batch group, kv-head group) this cluster owns
   int cid = blockIdx.x / C;
@@ -362,7 +368,7 @@ scan_select_kernel(const __grid_constant__ ScanParams P) {
             const int tok = tok_lo + 8 * (jv >> 1);
             const uint32_t key = score_key(c[jv]);
             const bool pass = qi < P.nq_cta && q0 + qi < P.nq_valid && tok < part_hi &&
-                              key > thr2[jv & 1];
+                              key > thr2[jv & 1] && !(P.debug & 4);
             const unsigned bal = __ballot_sync(0xffffffffu, pass);
             if (bal) {
               const unsigned mym = bal & tmask;
@@ -446,7 +452,7 @@ scan_select_kernel(const __grid_constant__ ScanParams P) {
 #pragma unroll
         for (int v = 0; v < NV; ++v) {
           const uint32_t key = score_key(mine[v]);
-          const bool pass = my_valid[v] && in_range && key > my_thr[v];
+          const bool pass = my_valid[v] && in_range && key > my_thr[v] && !(P.debug & 4);
           const unsigned bal = __ballot_sync(0xffffffffu, pass);
           if (bal) {
             const unsigned mym = bal & grp_mask;
@@ -475,7 +481,7 @@ scan_select_kernel(const __grid_constant__ ScanParams P) {
         int need = 0;
 #pragma unroll
         for (int l = 0; l < NL; ++l)
-          if (ctrl->cnt[l] > cap - R * G * T) need |= 1 << l;
+          if (ctrl->cnt[l] > cap - R * G * T && !(P.debug & 8)) need |= 1 << l;
         consumer_sync(nct);
         if (need) {
 #pragma unroll
@@ -494,6 +500,7 @@ scan_select_kernel(const __grid_constant__ ScanParams P) {
   }
   __syncthreads();
 
+  if (P.debug & 16) return;  // tuning aid: time the scan without the merge
   // ------------------------------------------------------------------ cluster merge
   // The pipeline stages are free now and become the merge scratch.
   MergeArgs A = P.m;

@@ -9,6 +9,7 @@ struct ScanParams {
   MergeArgs m;               // selection / output arguments (list_off is set per cluster)
   const __half* q;           // [B,Hq,128]
   unsigned* status;          // one word, bit 0 = a bounded wait gave up
+  unsigned char* list_ws;    // optional: global memory for the candidate lists, grid * NL * cap * 8 bytes
   const int* part_ids;       // optional [B,Hq,nparts]: which slice of length part_len each part is
   int batch, hq, hkv, n_tokens;
   int group;                 // hq / hkv
