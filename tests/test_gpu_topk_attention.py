@@ -30,6 +30,9 @@ def test_config0_reference_cpu_case():
     (2, 16, 16, 40000, 2048, True),
     (1, 8, 1, 3000, 100, False),       # 8 query heads on one kv head
     (5, 6, 3, 2049, 33, False),        # batch that does not share evenly
+    (1, 8, 2, 40000, 2048, False),     # GQA with lists too large for shared memory (global lists)
+    (1, 8, 2, 70000, 4096, False),     # the same at k = 4096
+    (2, 4, 4, 30000, 3000, False),     # two batch rows on one cache, k not a power of two
 ])
 def test_random_shapes(B, Hq, Hkv, N, k, per_batch):
     q, k_, v = rand_case(B, Hq, Hkv, N, per_batch, seed=N + k)
@@ -176,3 +179,14 @@ def test_bad_arguments_are_rejected():
     p = capi.RaParams()
     assert capi.lib().ra_topk_attention(C.byref(p)) != capi.RA_OK
     assert capi.lib().ra_topk_attention(None) == capi.RA_ERR_INVALID_ARGUMENT
+
+
+def test_global_candidate_lists(monkeypatch, capfd):
+    """Four queries per K row with k = 4096 need more list space than shared memory has: the lists
+    move to the workspace.  The plan line proves that this path ran."""
+    monkeypatch.setenv("RA_FORCE_QSPLIT", "1")
+    monkeypatch.setenv("RA_VERBOSE", "1")
+    q, k, v = rand_case(1, 8, 2, 50048, False, seed=21)
+    check_topk_attention(q, k, v, 4096, sm_scale=0.7)
+    err = capfd.readouterr().err
+    assert "glists=1" in err, err[-400:]
