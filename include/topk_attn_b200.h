@@ -207,6 +207,18 @@ int ra_two_level_topk(const ra_two_level_params* p);
 size_t ra_two_level_workspace_bytes(int32_t batch, int32_t num_heads, int32_t num_centers,
                                     int32_t top_clusters, int32_t topk_per_cluster);
 
+/* The step of a decode loop that precedes the attention: store the new token's key and value
+ * rows (fp16 [caches, num_kv_heads, 128], caches = batch for per-sequence caches, else 1) at token
+ * `position` of the caches and, when `centers` (fp16 [num_kv_heads, num_centers, 128]) is given
+ * with a shared cache, fold the key into the running mean of centroid position / cluster_len.
+ * The reference assumes caches and centroids are given (gemv_topk.cu:218, baseline_1.py:44-68);
+ * this keeps them in the layouts its kernels read. */
+int ra_kv_append(void* k_cache, void* v_cache, const void* new_k, const void* new_v,
+                 int32_t caches, int32_t num_kv_heads, int32_t head_dim, int32_t position,
+                 int32_t capacity_tokens, int64_t kv_batch_stride, int64_t kv_token_stride,
+                 int64_t kv_head_stride, void* centers, int32_t num_centers, int32_t cluster_len,
+                 void* stream);
+
 /* Dense decode attention over the whole cache, split-KV with a log-sum-exp combine
  * ("flash decoding"): the dense baseline of the path and the reference's
  * baseline_attention_kernel (retrieval_attn/retrieval_attention.cu:51-168) /

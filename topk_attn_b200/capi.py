@@ -148,6 +148,8 @@ def _declare(l: C.CDLL) -> None:
         "ra_gathered_attention": (C.c_int, [C.POINTER(RaGatherParams)]),
         "ra_flash_decoding": (C.c_int, [C.POINTER(RaDenseParams)]),
         "ra_two_level_topk": (C.c_int, [C.POINTER(RaTwoLevelParams)]),
+        "ra_kv_append": (C.c_int, [vp, vp, vp, vp, i32, i32, i32, i32, i32, C.c_int64, C.c_int64,
+                                   C.c_int64, vp, i32, i32, vp]),
         "ra_two_level_workspace_bytes": (sz, [i32, i32, i32, i32, i32]),
         "ra_flash_workspace_bytes": (sz, [i32, i32, i32, i32, i32]),
         "ra_center_only_topk": (C.c_int, [C.POINTER(RaCenterParams)]),

@@ -791,6 +791,26 @@ int ra_two_level_topk(const ra_two_level_params* p) {
   return run(&fp, attend, &ext);
 }
 
+int ra_kv_append(void* k_cache, void* v_cache, const void* new_k, const void* new_v, int32_t caches,
+                 int32_t num_kv_heads, int32_t head_dim, int32_t position, int32_t capacity_tokens,
+                 int64_t kv_batch_stride, int64_t kv_token_stride, int64_t kv_head_stride,
+                 void* centers, int32_t num_centers, int32_t cluster_len, void* stream) {
+  if (!k_cache || !v_cache || !new_k || !new_v) return invalid("a required pointer is null");
+  if (head_dim != kHeadDim) return unsupported("head_dim must be 128");
+  if (caches < 1 || num_kv_heads < 1 || caches > 65535) return invalid("bad cache or head count");
+  if (position < 0 || position >= capacity_tokens) return invalid("position outside the cache");
+  if (caches > 1 && kv_batch_stride <= 0) return invalid("several caches need kv_batch_stride");
+  if (centers && (num_centers < 1 || cluster_len < 1)) return invalid("bad centroid geometry");
+  if (centers && caches > 1) return unsupported("centroid maintenance needs one shared cache");
+  cudaError_t e = launch_kv_append(static_cast<__half*>(k_cache), static_cast<__half*>(v_cache),
+                                   static_cast<const __half*>(new_k), static_cast<const __half*>(new_v),
+                                   static_cast<__half*>(centers), caches, num_kv_heads, position,
+                                   caches > 1 ? kv_batch_stride : 0, kv_token_stride, kv_head_stride,
+                                   num_centers, cluster_len, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "kv_append launch");
+  return RA_OK;
+}
+
 // Effective split geometry: split_len is a multiple of the 128-token tile.
 static void flash_geometry(int batch, int hkv, int n, int asked, int& splits, int& split_len) {
   int want = asked;

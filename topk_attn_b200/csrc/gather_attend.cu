@@ -374,6 +374,38 @@ cudaError_t launch_rank_sort(const float* score, const int* idx, int rows, int n
   return cudaGetLastError();
 }
 
+// Decode-loop step before the attention: write the new token's K and V rows into the caches at
+// `pos` and fold the key into the running mean of its cluster's centroid.
+__global__ void __launch_bounds__(kHeadDim)
+kv_append_kernel(__half* __restrict__ kc, __half* __restrict__ vc, const __half* __restrict__ nk,
+                 const __half* __restrict__ nv, __half* __restrict__ centers, int hkv, int pos,
+                 long long bstride, long long tstride, long long hstride, int num_centers,
+                 int cluster_len) {
+  const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+  const size_t src = ((size_t)b * hkv + h) * kHeadDim + d;
+  const size_t dst = (size_t)b * bstride + (size_t)pos * tstride + (size_t)h * hstride + d;
+  const __half kval = nk[src];
+  kc[dst] = kval;
+  vc[dst] = nv[src];
+  if (centers && b == 0) {
+    const int c = pos / cluster_len, seen = pos % cluster_len;
+    if (c < num_centers) {
+      __half* cp = centers + ((size_t)h * num_centers + c) * kHeadDim + d;
+      const float old = seen ? __half2float(*cp) : 0.f;
+      *cp = __float2half_rn((old * seen + __half2float(kval)) / (float)(seen + 1));
+    }
+  }
+}
+
+cudaError_t launch_kv_append(__half* kc, __half* vc, const __half* nk, const __half* nv,
+                             __half* centers, int batch, int hkv, int pos, long long bstride,
+                             long long tstride, long long hstride, int num_centers, int cluster_len,
+                             cudaStream_t stream) {
+  kv_append_kernel<<<dim3(hkv, batch), kHeadDim, 0, stream>>>(kc, vc, nk, nv, centers, hkv, pos, bstride,
+                                                           tstride, hstride, num_centers, cluster_len);
+  return cudaGetLastError();
+}
+
 size_t gather_attend_smem_bytes(int per, int cap, int n_src) {
   return ((sizeof(MergeScratch) + (size_t)per * 8 + 127) & ~size_t(127)) + (size_t)cap * 8 + 16 +
          (size_t)n_src * 4 + 128;

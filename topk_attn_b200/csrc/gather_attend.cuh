@@ -20,6 +20,10 @@ struct GatherParams {
 };
 
 size_t gather_attend_smem_bytes(int per, int cap, int n_src);
+cudaError_t launch_kv_append(__half* kc, __half* vc, const __half* nk, const __half* nv,
+                             __half* centers, int batch, int hkv, int pos, long long bstride,
+                             long long tstride, long long hstride, int num_centers, int cluster_len,
+                             cudaStream_t stream);
 size_t gather_flash_smem_bytes(int n_src);
 cudaError_t launch_gather_flash(const GatherParams& P, int rows, size_t smem, cudaStream_t stream);
 cudaError_t launch_rank_sort(const float* score, const int* idx, int rows, int n, int* out_idx,

@@ -238,6 +238,31 @@ def two_level_topk(q: Tensor, centers: Tensor, k: Tensor, top_clusters: int, clu
     return (cids, idx, sc) + ((out,) if out is not None else ())
 
 
+def kv_append(k_cache: Tensor, v_cache: Tensor, new_k: Tensor, new_v: Tensor, position: int,
+              centers: Optional[Tensor] = None, cluster_len: int = 0) -> None:
+    """In place: caches[.., position, :, :] = new rows ([Hkv,128] for a shared cache, [B,Hkv,128]
+    for per-sequence caches) and, with ``centers`` [Hkv,CSZ,128], the running mean of centroid
+    position // cluster_len absorbs the key."""
+    per_batch = k_cache.dim() == 4
+    caches = k_cache.size(0) if per_batch else 1
+    N, Hkv = k_cache.size(-3), k_cache.size(-2)
+    want = (caches, Hkv, 128) if per_batch else (Hkv, 128)
+    for t in (k_cache, v_cache, new_k, new_v):
+        if t.dtype != torch.float16 or not t.is_contiguous() or not t.is_cuda:
+            raise ValueError("caches and rows must be contiguous fp16 CUDA tensors")
+    if tuple(new_k.shape) != want or new_v.shape != new_k.shape or v_cache.shape != k_cache.shape:
+        raise ValueError(f"new rows must be {want}")
+    cptr, csz = (None, 0)
+    if centers is not None:
+        if centers.dtype != torch.float16 or not centers.is_contiguous() or centers.size(0) != Hkv:
+            raise ValueError("centers must be contiguous fp16 [Hkv,CSZ,128]")
+        cptr, csz = centers.data_ptr(), centers.size(1)
+    capi.check(capi.lib().ra_kv_append(
+        k_cache.data_ptr(), v_cache.data_ptr(), new_k.data_ptr(), new_v.data_ptr(), caches, Hkv, 128,
+        position, N, N * Hkv * 128 if per_batch else 0, Hkv * 128, 128, cptr, csz, cluster_len,
+        _stream_ptr()))
+
+
 def merge_attend(cand_scores: Tensor, cand_indices: Tensor, v: Tensor, topk: int, sm_scale: float,
                  own_base: int, partial: bool = True, return_indices: bool = False):
     """Select the global top-k out of ``cand_* [parts,B,Hq,topk]`` (global ids) and mix the V rows
