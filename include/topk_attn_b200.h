@@ -161,7 +161,8 @@ typedef struct ra_center_params {
   int32_t num_centers;      /* CSZ */
   int32_t cluster_len;      /* CLEN */
   int32_t top_clusters;     /* TOPC */
-  int32_t* out_cluster_ids; /* optional int32 [batch, num_heads, top_clusters], unordered */
+  int32_t* out_cluster_ids; /* optional int32 [batch, num_heads, top_clusters]; in descending
+                               score order when out_indices is given without out, else unordered */
   int32_t* out_indices;     /* optional int32 [batch, num_heads, top_clusters*cluster_len] */
   const void* k;            /* optional fp16 [num_tokens, num_heads, 128] (or per batch row) */
   const void* v;

@@ -1,0 +1,20 @@
+"""The stand-alone C++ driver: data generated like the reference's benchmark programs, selection
+on the GPU through the C ABI, verified against a double-precision CPU reference with the
+reference's own check (exact id sets per (head, cluster rank) slice, order ignored)."""
+import os
+import subprocess
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+BIN = os.path.join(ROOT, "topk_attn_b200", "bin", "ra_verify")
+
+
+@pytest.mark.parametrize("mode,heads", [("topk", "4"), ("center", "32")])
+def test_cli_verify(mode, heads):
+    assert os.path.exists(BIN), "build with python -m topk_attn_b200.build"
+    r = subprocess.run([BIN, mode, "--verify", heads, "--iters", "20"], capture_output=True,
+                       text=True, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "PASS" in r.stdout and "recall=100.0000%" in r.stdout

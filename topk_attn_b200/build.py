@@ -96,8 +96,22 @@ def build_extension(force: bool = False) -> str:
     return out
 
 
+def build_cli(force: bool = False) -> str:
+    """The stand-alone C++ driver (host code only, links the C-ABI library)."""
+    bindir = os.path.join(PKG, "bin")
+    os.makedirs(bindir, exist_ok=True)
+    src = os.path.join(CSRC, "cli", "ra_verify.cpp")
+    out = os.path.join(bindir, "ra_verify")
+    if force or _newer(out, [src, LIB]):
+        subprocess.check_call([NVCC, "-O2", "-std=c++17", "-x", "cu", *ARCH, "-I",
+                               os.path.join(ROOT, "include"), src, "-o", out, "-L", LIBDIR,
+                               "-ltopk_attn_b200", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../lib"])
+    return out
+
+
 def build_all(force: bool = False, verbose: bool = False) -> None:
     build_library(force, verbose)
+    build_cli(force)
     if os.path.exists(os.path.join(CSRC, "bind.cpp")):
         build_extension(force)
 

@@ -176,7 +176,7 @@ Plan make_plan(const Shape& s) {
     for (int cluster : {1, 2, 4, 8, 16}) {
       if (f_cluster && cluster != f_cluster) continue;
       for (int nsplit = 1; nsplit <= kMaxSplit; ++nsplit) {
-        if (nsplit > 1 && s.segments > 1) break;
+        if (nsplit > 1 && (s.segments > 1 || (s.fused_ok & 4))) break;
         if (f_nsplit && nsplit != f_nsplit) continue;
         int part_len = ceil_div(ceil_div(seg_len, nsplit), T) * T;
         if (nsplit > 1 && part_len < s.topk) break;           // every part must hold k keys
@@ -239,7 +239,13 @@ Plan make_plan(const Shape& s) {
         const double slab = (double)ceil_div(tiles, cluster) * T;
         const double cuts = slab > cap ? std::log(slab / cap) / std::log1p(room / s.topk) + 1.0 : 0.0;
         const bool two_stage = nsplit > 1 || s.segments > 1;
-        double cost = waves * (bytes_cta / rate + cuts * nl * 2e-6 + 6e-6 + 1.5e-6 * cluster) +
+        // clusters of up to 4 CTAs cost little; 8 and more are hard to co-schedule with 227 KiB of
+        // shared memory per CTA and measured about twice as slow
+        const double cluster_cost = cluster <= 4 ? 0.4e-6 * cluster : 4e-6 * cluster;
+        // until a list has filled once every key passes the threshold and is appended: about a
+        // microsecond per iteration instead of a fraction of one
+        const double warmup = 1e-6 * std::min(ceil_div(tiles, cluster), cap / T) / cgroups;
+        double cost = waves * (bytes_cta / rate + cuts * nl * 2e-6 + warmup + 6e-6 + cluster_cost) +
                       (two_stage ? 8e-6 : 0.0);
         Plan pl;
         pl.hg = hg; pl.nq = nq; pl.bshare = bshare; pl.nq_valid = nq_valid;
@@ -378,19 +384,25 @@ constexpr float kLog2e = 1.4426950408889634f;
 struct PartIds {
   const int* ids;
   int real_tokens;
+  // centroid retrieval in one launch: the winners are cluster ids, expanded in rank order
+  int expand_clen = 0;
+  int* expand_out = nullptr;
+  int* expand_ids = nullptr;
 };
 
 int run(const ra_params* p, bool attend, const PartIds* ext = nullptr) {
   Checked c;
   int st = check_params(p, attend, attend, c);
   if (st != RA_OK) return st;
-  if (!attend && !p->out_indices) return invalid("out_indices is required");
+  if (!attend && !p->out_indices && !(ext && ext->expand_out)) return invalid("out_indices is required");
   Shape s = c.shape;
-  s.fused_ok = ext ? 3 : 1;  // bit 1: every (row, head) scans its own parts — nothing is shared
-  const int real_tokens = ext ? ext->real_tokens : s.n;
+  // bit 1: every (row, head) scans its own parts — nothing is shared; bit 2: one part only (the
+  // scan kernel itself must produce the final winners)
+  s.fused_ok = 1 | ((ext && ext->ids) ? 2 : 0) | ((ext && ext->expand_out) ? 4 : 0);
+  const int real_tokens = (ext && ext->ids) ? ext->real_tokens : s.n;
   const Plan pl = make_plan(s);
   if (!pl.ok) return unsupported("no launch geometry fits these sizes");
-  static const bool verbose = getenv("RA_VERBOSE") != nullptr;
+  const bool verbose = getenv("RA_VERBOSE") != nullptr;
   static thread_local Shape last_shown = {};
   const bool show = verbose && ((last_shown < s) || (s < last_shown));
   if (show) last_shown = s;
@@ -424,6 +436,10 @@ int run(const ra_params* p, bool attend, const PartIds* ext = nullptr) {
   sp.status = status;
   sp.batch = s.batch; sp.hq = s.hq; sp.hkv = s.hkv; sp.n_tokens = real_tokens;
   sp.part_ids = ext ? ext->ids : nullptr;
+  if (ext && ext->expand_out) {
+    sp.m.expand_clen = ext->expand_clen; sp.m.expand_out = ext->expand_out;
+    sp.m.expand_ids = ext->expand_ids;
+  }
   if (pl.global_lists) {
     const size_t cand_bytes = ((size_t)kStatusBytes + (size_t)s.batch * s.hq * parts * s.topk * 8 + 255) & ~size_t(255);
     sp.list_ws = static_cast<unsigned char*>(p->workspace) + cand_bytes;
@@ -697,9 +713,18 @@ int ra_center_only_topk(const ra_center_params* p) {
   sp.kv_batch_stride = 0; sp.kv_token_stride = kHeadDim;
   sp.kv_head_stride = (int64_t)p->num_centers * kHeadDim;
   sp.topk = p->top_clusters; sp.num_segments = 1; sp.sm_scale = 1.f;
+  sp.workspace = p->workspace; sp.workspace_bytes = tail; sp.stream = p->stream;
+  if (!attend && p->out_indices) {
+    // selection + expansion in one launch: the scan kernel ranks its winners and writes the
+    // member tokens (and the cluster ids) in rank order
+    PartIds ext;
+    ext.ids = nullptr; ext.real_tokens = 0;
+    ext.expand_clen = p->cluster_len; ext.expand_out = p->out_indices;
+    ext.expand_ids = p->out_cluster_ids;
+    return run(&sp, false, &ext);
+  }
   sp.out_indices = p->out_cluster_ids ? p->out_cluster_ids : c_ids;
   sp.out_scores = c_score;
-  sp.workspace = p->workspace; sp.workspace_bytes = tail; sp.stream = p->stream;
   int st = ra_gemv_topk(&sp);
   if (st != RA_OK) return st;
   if (!attend && !p->out_indices) return RA_OK;

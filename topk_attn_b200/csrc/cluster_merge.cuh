@@ -50,6 +50,9 @@ struct MergeArgs {
   int id_shift;        // subtracted from an id to address V (ids of another shard's frame)
   int select_all;      // 1: every candidate is a winner (topk == number of candidates)
   int local_deal;      // with select_all: CTA c already holds winners c*per .. c*per+cnt-1, keep them
+  int expand_clen;     // > 0 with expand_out: winners are cluster ids, written out expanded
+  int* expand_out;     // [B,Hq,topk*expand_clen] member tokens id*clen+i, clusters in rank order
+  int* expand_ids;     // optional [B,Hq,topk]: the winners themselves in rank order
   int n_tokens;        // rows of V; ids outside [0, n_tokens) after the shift are never read
   unsigned* status;    // device status word (bit kStatusBadId is set on such an id)
   int* sel_idx;        // optional
@@ -291,6 +294,39 @@ __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char*
     });
   }
   cluster.sync();
+  }
+
+  // Centroid retrieval: the winners are cluster ids.  Rank every local winner among all k winners
+  // of its list (descending score, ties by id; the peers' winners are read through distributed
+  // shared memory) and write the clusters' member tokens in that order.
+  if (A.expand_clen > 0 && A.expand_out) {
+#pragma unroll 1
+    for (int l = 0; l < NL; ++l) {
+      const ListDest ld = dest(l);
+      if (!ld.valid) continue;
+      const int total = ms->total_sel[l];
+      const int n_l = max(0, min(per, total - crank * per));
+      const size_t rowi = (size_t)ld.bq * A.hq_total + ld.hq;
+      for (int e = warp; e < n_l; e += nwarps) {
+        const uint32_t mk = sel_key[(size_t)l * per + e];
+        const int mi = sel_idx[(size_t)l * per + e];
+        int rank = 0;
+        for (int j = lane; j < total; j += 32) {
+          const int c = j / per, slot = j - c * per;
+          const uint32_t ok = cluster.map_shared_rank(sel_key, c)[(size_t)l * per + slot];
+          const int oi = cluster.map_shared_rank(sel_idx, c)[(size_t)l * per + slot];
+          rank += (ok > mk) || (ok == mk && oi < mi);
+        }
+#pragma unroll
+        for (int off = 16; off; off >>= 1) rank += __shfl_xor_sync(0xffffffffu, rank, off);
+        if (A.expand_ids && lane == 0) A.expand_ids[rowi * k + rank] = mi + A.index_base;
+        int* dst = A.expand_out + (rowi * k + rank) * A.expand_clen;
+        const int t0 = mi * A.expand_clen;
+        for (int i = lane; i < A.expand_clen; i += 32) dst[i] = t0 + i;
+      }
+    }
+    cluster.sync();  // nobody leaves or reuses its winner slots while a peer still ranks against them
+    if (A.out_mode == kOutNone && !A.sel_idx) return;
   }
 
 #pragma unroll 1
