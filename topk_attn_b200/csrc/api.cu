@@ -215,10 +215,10 @@ Plan make_plan(const Shape& s) {
           }
           if (nstages) break;
         }
-        // Lists that leave no room next to a 4-stage pipeline move to global memory: deep
-        // pipeline, capacity 4k, few cuts.
+        // Several large lists per CTA leave too little room next to the pipeline: they move to
+        // global memory (deep pipeline, capacity 4k, few cuts).
         if (nq > 1 && lists_may_spill(nl, s.topk) && !getenv("RA_NO_GLOBAL_LISTS") &&
-            (!nstages || nstages < 4 || cap < s.topk + s.topk / 2) &&
+            
             groups * nsplit * cluster <= kMaxSpillGrid && (size_t)kMaxStages * kStageBytes >= scratch) {
           nstages = kMaxStages; cgroups = 2; rdv = 4; cap = 4 * s.topk; glists = true;
         }

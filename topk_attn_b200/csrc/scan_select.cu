@@ -170,8 +170,11 @@ scan_select_kernel(const __grid_constant__ ScanParams P) {
   const int G = P.groups;      // consumer warp groups (1 or 2), each on its own tile
   const int R = P.rendezvous;  // iterations between overflow checks
   const int nct = 256 * G;     // consumer threads
-  // a cut may leave up to half of the free room occupied
-  const int accept = P.m.topk + max(0, (P.cap - R * G * (kTileRows / HG) - P.m.topk) / 2);
+  // a cut may leave a little more than k candidates (an eighth of the free room, at least 256):
+  // one histogram pass over the actual key range usually gets that close, and the fewer
+  // candidates stay the longer it takes until the next cut
+  const int room = max(0, P.cap - R * G * (kTileRows / HG) - P.m.topk);
+  const int accept = P.m.topk + min(room / 2, max(256, room / 8));
   extern __shared__ __align__(128) unsigned char smem_raw[];
   unsigned char* smem =
       reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
