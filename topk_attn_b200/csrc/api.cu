@@ -63,6 +63,7 @@ constexpr int kMaxSplit = 16;  // parts one head's context may be cut into
 
 // Candidate lists of nl queries x k keys that may not fit in shared memory next to the pipeline.
 constexpr int kMaxSpillGrid = 304;
+constexpr int kSpillCapFactor = 4;  // capacity of a global candidate list in units of k
 static bool lists_may_spill(int nl, int topk) { return (size_t)nl * topk * 16 > 96 * 1024; }
 
 struct Plan {
@@ -220,7 +221,7 @@ Plan make_plan(const Shape& s) {
         if (nq > 1 && lists_may_spill(nl, s.topk) && !getenv("RA_NO_GLOBAL_LISTS") &&
             
             groups * nsplit * cluster <= kMaxSpillGrid && (size_t)kMaxStages * kStageBytes >= scratch) {
-          nstages = kMaxStages; cgroups = 2; rdv = 4; cap = 4 * s.topk; glists = true;
+          nstages = kMaxStages; cgroups = 2; rdv = 4; cap = kSpillCapFactor * s.topk; glists = true;
         }
         if (!nstages) continue;
         const size_t smem = scan_smem_bytes(glists ? 0 : nl, cap, nstages);
@@ -333,7 +334,7 @@ size_t workspace_bound(const Shape& s) {
       if (s.batch % b == 0 && b * group <= 8) bshare = b;
   const int nq_valid = bshare * group;
   if (nq_valid > 1 && lists_may_spill(next_pow2(nq_valid), s.topk))
-    w += (size_t)kMaxSpillGrid * next_pow2(nq_valid) * 4 * s.topk * 8;
+    w += (size_t)kMaxSpillGrid * next_pow2(nq_valid) * kSpillCapFactor * s.topk * 8;
   return w;
 }
 
