@@ -30,113 +30,142 @@ struct Ctrl {
   uint64_t empty[kMaxStages];
   int cnt[kMaxLists];
   uint32_t thr[kMaxLists];
-  int hist[256];
-  int digit, remaining, wpos, eqc, binpop;
-  uint32_t kmax;
+  int hist[kMaxLists][256];
+  // per-list state of a cut (see compact_lists)
+  uint32_t kmax[kMaxLists], base[kMaxLists], prefix[kMaxLists], mask[kMaxLists];
+  int shift[kMaxLists], remaining[kMaxLists], state[kMaxLists];
+  int wpos, eqc;
   int timeout;
 };
+enum CutState : int { kCutIdle = 0, kCutRun = 1, kCutInclusive = 2, kCutExact = 3 };
 
 // Barrier among the consumer warps only (the producer warp never joins it).
 __device__ __forceinline__ void consumer_sync(int nct) {
   asm volatile("bar.sync 1, %0;" ::"r"(nct) : "memory");
 }
 
-// Cut list `l` back: raise its threshold so that at least k and at most `accept` candidates stay.
-// All candidates lie above the old threshold, so the radix select works on (key - old threshold)
-// and starts at the highest bit that actually differs; it stops as soon as keeping the whole
-// current bin leaves few enough candidates, and only runs down to an exact k-th key (with ties
-// taken one by one) when it has to.  Called by all consumer threads.
-__device__ void compact_list(uint32_t* keys, int* idxs, Ctrl* ctrl, int l, int k, int cap,
-                             int accept, int tid, int nct) {
-  const int n = min(ctrl->cnt[l], cap);
-  const int lane = tid & 31;
-  const uint32_t base = ctrl->thr[l] + 1u;  // smallest key the list can hold
-  if (tid == 0) ctrl->kmax = 0u;
+// Cut back every list whose bit is set in `need`: raise its threshold so that at least k and at most
+// `accept` candidates stay.  All candidates of a list lie above its old threshold, so the radix
+// select works on (key - old threshold) and starts at the highest bit that actually differs; a
+// list is done as soon as keeping the whole current bin leaves few enough candidates, and only
+// runs down to an exact k-th key (ties taken one by one) when it has to.  The lists go through
+// the passes together (one set of barriers for all of them, their loads overlap); only the
+// in-place filtering is done list by list.  Called by all consumer threads.
+template <int NL>
+__device__ void compact_lists(uint32_t* keys, int* idxs, Ctrl* ctrl, int need, int k, int cap,
+                              int accept, int tid, int nct) {
+  const int lane = tid & 31, warp = tid >> 5, nwarps = nct >> 5;
+  if (tid < NL) ctrl->kmax[tid] = 0u;
   consumer_sync(nct);
-  {
+#pragma unroll
+  for (int l = 0; l < NL; ++l) {
+    if (!((need >> l) & 1)) continue;
+    const int n = min(ctrl->cnt[l], cap);
     uint32_t mx = 0u;
-    for_each_key(keys, n, tid, nct, [&](uint32_t key, int) { mx = max(mx, key); });
+    for_each_key(keys + (size_t)l * cap, n, tid, nct, [&](uint32_t key, int) { mx = max(mx, key); });
 #pragma unroll
     for (int off = 16; off; off >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, off));
-    if (lane == 0) atomicMax(&ctrl->kmax, mx);
+    if (lane == 0) atomicMax(&ctrl->kmax[l], mx);
   }
   consumer_sync(nct);
-  const uint32_t range = ctrl->kmax - base;
-  int shift = max(0, 32 - __clz((int)(range | 1u)) - 8);
-  uint32_t prefix = 0u, mask = 0u;
-  int remaining = k;
-  bool inclusive = false;
+  if (tid < NL) {
+    const int l = tid;
+    const bool on = (need >> l) & 1;
+    const uint32_t base = ctrl->thr[l] + 1u;  // smallest key the list can hold
+    const uint32_t range = ctrl->kmax[l] - base;
+    ctrl->base[l] = base;
+    ctrl->shift[l] = max(0, 32 - __clz((int)(range | 1u)) - 8);
+    ctrl->prefix[l] = 0u;
+    ctrl->mask[l] = 0u;
+    ctrl->remaining[l] = k;
+    ctrl->state[l] = on ? kCutRun : kCutIdle;
+  }
+  consumer_sync(nct);
 #pragma unroll 1
   for (;;) {
-    if (tid < 256) ctrl->hist[tid] = 0;
+    for (int i = tid; i < NL * 256; i += nct) (&ctrl->hist[0][0])[i] = 0;
     consumer_sync(nct);
-    for_each_key(keys, n, tid, nct, [&](uint32_t key, int) {
-      const uint32_t rel = key - base;
-      if ((rel & mask) == prefix) atomicAdd(&ctrl->hist[(rel >> shift) & 255], 1);
-    });
+    bool any = false;
+#pragma unroll
+    for (int l = 0; l < NL; ++l) {
+      if (ctrl->state[l] != kCutRun) continue;
+      any = true;
+      const int n = min(ctrl->cnt[l], cap);
+      const uint32_t base = ctrl->base[l], prefix = ctrl->prefix[l], mask = ctrl->mask[l];
+      const int shift = ctrl->shift[l];
+      for_each_key(keys + (size_t)l * cap, n, tid, nct, [&](uint32_t key, int) {
+        const uint32_t rel = key - base;
+        if ((rel & mask) == prefix) atomicAdd(&ctrl->hist[l][(rel >> shift) & 255], 1);
+      });
+    }
+    if (!any) break;  // the states were settled before the barrier above: same for every thread
     consumer_sync(nct);
-    if (tid < 32) {
+    for (int l = warp; l < NL; l += nwarps) {
+      if (ctrl->state[l] != kCutRun) continue;
       int d, nr;
-      warp_find_digit(ctrl->hist, remaining, lane, d, nr);
+      warp_find_digit(ctrl->hist[l], ctrl->remaining[l], lane, d, nr);
       if (lane == 0) {
-        ctrl->digit = d;
-        ctrl->remaining = nr;
-        ctrl->binpop = ctrl->hist[d];
+        const int shift = ctrl->shift[l];
+        ctrl->prefix[l] |= (uint32_t)d << shift;
+        ctrl->mask[l] = 0xffffffffu << shift;
+        ctrl->remaining[l] = nr;
+        const int kept = (k - nr) + ctrl->hist[l][d];  // candidates at or above the bin's start
+        if (kept <= accept) ctrl->state[l] = kCutInclusive;
+        else if (shift == 0) ctrl->state[l] = kCutExact;
+        else ctrl->shift[l] = max(0, shift - 8);
       }
     }
     consumer_sync(nct);
-    prefix |= (uint32_t)ctrl->digit << shift;
-    mask = 0xffffffffu << shift;
-    remaining = ctrl->remaining;
-    // candidates at or above the start of the chosen bin
-    const int kept = (k - remaining) + ctrl->binpop;
-    if (kept <= accept) {
-      inclusive = true;
-      break;
-    }
-    if (shift == 0) break;
-    shift = max(0, shift - 8);
   }
-  // inclusive: keep every key >= base + prefix; exact: keep keys above the k-th and need_eq ties
-  const uint32_t kth = base + prefix;
-  const int need_eq = remaining;
-  if (tid == 0) {
-    ctrl->wpos = 0;
-    ctrl->eqc = 0;
-  }
-  consumer_sync(nct);
-  constexpr int E = 8;
+  // inclusive: keep every key >= base + prefix; exact: keys above the k-th and `remaining` ties
 #pragma unroll 1
-  for (int cb = 0; cb < n; cb += nct * E) {
-    uint32_t kk[E];
-    int ii[E];
-#pragma unroll
-    for (int e = 0; e < E; ++e) {
-      const int i = cb + e * nct + tid;
-      kk[e] = (i < n) ? keys[i] : 0u;
-      ii[e] = (i < n) ? idxs[i] : 0;
+  for (int l = 0; l < NL; ++l) {
+    const int st = ctrl->state[l];
+    if (st != kCutInclusive && st != kCutExact) continue;  // uniform
+    const bool inclusive = st == kCutInclusive;
+    const uint32_t kth = ctrl->base[l] + ctrl->prefix[l];
+    const int need_eq = ctrl->remaining[l];
+    const int n = min(ctrl->cnt[l], cap);
+    uint32_t* kl = keys + (size_t)l * cap;
+    int* il = idxs + (size_t)l * cap;
+    if (tid == 0) {
+      ctrl->wpos = 0;
+      ctrl->eqc = 0;
     }
     consumer_sync(nct);
+    constexpr int E = 8;
+#pragma unroll 1
+    for (int cb = 0; cb < n; cb += nct * E) {
+      uint32_t kk[E];
+      int ii[E];
 #pragma unroll
-    for (int e = 0; e < E; ++e) {
-      const int i = cb + e * nct + tid;
-      if (i < n) {
-        bool keep = inclusive ? (kk[e] >= kth) : (kk[e] > kth);
-        if (!inclusive && kk[e] == kth) keep = atomicAdd(&ctrl->eqc, 1) < need_eq;
-        if (keep) {
-          const int p = atomicAdd(&ctrl->wpos, 1);
-          keys[p] = kk[e];
-          idxs[p] = ii[e];
+      for (int e = 0; e < E; ++e) {
+        const int i = cb + e * nct + tid;
+        kk[e] = (i < n) ? kl[i] : 0u;
+        ii[e] = (i < n) ? il[i] : 0;
+      }
+      consumer_sync(nct);
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        const int i = cb + e * nct + tid;
+        if (i < n) {
+          bool keep = inclusive ? (kk[e] >= kth) : (kk[e] > kth);
+          if (!inclusive && kk[e] == kth) keep = atomicAdd(&ctrl->eqc, 1) < need_eq;
+          if (keep) {
+            const int p = atomicAdd(&ctrl->wpos, 1);
+            kl[p] = kk[e];
+            il[p] = ii[e];
+          }
         }
       }
+      consumer_sync(nct);
+    }
+    if (tid == 0) {
+      ctrl->cnt[l] = ctrl->wpos;
+      ctrl->thr[l] = inclusive ? kth - 1u : kth;
     }
     consumer_sync(nct);
   }
-  if (tid == 0) {
-    ctrl->cnt[l] = ctrl->wpos;
-    ctrl->thr[l] = inclusive ? kth - 1u : kth;
-  }
-  consumer_sync(nct);
 }
 
 // acc0 += k.lo * q.lo, acc1 += k.hi * q.hi for one packed pair of fp16 values; products of
@@ -487,10 +516,7 @@ scan_select_kernel(const __grid_constant__ ScanParams P) {
           if (ctrl->cnt[l] > cap - R * G * T && !(P.debug & 8)) need |= 1 << l;
         consumer_sync(nct);
         if (need) {
-#pragma unroll
-          for (int l = 0; l < NL; ++l)
-            if ((need >> l) & 1)
-              compact_list(keys + (size_t)l * cap, idxs + (size_t)l * cap, ctrl, l, k, cap, accept, tid, nct);
+          compact_lists<NL>(keys, idxs, ctrl, need, k, cap, accept, tid, nct);
 #pragma unroll
           for (int v = 0; v < NV; ++v) my_thr[v] = ctrl->thr[my_list[v]];
           if constexpr (MODE == 2) {
