@@ -228,6 +228,39 @@ def run_center_published(args):
         "gpu_launches": args.steps}))
 
 
+def phase_breakdown(step, steps):
+    """Where the time of the fused kernel goes, in the manner of the reference's split profile
+    (gemv_profile_split.cu: GEMV alone, then with the selection): the same launch repeated with
+    parts of the kernel switched off through the library's RA_DEBUG_FLAGS tuning aid (1 = no
+    scoring, 4 = no list appends, 8 = no list cuts, 16 = return before select + softmax.V).  The
+    outputs of those launches are meaningless; only their durations are used."""
+    def timed(flags):
+        if flags:
+            os.environ["RA_DEBUG_FLAGS"] = str(flags)
+        else:
+            os.environ.pop("RA_DEBUG_FLAGS", None)
+        for _ in range(3):
+            step()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / steps
+    try:
+        stream = timed(1 | 4 | 8 | 16)
+        score = timed(4 | 8 | 16)
+        select = timed(16)
+    finally:
+        os.environ.pop("RA_DEBUG_FLAGS", None)
+    full = timed(0)
+    return {"stream_only_us": stream, "stream_score_us": score, "stream_score_select_us": select,
+            "full_step_us": full, "attend_us": full - select,
+            "note": "each figure is a whole launch with the later parts switched off"}
+
+
 def run_ours(args):
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback")
@@ -269,17 +302,20 @@ def run_ours(args):
     ops.check_status(dev)
     torch.cuda.synchronize()
     small = w.algorithmic_bytes() <= (256 << 20)     # would sit in the 126 MB L2
-    launches_per_step = 1
+    from topk_attn_b200 import capi
+    count = capi.lib().ra_launch_count                # kernels launched by the library so far
     sampler = ClockSampler(physical_gpu_index(local))
     if not small:
         sampler.start()
         evs = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
         torch.cuda.synchronize()
+        c0 = count()
         evs[0].record()
         for i in range(args.steps):
             step()
             evs[i + 1].record()
         torch.cuda.synchronize()
+        gpu_launches = count() - c0
         clocks = sampler.stop()
         total_ms = evs[0].elapsed_time(evs[-1])
         per_ms = total_ms / args.steps
@@ -295,8 +331,10 @@ def run_ours(args):
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
             step()
+            c0 = count()
             with torch.cuda.graph(graph, stream=side):
                 step()
+            gpu_launches = (count() - c0) * args.steps   # every replay runs the captured launches
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
         sampler.start()
@@ -312,7 +350,6 @@ def run_ours(args):
         launch_ms = sorted(a.elapsed_time(bq) for a, bq in pairs)
         per_ms = sum(launch_ms) / len(launch_ms)
         l2_note = "l2_flushed_between_steps (512 MB overwrite), step replayed from a CUDA graph"
-        launches_per_step = 2 if kind != "topk" else 1
     ops.check_status(dev)
 
     # end to end: query from pinned host memory, output read back, every step
@@ -364,9 +401,15 @@ def run_ours(args):
                          "cores": torch.get_num_threads(), "kind": "port", "sample": what},
         "e2e": {"value": tokens / e2e_s, "unit": "tokens/s", "us_per_step": e2e_s * 1e6,
                 "h2d_bytes_per_step": q_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 2},
-        "gpu_launches": args.steps * launches_per_step,
+        "gpu_launches": gpu_launches,
         "clocks": clocks,
     }
+    if args.phases:
+        if kind != "topk" or small or gpu_launches != args.steps:
+            line["phases"] = "only for a step that is one launch of the fused kernel"
+        else:
+            line["phases"] = phase_breakdown(step, min(args.steps, 50))
+            ops.check_status(dev)
     traffic_file = os.path.join(ROOT, "profiles", "traffic.json")
     if os.path.exists(traffic_file):
         try:
@@ -384,6 +427,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling)")
+    ap.add_argument("--phases", action="store_true",
+                    help="also time the fused kernel with selection / attention switched off")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

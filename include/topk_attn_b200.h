@@ -68,6 +68,10 @@ const char* ra_strerror(int status);
 int ra_version(void);
 /* Text of the last failing CUDA call made by this library on the calling thread. */
 const char* ra_last_cuda_error(void);
+/* Kernels this library has launched since it was loaded, over all threads (a host-side counter
+ * bumped beside every launch; no counterpart in the reference).  Benchmarks read it before and
+ * after a timed region to state how many launches the region held. */
+unsigned long long ra_launch_count(void);
 
 /* Scratch needed by ra_topk_attention / ra_gemv_topk for these operands (the largest any
  * internal plan may use).  Replaces the per-call cudaMalloc of the reference's host runners

@@ -137,6 +137,7 @@ def _declare(l: C.CDLL) -> None:
         "ra_strerror": (C.c_char_p, [C.c_int]),
         "ra_version": (C.c_int, []),
         "ra_last_cuda_error": (C.c_char_p, []),
+        "ra_launch_count": (C.c_ulonglong, []),
         "ra_workspace_bytes": (sz, [P]),
         "ra_topk_attention": (C.c_int, [P]),
         "ra_gemv_topk": (C.c_int, [P]),

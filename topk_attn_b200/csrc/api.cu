@@ -18,6 +18,7 @@
 
 namespace ra {
 int scan_max_active_clusters(int hg, int nq, int cluster, size_t smem);
+std::atomic<unsigned long long> g_launch_count{0};
 }
 
 namespace {
@@ -525,6 +526,8 @@ const char* ra_strerror(int status) {
 int ra_version(void) { return 100; }
 
 const char* ra_last_cuda_error(void) { return g_last_error.c_str(); }
+
+unsigned long long ra_launch_count(void) { return ra::g_launch_count.load(std::memory_order_relaxed); }
 
 size_t ra_workspace_bytes(const ra_params* p) {
   Checked c;

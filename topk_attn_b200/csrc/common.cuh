@@ -6,6 +6,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 namespace ra {
 
 constexpr int kHeadDim = 128;          // the reference's only head size
@@ -158,5 +160,9 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+
+// host-side count of kernel launches (read through ra_launch_count)
+extern std::atomic<unsigned long long> g_launch_count;
+inline void note_launch() { g_launch_count.fetch_add(1, std::memory_order_relaxed); }
 
 }  // namespace ra

@@ -242,6 +242,7 @@ cudaError_t launch_flash_decode(const FlashParams& P, int grid, size_t smem, cud
   auto kern = flash_decode_kernel;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
+  note_launch();
   kern<<<grid, kFdThreads, smem, stream>>>(P);
   return cudaGetLastError();
 }

@@ -341,6 +341,7 @@ cudaError_t launch_gather_flash(const GatherParams& P, int rows, size_t smem, cu
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  note_launch();
   return cudaLaunchKernelEx(&cfg, kern, P);
 }
 
@@ -370,6 +371,7 @@ rank_sort_kernel(const float* __restrict__ score, const int* __restrict__ idx, i
 
 cudaError_t launch_rank_sort(const float* score, const int* idx, int rows, int n, int* out_idx,
                              float* out_score, cudaStream_t stream) {
+  note_launch();
   rank_sort_kernel<<<rows, 256, (size_t)n * 8, stream>>>(score, idx, n, out_idx, out_score);
   return cudaGetLastError();
 }
@@ -401,6 +403,7 @@ cudaError_t launch_kv_append(__half* kc, __half* vc, const __half* nk, const __h
                              __half* centers, int batch, int hkv, int pos, long long bstride,
                              long long tstride, long long hstride, int num_centers, int cluster_len,
                              cudaStream_t stream) {
+  note_launch();
   kv_append_kernel<<<dim3(hkv, batch), kHeadDim, 0, stream>>>(kc, vc, nk, nv, centers, hkv, pos, bstride,
                                                            tstride, hstride, num_centers, cluster_len);
   return cudaGetLastError();
@@ -427,6 +430,7 @@ cudaError_t launch_gather_attend(const GatherParams& P, int rows, size_t smem, c
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  note_launch();
   return cudaLaunchKernelEx(&cfg, kern, P);
 }
 

@@ -76,6 +76,7 @@ cudaError_t launch_merge_attend(const MergeParams& P, int rows, size_t smem, cud
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  note_launch();
   return cudaLaunchKernelEx(&cfg, kern, P);
 }
 
@@ -98,6 +99,7 @@ lse_combine_kernel(const float* __restrict__ partials, int parts, int rows, __ha
 
 cudaError_t launch_lse_combine(const float* partials, int parts, int rows, __half* out,
                                cudaStream_t stream) {
+  note_launch();
   lse_combine_kernel<<<rows, kHeadDim, 0, stream>>>(partials, parts, rows, out);
   return cudaGetLastError();
 }
@@ -297,6 +299,7 @@ cudaError_t launch_merge_attend_cta(const MergeParams& P, int rows, size_t smem,
   auto kern = merge_attend_cta_kernel;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
+  note_launch();
   kern<<<rows, kMergeCtaThreads, smem, stream>>>(P);
   return cudaGetLastError();
 }

@@ -577,6 +577,7 @@ static cudaError_t launch_one(const ScanParams& P, int grid, size_t smem, cudaSt
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  note_launch();
   return cudaLaunchKernelEx(&cfg, kern, P);
 }
 

@@ -144,6 +144,8 @@ def bench(args, rank: int, local: int, world: int, ClockSampler, measured_peak_g
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sel = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
            for _ in range(args.steps)]
+    from . import capi
+    launches0 = capi.lib().ra_launch_count()
     e0.record()
     for i in range(args.steps):
         # the scan is the dominant kernel: time it separately inside the step
@@ -157,6 +159,7 @@ def bench(args, rank: int, local: int, world: int, ClockSampler, measured_peak_g
         _all_gather(partials, part)
         op.backend.combine(partials)
     e1.record()
+    launches = capi.lib().ra_launch_count() - launches0      # this rank's, in the timed region
     torch.cuda.synchronize()
     dist.barrier()
     clocks = sampler.stop()
@@ -210,7 +213,7 @@ def bench(args, rank: int, local: int, world: int, ClockSampler, measured_peak_g
             "e2e": {"value": tokens / e2e_s, "unit": "tokens/s", "us_per_step": e2e_s * 1e6,
                     "h2d_bytes_per_step": q_host.numel() * 2,
                     "d2h_bytes_per_step": out_host.numel() * 2},
-            "gpu_launches": args.steps * 3 * world,
+            "gpu_launches": launches * world,
             "clocks": clocks,
         }
         print(json.dumps(line))
