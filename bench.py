@@ -203,29 +203,39 @@ def run_center_published(args):
     graph = torch.cuda.CUDAGraph()
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
+    # one graph holds `inner` back-to-back steps: replaying a one-launch graph from Python takes
+    # longer than the launch itself, and the reference's loop is back-to-back launches from C++
+    inner = 50
+    replays = max(1, args.steps // inner)
+    from topk_attn_b200 import capi
+    c0 = capi.lib().ra_launch_count()
     with torch.cuda.stream(side):
         with torch.cuda.graph(graph, stream=side):
-            ops.center_only_topk(q, centers, 64, 128)
+            for _ in range(inner):
+                ops.center_only_topk(q, centers, 64, 128)
+    launches_per_step = (capi.lib().ra_launch_count() - c0) // inner
     torch.cuda.current_stream().wait_stream(side)
     torch.cuda.synchronize()
+    graph.replay()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
+    for _ in range(replays):
         graph.replay()
     e1.record()
     torch.cuda.synchronize()
-    us = e0.elapsed_time(e1) * 1e3 / args.steps
+    steps = replays * inner
+    us = e0.elapsed_time(e1) * 1e3 / steps
     published = 16.401
     print(json.dumps({
         "metric": "centroid_only_selection_latency", "value": us, "unit": "us", "n_gpus": 1,
-        "steps": args.steps, "warmup": max(args.warmup, 10), "ms_per_step": us * 1e-3,
+        "steps": steps, "warmup": max(args.warmup, 10), "ms_per_step": us * 1e-3,
         "higher_is_better": False, "scaling": "weak", "vs_baseline": us / published,
         "dtype": "f16 inputs, f32 accumulate", "data": "synthetic",
         "config": {"workload": "center_pub", "heads": 32, "head_dim": 128, "centroids": 1024,
                    "top_clusters": 64, "cluster_len": 128, "l2": "warm, as in the reference's loop",
                    "published_us": {"sm_90 cluster": 16.401, "sm_120a cluster": 18.446,
                                     "sm_120a single CTA": 20.561, "sm_90 single CTA": 24.594}},
-        "gpu_launches": args.steps}))
+        "gpu_launches": steps * launches_per_step}))
 
 
 def phase_breakdown(step, steps):

@@ -64,6 +64,65 @@ def test_center_only_selection_without_attention():
     assert torch.equal(tids.cpu().long().sort(-1).values, ids_ref.sort(-1).values)
 
 
+def expected_rank_order(cs, topc):
+    """ids by descending score, ties by ascending id: the order both centroid paths promise"""
+    csz = cs.size(-1)
+    order = torch.argsort(cs.double() * 1.0, dim=-1, descending=True, stable=True)
+    return order[..., :topc]
+
+
+@pytest.mark.parametrize("csz,clen,topc,heads,batch", [
+    (37, 3, 5, 3, 2),          # odd everything, members not a multiple of four
+    (1000, 6, 1000, 2, 1),     # keep all, slices that do not divide
+    (4096, 4, 300, 2, 2),      # eight CTAs per row
+    (8192, 2, 1024, 1, 1),     # largest table the shared-memory kernel takes
+    (9000, 2, 16, 2, 1),       # beyond it: the streaming kernel takes over
+])
+def test_center_selection_rank_order_exact_on_exact_scores(csz, clen, topc, heads, batch):
+    """Centroids and queries with small integer entries: every score is exact in fp16 x fp32, so
+    the expected order is unambiguous, and ties are plentiful."""
+    from topk_attn_b200 import ops
+    g = torch.Generator().manual_seed(csz + topc)
+    q = torch.randint(-2, 3, (batch, heads, 128), generator=g).half()
+    centers = torch.randint(-2, 3, (heads, csz, 128), generator=g).half()
+    cids, tids = ops.center_only_topk(q.to(DEV), centers.to(DEV), topc, clen)
+    ops.check_status(torch.device(DEV))
+    cs = torch.einsum("bhd,hcd->bhc", q.float(), centers.float())
+    want = expected_rank_order(cs, topc)
+    t = tids.cpu().long().view(batch, heads, topc, clen)
+    assert torch.equal(t - t[..., :1], torch.arange(clen).expand_as(t))
+    got_scores = torch.gather(cs, -1, t[..., 0] // clen)
+    want_scores = torch.gather(cs, -1, want)
+    assert torch.equal(got_scores, want_scores)               # same scores rank by rank
+    assert torch.equal(cids.cpu().long().sort(-1).values, (t[..., 0] // clen).sort(-1).values)
+    if csz <= 8192:
+        assert torch.equal(t[..., 0] // clen, want)           # ties broken by the lower id
+        assert torch.equal(cids.cpu().long(), want)
+
+
+def test_center_selection_all_scores_equal():
+    from topk_attn_b200 import ops
+    q = torch.zeros(1, 4, 128).half()
+    centers = torch.randn(4, 700, 128).half()
+    cids, tids = ops.center_only_topk(q.to(DEV), centers.to(DEV), 9, 4)
+    ops.check_status(torch.device(DEV))
+    assert torch.equal(cids.cpu().long(), torch.arange(9).expand(1, 4, 9))
+    assert torch.equal(tids.cpu().long(), torch.arange(36).expand(1, 4, 36))
+
+
+def test_center_selection_paths_agree(monkeypatch):
+    """The shared-memory kernel and the streaming kernel give the same clusters."""
+    from topk_attn_b200 import ops
+    w = W.centroid_retrieval(csz=1024, clen=128, topc=64, heads=32)
+    q, c = w.q.to(DEV), w.centers.to(DEV)
+    a_c, a_t = ops.center_only_topk(q, c, 64, 128)
+    monkeypatch.setenv("RA_NO_CENTER_SELECT", "1")
+    b_c, b_t = ops.center_only_topk(q, c, 64, 128)
+    ops.check_status(torch.device(DEV))
+    assert torch.equal(a_c.sort(-1).values, b_c.sort(-1).values)
+    assert torch.equal(a_t, b_t)
+
+
 @pytest.mark.parametrize("B,Hq,Hkv,N,S,per_batch,shared_idx", [
     (1, 32, 32, 40960, 2560, False, True),     # flash_decoding.cu:32-37 shape
     (2, 8, 2, 5000, 777, True, False),

@@ -11,6 +11,7 @@
 #include <string>
 #include <tuple>
 
+#include "center_select.cuh"
 #include "flash_decode.cuh"
 #include "gather_attend.cuh"
 #include "merge_attend.cuh"
@@ -685,6 +686,30 @@ size_t ra_center_workspace_bytes(int32_t batch, int32_t num_heads, int32_t num_c
   return workspace_bound(s) + (size_t)batch * num_heads * top_clusters * 8 + 256;
 }
 
+// Centroid tables whose per-head scores fit in shared memory: scores, exact top-C in rank order
+// and (optionally) the member ids of the winners in one launch.
+static int center_select(const void* q, const void* centers, int batch, int heads, int csz, int topc,
+                         int clen, int* ids, float* scores, int* members, cudaStream_t stream) {
+  CenterSelectParams cp;
+  memset(&cp, 0, sizeof cp);
+  cp.q = static_cast<const __half*>(q);
+  cp.centers = static_cast<const __half*>(centers);
+  cp.heads = heads; cp.csz = csz; cp.topc = topc; cp.clen = clen;
+  int cluster = 1;
+  while (cluster < kCenterMaxCluster && csz > 256 * cluster) cluster <<= 1;
+  if (const char* f = getenv("RA_CENTER_CLUSTER")) {   // tuning aid
+    const int c = atoi(f);
+    if (c == 1 || c == 2 || c == 4 || c == 8) cluster = c;
+  }
+  cp.cluster = cluster;
+  cp.per = (ceil_div(csz, cluster) + 3) & ~3;
+  cp.out_cluster_ids = ids; cp.out_scores = scores; cp.out_members = members;
+  cp.vec_members = members && clen % 4 == 0 && (reinterpret_cast<uintptr_t>(members) & 15u) == 0;
+  cudaError_t e = launch_center_select(cp, batch * heads, stream);
+  if (e != cudaSuccess) return cuda_fail(e, "center_select launch");
+  return RA_OK;
+}
+
 int ra_center_only_topk(const ra_center_params* p) {
   if (!p) return invalid("params is null");
   if (!p->q || !p->centers) return invalid("q or centers is null");
@@ -718,6 +743,21 @@ int ra_center_only_topk(const ra_center_params* p) {
   sp.kv_head_stride = (int64_t)p->num_centers * kHeadDim;
   sp.topk = p->top_clusters; sp.num_segments = 1; sp.sm_scale = 1.f;
   sp.workspace = p->workspace; sp.workspace_bytes = tail; sp.stream = p->stream;
+  if (p->num_centers <= kCenterMaxCsz && !getenv("RA_NO_CENTER_SELECT")) {
+    int* ids = p->out_cluster_ids ? p->out_cluster_ids : c_ids;
+    int st = center_select(p->q, p->centers, p->batch, p->num_heads, p->num_centers, p->top_clusters,
+                           p->cluster_len, ids, c_score, attend ? nullptr : p->out_indices,
+                           static_cast<cudaStream_t>(p->stream));
+    if (st != RA_OK || !attend) return st;
+    return run_gather(static_cast<const __half*>(p->q), static_cast<const __half*>(p->k),
+                      static_cast<const __half*>(p->v), static_cast<__half*>(p->out), nullptr,
+                      p->batch, p->num_heads, p->num_heads, p->num_tokens, p->kv_batch_stride,
+                      p->kv_token_stride, p->kv_head_stride, ids, c_score,
+                      (long long)p->num_heads * p->top_clusters, p->top_clusters, p->top_clusters,
+                      p->cluster_len, p->out_indices, p->sm_scale > 0.f ? p->sm_scale : 1.f,
+                      static_cast<unsigned*>(p->workspace), true,
+                      static_cast<cudaStream_t>(p->stream));
+  }
   if (!attend && p->out_indices) {
     // selection + expansion in one launch: the scan kernel ranks its winners and writes the
     // member tokens (and the cluster ids) in rank order
@@ -797,12 +837,19 @@ int ra_two_level_topk(const ra_two_level_params* p) {
   sp.topk = p->top_clusters; sp.num_segments = 1; sp.sm_scale = 1.f;
   sp.out_indices = c_ids; sp.out_scores = c_score;
   sp.workspace = ws; sp.workspace_bytes = coarse; sp.stream = p->stream;
-  int st = run(&sp, false);
-  if (st != RA_OK) return st;
-  // 2) rank order
   int* sorted = p->out_cluster_ids ? p->out_cluster_ids : c_sorted;
-  cudaError_t e = launch_rank_sort(c_score, c_ids, (int)rows, p->top_clusters, sorted, nullptr, stream);
-  if (e != cudaSuccess) return cuda_fail(e, "rank_sort launch");
+  if (p->num_centers <= kCenterMaxCsz && !getenv("RA_NO_CENTER_SELECT")) {
+    // steps 1 and 2 in one launch
+    int st = center_select(p->q, p->centers, p->batch, p->num_heads, p->num_centers, p->top_clusters,
+                           p->cluster_len, sorted, nullptr, nullptr, stream);
+    if (st != RA_OK) return st;
+  } else {
+    int st = run(&sp, false);
+    if (st != RA_OK) return st;
+    // 2) rank order
+    cudaError_t e = launch_rank_sort(c_score, c_ids, (int)rows, p->top_clusters, sorted, nullptr, stream);
+    if (e != cudaSuccess) return cuda_fail(e, "rank_sort launch");
+  }
   // 3) per-cluster top-k over the chosen clusters (+ attention over all kept keys)
   ra_params fp;
   memset(&fp, 0, sizeof fp);

@@ -1,0 +1,268 @@
+// Exact top-C of q.centroid per (batch row, head) for centroid tables small enough that one
+// head's scores fit in shared memory (csz <= 8192), written in rank order together with the
+// member token ids of the winners.
+//
+// The role of the reference's centroid pipeline (center_only_topk/gemv_topk.cu:157-457: GEMV over
+// the [H,CSZ,D] table, radix top-k, expansion of each winner to its CLEN member tokens :271-279)
+// and of the coarse stage of the two-level selection (gemv_topk.cu:218-262).  One cluster of CTAs
+// per row: every CTA scores a slice of the table with half-warp-per-row 128-bit loads and stores
+// each score into the shared memory of all CTAs of the cluster, so after one cluster barrier every
+// CTA holds the whole score vector.  Each CTA then finds the C-th largest (score, id) pair by a
+// radix descent over 64-bit composites (score key, inverted id) -- distinct values, so the
+// descent always ends on an exact cut --, ranks the C winners among themselves and writes the
+// outputs of the winners that lie in its own slice.  No global scratch, one launch.
+#include <cooperative_groups.h>
+
+#include "center_select.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace ra {
+
+namespace {
+
+struct CenterCtrl {
+  unsigned hist[256];
+  unsigned wmin[kCenterThreads / 32], wmax[kCenterThreads / 32];
+  unsigned long long base;   // lower edge of the active interval of composites
+  unsigned long long range;  // its width - 1
+  int need;                  // winners still to take from the active interval
+  int done;
+  int nwin, nown;
+};
+
+__device__ __forceinline__ unsigned long long composite(uint32_t key, int idx) {
+  return ((unsigned long long)key << 32) | (uint32_t)~idx;
+}
+
+}  // namespace
+
+__global__ void __launch_bounds__(kCenterThreads)
+center_select_kernel(const __grid_constant__ CenterSelectParams P) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  cg::cluster_group cluster = cg::this_cluster();
+  const int C = P.cluster;
+  const int crank = C > 1 ? (int)cluster.block_rank() : 0;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int hw = tid >> 4, l16 = tid & 15;
+  const int row = blockIdx.x / C;
+  const int h = row % P.heads;
+  const int n = P.csz;
+  const int n_pad = (n + 3) & ~3;
+
+  uint32_t* keys = reinterpret_cast<uint32_t*>(smem_raw);          // [n_pad]
+  int* winners = reinterpret_cast<int*>(keys + n_pad);             // [topc]
+  int2* own = reinterpret_cast<int2*>(winners + ((P.topc + 1) & ~1));  // [topc] (rank, id)
+  __shared__ CenterCtrl ctrl;
+
+  if (tid == 0) {
+    ctrl.nwin = 0;
+    ctrl.nown = 0;
+    ctrl.done = 0;
+  }
+
+  // ---- scores of this CTA's slice, pushed into every CTA of the cluster ----
+  const uint4 qraw = *reinterpret_cast<const uint4*>(P.q + (size_t)row * kHeadDim + l16 * 8);
+  float qf[8];
+  {
+    const float2 a = h2f2(qraw.x), b = h2f2(qraw.y), c = h2f2(qraw.z), d = h2f2(qraw.w);
+    qf[0] = a.x; qf[1] = a.y; qf[2] = b.x; qf[3] = b.y;
+    qf[4] = c.x; qf[5] = c.y; qf[6] = d.x; qf[7] = d.y;
+  }
+  if (C > 1) cluster.sync();   // every CTA of the cluster is running before its memory is written
+  const int lo = crank * P.per, hi = min(n, lo + P.per);
+  const __half* table = P.centers + (size_t)h * n * kHeadDim + l16 * 8;
+  constexpr int U = 8;         // rows in flight per half-warp
+  for (int r0 = lo; r0 < hi; r0 += (kCenterThreads / 16) * U) {   // same trip count for all threads
+    uint4 kv[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int r = r0 + u * (kCenterThreads / 16) + hw;
+      kv[u] = r < hi ? ldg128_nc(table + (size_t)r * kHeadDim) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int r = r0 + u * (kCenterThreads / 16) + hw;
+      const float2 a = h2f2(kv[u].x), b = h2f2(kv[u].y), c = h2f2(kv[u].z), d = h2f2(kv[u].w);
+      float s = a.x * qf[0];
+      s = fmaf(a.y, qf[1], s); s = fmaf(b.x, qf[2], s); s = fmaf(b.y, qf[3], s);
+      s = fmaf(c.x, qf[4], s); s = fmaf(c.y, qf[5], s); s = fmaf(d.x, qf[6], s);
+      s = fmaf(d.y, qf[7], s);
+      s += __shfl_xor_sync(0xffffffffu, s, 8);
+      s += __shfl_xor_sync(0xffffffffu, s, 4);
+      s += __shfl_xor_sync(0xffffffffu, s, 2);
+      s += __shfl_xor_sync(0xffffffffu, s, 1);
+      if (l16 == 0 && r < hi) {
+        const uint32_t key = score_key(s);
+        if (C > 1) {
+          for (int c2 = 0; c2 < C; ++c2) *cluster.map_shared_rank(&keys[r], c2) = key;
+        } else {
+          keys[r] = key;
+        }
+      }
+    }
+  }
+  if (C > 1) cluster.sync(); else __syncthreads();
+  // from here on a CTA touches its own shared memory only
+
+  // ---- range of the keys ----
+  {
+    uint32_t mn = 0xffffffffu, mx = 0u;
+    for (int i = tid; i < n; i += kCenterThreads) {
+      const uint32_t k = keys[i];
+      mn = min(mn, k);
+      mx = max(mx, k);
+    }
+    mn = __reduce_min_sync(0xffffffffu, mn);
+    mx = __reduce_max_sync(0xffffffffu, mx);
+    if (lane == 0) {
+      ctrl.wmin[warp] = mn;
+      ctrl.wmax[warp] = mx;
+    }
+    if (tid < 256) ctrl.hist[tid] = 0u;
+    __syncthreads();
+    if (tid == 0) {
+      for (int w = 0; w < kCenterThreads / 32; ++w) {
+        mn = min(mn, ctrl.wmin[w]);
+        mx = max(mx, ctrl.wmax[w]);
+      }
+      ctrl.base = (unsigned long long)mn << 32;
+      ctrl.range = (((unsigned long long)mx << 32) | 0xffffffffull) - ctrl.base;
+      ctrl.need = P.topc;
+    }
+    __syncthreads();
+  }
+
+  // ---- radix descent to the topc-th largest composite: at most 8 digits of 8 bits ----
+  unsigned long long base = ctrl.base, range = ctrl.range;
+  for (int it = 0; it < 9; ++it) {
+    const int bits = 64 - __clzll(range | 1ull);
+    const int shift = max(0, bits - 8);
+    for (int i = tid; i < n; i += kCenterThreads) {
+      const unsigned long long c = composite(keys[i], i);
+      if (c >= base && c - base <= range) atomicAdd(&ctrl.hist[(unsigned)((c - base) >> shift)], 1u);
+    }
+    __syncthreads();
+    if (warp == 0) {
+      // lane l owns bins 255-8l .. 248-8l; walk from the top until `need` composites are covered
+      const unsigned need = (unsigned)ctrl.need;   // read by every lane before the shuffles below
+      unsigned cnt[8], s = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        cnt[j] = ctrl.hist[255 - 8 * lane - j];
+        s += cnt[j];
+      }
+      unsigned incl = s;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const unsigned t = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += t;
+      }
+      unsigned above = incl - s;
+      if (above < need && need <= incl) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (above < need && need <= above + cnt[j]) {
+            const int b = 255 - 8 * lane - j;
+            ctrl.base = base + ((unsigned long long)b << shift);
+            ctrl.range = shift ? ((1ull << shift) - 1ull) : 0ull;
+            ctrl.need = (int)(need - above);
+            ctrl.done = (cnt[j] == need - above) ? 1 : 0;   // the whole bin wins: exact cut
+            above = need;                                    // stop the walk
+          } else {
+            above += cnt[j];
+          }
+        }
+      }
+    }
+    __syncthreads();
+    base = ctrl.base;
+    range = ctrl.range;
+    const int done = ctrl.done;
+    if (tid < 256) ctrl.hist[tid] = 0u;
+    __syncthreads();
+    if (done) break;
+  }
+  // every composite >= base is a winner, and there are exactly topc of them
+
+  // ---- winners, their ranks, outputs of the winners in this CTA's slice ----
+  for (int i = tid; i < n; i += kCenterThreads)
+    if (composite(keys[i], i) >= base) {
+      const int slot = atomicAdd(&ctrl.nwin, 1);
+      if (slot < P.topc) winners[slot] = i;
+    }
+  __syncthreads();
+  const int nwin = min(ctrl.nwin, P.topc);
+  // eight lanes per winner count the winners ahead of it
+  for (int w0 = 0; w0 < nwin; w0 += kCenterThreads / 8) {   // same trip count for all threads
+    const int w = w0 + (tid >> 3), sub = tid & 7;
+    const bool valid = w < nwin;
+    const int id = valid ? winners[w] : 0;
+    const bool mine = valid && id >= lo && id < hi;
+    int ahead = 0;
+    if (mine) {
+      const unsigned long long me = composite(keys[id], id);
+      for (int j = sub; j < nwin; j += 8) {
+        const int oj = winners[j];
+        ahead += composite(keys[oj], oj) > me;
+      }
+    }
+    ahead += __shfl_xor_sync(0xffffffffu, ahead, 4);
+    ahead += __shfl_xor_sync(0xffffffffu, ahead, 2);
+    ahead += __shfl_xor_sync(0xffffffffu, ahead, 1);
+    if (mine && sub == 0) {
+      const size_t o = (size_t)row * P.topc + ahead;
+      if (P.out_cluster_ids) P.out_cluster_ids[o] = id;
+      if (P.out_scores) P.out_scores[o] = key_score(keys[id]);
+      own[atomicAdd(&ctrl.nown, 1)] = make_int2(ahead, id);
+    }
+  }
+  if (!P.out_members) return;
+  __syncthreads();
+  const int nown = ctrl.nown;
+  int* members = P.out_members + (size_t)row * P.topc * P.clen;
+  if (P.vec_members) {
+    const int q4 = P.clen >> 2;
+    for (int x = tid; x < nown * q4; x += kCenterThreads) {
+      const int2 wi = own[x / q4];
+      const int t = (x % q4) * 4, first = wi.y * P.clen + t;
+      *reinterpret_cast<int4*>(members + (size_t)wi.x * P.clen + t) =
+          make_int4(first, first + 1, first + 2, first + 3);
+    }
+  } else {
+    for (int x = tid; x < nown * P.clen; x += kCenterThreads) {
+      const int2 wi = own[x / P.clen];
+      const int t = x % P.clen;
+      members[(size_t)wi.x * P.clen + t] = wi.y * P.clen + t;
+    }
+  }
+}
+
+size_t center_select_smem_bytes(int csz, int topc) {
+  return (size_t)((csz + 3) & ~3) * 4 + (size_t)((topc + 1) & ~1) * 4 + (size_t)topc * 8;
+}
+
+cudaError_t launch_center_select(const CenterSelectParams& P, int rows, cudaStream_t stream) {
+  auto kern = center_select_kernel;
+  const size_t smem = center_select_smem_bytes(P.csz, P.topc);
+  static const cudaError_t attr_status = cudaFuncSetAttribute(
+      kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      (int)center_select_smem_bytes(kCenterMaxCsz, kCenterMaxCsz));
+  if (attr_status != cudaSuccess) return attr_status;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(rows * P.cluster), 1, 1);
+  cfg.blockDim = dim3(kCenterThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)P.cluster;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  note_launch();
+  return cudaLaunchKernelEx(&cfg, kern, P);
+}
+
+}  // namespace ra
