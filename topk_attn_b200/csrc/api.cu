@@ -752,7 +752,7 @@ int ra_center_only_topk(const ra_center_params* p) {
     return run_gather(static_cast<const __half*>(p->q), static_cast<const __half*>(p->k),
                       static_cast<const __half*>(p->v), static_cast<__half*>(p->out), nullptr,
                       p->batch, p->num_heads, p->num_heads, p->num_tokens, p->kv_batch_stride,
-                      p->kv_token_stride, p->kv_head_stride, ids, c_score,
+                      p->kv_token_stride, p->kv_head_stride, ids, /*already in rank order*/ nullptr,
                       (long long)p->num_heads * p->top_clusters, p->top_clusters, p->top_clusters,
                       p->cluster_len, p->out_indices, p->sm_scale > 0.f ? p->sm_scale : 1.f,
                       static_cast<unsigned*>(p->workspace), true,

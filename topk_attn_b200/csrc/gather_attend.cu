@@ -140,6 +140,7 @@ struct GatherPartial {
   float o[kHeadDim];
 };
 
+template <int UN>   // K and V rows in flight per half-warp
 __global__ void __launch_bounds__(kMergeThreads, 1)
 gather_flash_kernel(const __grid_constant__ GatherParams P) {
   extern __shared__ __align__(16) unsigned char smem_g[];
@@ -199,7 +200,6 @@ gather_flash_kernel(const __grid_constant__ GatherParams P) {
   const size_t head_off = (size_t)bq * P.m.v_batch_stride + (size_t)hkv * P.m.v_head_stride + l16 * 8;
   const __half* kb = P.k + head_off;
   const __half* vb = P.m.v + head_off;
-  constexpr int UN = 4;
   constexpr int kRowsPerIter = 2 * kW;
   float m_run = -INFINITY, l_run = 0.f, acc[8];
 #pragma unroll
@@ -326,7 +326,9 @@ size_t gather_flash_smem_bytes(int n_src) {
 }
 
 cudaError_t launch_gather_flash(const GatherParams& P, int rows, size_t smem, cudaStream_t stream) {
-  auto kern = gather_flash_kernel;
+  // long lists: eight rows in flight hide the DRAM latency; short ones: four, more CTAs per SM
+  const int un = ceil_div(P.n_entries, P.m.cluster) >= 512 ? 8 : 4;
+  auto kern = un == 8 ? gather_flash_kernel<8> : gather_flash_kernel<4>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   cudaLaunchConfig_t cfg = {};
