@@ -18,7 +18,7 @@
 #include "scan_select.cuh"
 
 namespace ra {
-int scan_max_active_clusters(int hg, int nq, int cluster, size_t smem);
+int scan_max_active_clusters(int hg, int nq, int cluster, size_t smem, int threads);
 std::atomic<unsigned long long> g_launch_count{0};
 }
 
@@ -192,7 +192,13 @@ Plan make_plan(const Shape& s) {
         // stages, consumer groups, check interval and list capacity within the shared-memory
         // budget: the deepest pipeline whose lists still hold k keys plus the keys that may arrive
         // between two overflow checks
-        int nstages = 0, cap = 0, cgroups = 0, rdv = 0;
+        // Long parts take the deepest pipeline that fits.  Short parts (a few tiles) are bound by
+        // fixed costs and by how many CTAs run at once: the shallower geometries, which leave room
+        // for two CTAs per SM, compete as well, at a penalty on their stream time.
+        struct Geo { int nstages, cap, cgroups, rdv; double slow; };
+        Geo geos[4];
+        int ngeo = 0;
+        static const double kSlow[4] = {1.0, 1.05, 1.2, 1.35};
         bool glists = false;
         // one query per K row: scoring is latency-bound, two warp groups and deep rings help;
         // several queries per row (tensor-core scoring): one group and roomier lists win
@@ -212,23 +218,27 @@ Plan make_plan(const Shape& s) {
             const int c = std::min(fit, 2 * s.topk + margin);
             const int want = (st > 4) ? (3 * s.topk) / 2 + margin : s.topk + margin + 64;
             if (c >= std::min(want, 2 * s.topk + margin)) {
-              nstages = st; cap = c; cgroups = g2; rdv = r;
+              geos[ngeo++] = Geo{st, c, g2, r, kSlow[gi]};
               break;
             }
           }
-          if (nstages) break;
+          if (ngeo && (tiles > 32 || f_stages)) break;
         }
         // Several large lists per CTA leave too little room next to the pipeline: they move to
         // global memory (deep pipeline, capacity 4k, few cuts).
         if (nq > 1 && lists_may_spill(nl, s.topk) && !getenv("RA_NO_GLOBAL_LISTS") &&
             
             groups * nsplit * cluster <= kMaxSpillGrid && (size_t)kMaxStages * kStageBytes >= scratch) {
-          nstages = kMaxStages; cgroups = 2; rdv = 4; cap = kSpillCapFactor * s.topk; glists = true;
+          geos[0] = Geo{kMaxStages, kSpillCapFactor * s.topk, 2, 4, 1.0};
+          ngeo = 1;
+          glists = true;
         }
-        if (!nstages) continue;
+        for (int gx = 0; gx < ngeo; ++gx) {
+        const int nstages = geos[gx].nstages, cap = geos[gx].cap, cgroups = geos[gx].cgroups,
+                  rdv = geos[gx].rdv;
         const size_t smem = scan_smem_bytes(glists ? 0 : nl, cap, nstages);
         const int nclusters = groups * nsplit;
-        const int active = scan_max_active_clusters(hg, nq, cluster, smem);
+        const int active = scan_max_active_clusters(hg, nq, cluster, smem, 32 * (8 * cgroups + 1));
         if (active <= 0) continue;
         const int waves = ceil_div(nclusters, active);
         const int live = std::min(nclusters, active) * cluster;
@@ -248,7 +258,8 @@ Plan make_plan(const Shape& s) {
         // until a list has filled once every key passes the threshold and is appended: about a
         // microsecond per iteration instead of a fraction of one
         const double warmup = 1e-6 * std::min(ceil_div(tiles, cluster), cap / T) / cgroups;
-        double cost = waves * (bytes_cta / rate + cuts * nl * 2e-6 + warmup + 6e-6 + cluster_cost) +
+        double cost = waves * (geos[gx].slow * bytes_cta / rate + cuts * nl * 2e-6 + warmup + 6e-6 +
+                               cluster_cost) +
                       (two_stage ? 8e-6 : 0.0);
         Plan pl;
         pl.hg = hg; pl.nq = nq; pl.bshare = bshare; pl.nq_valid = nq_valid;
@@ -262,6 +273,7 @@ Plan make_plan(const Shape& s) {
           continue;
         pl.ok = true;
         if (!best.ok || pl.cost < best.cost) best = pl;
+        }
       }
     }
   }

@@ -598,7 +598,7 @@ cudaError_t launch_scan_select(const ScanParams& P, int hg, int nq, int grid, si
 namespace ra {
 
 template <int HG, int NQ>
-static int max_clusters_one(int cluster, size_t smem) {
+static int max_clusters_one(int cluster, size_t smem, int threads) {
   auto kern = scan_select_kernel<HG, NQ, 1>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
     (void)cudaGetLastError();
@@ -611,7 +611,7 @@ static int max_clusters_one(int cluster, size_t smem) {
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)cluster * 64, 1, 1);
-  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.blockDim = dim3((unsigned)threads, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -629,10 +629,10 @@ static int max_clusters_one(int cluster, size_t smem) {
 }
 
 // Clusters of this shape that can be resident at once on the current device (cached).
-int scan_max_active_clusters(int hg, int nq, int cluster, size_t smem) {
+int scan_max_active_clusters(int hg, int nq, int cluster, size_t smem, int threads) {
   static std::mutex mu;
   static std::map<std::tuple<int, int, int, size_t>, int> cache;
-  const auto key = std::make_tuple(hg, nq, cluster, (smem + 4095) / 4096);
+  const auto key = std::make_tuple(hg, nq, cluster * 4096 + threads, (smem + 4095) / 4096);
   {
     std::lock_guard<std::mutex> g(mu);
     auto it = cache.find(key);
@@ -640,7 +640,7 @@ int scan_max_active_clusters(int hg, int nq, int cluster, size_t smem) {
   }
   int n = 0;
 #define RA_CASE(H, Q) \
-  if (hg == H && nq == Q) n = max_clusters_one<H, Q>(cluster, smem);
+  if (hg == H && nq == Q) n = max_clusters_one<H, Q>(cluster, smem, threads);
   RA_CASE(1, 1) RA_CASE(2, 1) RA_CASE(4, 1) RA_CASE(8, 1)
   RA_CASE(1, 2) RA_CASE(2, 2) RA_CASE(4, 2)
   RA_CASE(1, 4) RA_CASE(2, 4)
