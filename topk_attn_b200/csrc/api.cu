@@ -22,6 +22,17 @@ int scan_max_active_clusters(int hg, int nq, int cluster, size_t smem, int threa
 std::atomic<unsigned long long> g_launch_count{0};
 }
 
+extern "C" {
+// attention over id lists (defined with the entry points below); with src_score and
+// expand_clen == 0 the lists carry their scores and only V is read
+static int run_gather(const __half* q, const __half* k, const __half* v, __half* out, float* out_lse,
+                      int batch, int hq, int hkv, int n_tokens, long long bs, long long ts,
+                      long long hs, const int* src_idx, const float* src_score,
+                      long long src_bstride, long long src_hstride, int n_src, int expand_clen,
+                      int* out_token_ids, float sm_scale, unsigned* status, bool attend,
+                      cudaStream_t stream, int id_shift = 0);
+}
+
 namespace {
 
 using namespace ra;
@@ -494,6 +505,18 @@ int run(const ra_params* p, bool attend, const PartIds* ext = nullptr) {
   if (!two_stage) return RA_OK;
 
   if (lists_final && !attend) return RA_OK;
+  if (lists_final) {
+    // every listed key takes part: one pass over the V rows of the lists with the scores the scan
+    // wrote, a cluster of CTAs per row
+    const long long per_row = (long long)s.segments * s.topk;
+    const int st = run_gather(static_cast<const __half*>(p->q), nullptr,
+                              static_cast<const __half*>(p->v), static_cast<__half*>(p->out),
+                              p->out_lse, s.batch, s.hq, s.hkv, real_tokens, p->kv_batch_stride,
+                              p->kv_token_stride, p->kv_head_stride, sp.m.sel_idx, sp.m.sel_score,
+                              (long long)s.hq * per_row, per_row, (int)per_row, 0, nullptr,
+                              p->sm_scale, status, true, stream, p->index_base);
+    if (st != RA_ERR_UNSUPPORTED) return st;   // lists too long for that kernel: the merge below
+  }
   MergeParams mp;
   memset(&mp, 0, sizeof mp);
   mp.m = sp.m;
@@ -634,7 +657,7 @@ static int run_gather(const __half* q, const __half* k, const __half* v, __half*
                       long long hs, const int* src_idx, const float* src_score,
                       long long src_bstride, long long src_hstride, int n_src, int expand_clen,
                       int* out_token_ids, float sm_scale, unsigned* status, bool attend,
-                      cudaStream_t stream) {
+                      cudaStream_t stream, int id_shift) {
   const long long n_entries_ll = (long long)n_src * (expand_clen > 0 ? expand_clen : 1);
   if (n_entries_ll > (1 << 20)) return unsupported("more than 2^20 ids per head");
   const int n_entries = (int)n_entries_ll;
@@ -648,7 +671,7 @@ static int run_gather(const __half* q, const __half* k, const __half* v, __half*
   m.topk = n_entries; m.per = per; m.cluster = cluster; m.select_all = 1; m.local_deal = 1;
   m.out_mode = attend ? kOutFinal : kOutNone;
   m.hq_total = hq; m.list_pitch = n_entries; m.list_off = 0; m.index_base = 0;
-  m.own_lo = 0; m.own_hi = 0x7fffffff; m.id_shift = 0; m.n_tokens = n_tokens; m.status = status;
+  m.own_lo = 0; m.own_hi = 0x7fffffff; m.id_shift = id_shift; m.n_tokens = n_tokens; m.status = status;
   m.sel_idx = nullptr; m.sel_score = nullptr;
   m.v = v; m.v_batch_stride = bs; m.v_token_stride = ts; m.v_head_stride = hs;
   m.out = out; m.out_lse = out_lse; m.out_partial = nullptr;

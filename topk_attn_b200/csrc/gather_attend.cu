@@ -140,7 +140,9 @@ struct GatherPartial {
   float o[kHeadDim];
 };
 
-template <int UN>   // K and V rows in flight per half-warp
+// UN: K and V rows in flight per half-warp.  GIVEN: the list carries the raw scores q.K of its ids
+// (src_score, expand_clen == 0), so only the V rows are read.
+template <int UN, bool GIVEN>
 __global__ void __launch_bounds__(kMergeThreads, 1)
 gather_flash_kernel(const __grid_constant__ GatherParams P) {
   extern __shared__ __align__(16) unsigned char smem_g[];
@@ -157,8 +159,10 @@ gather_flash_kernel(const __grid_constant__ GatherParams P) {
   int* src = reinterpret_cast<int*>(cpart + 1);
 
   const int* gsrc = P.src_idx + (size_t)bq * P.src_batch_stride + (size_t)hq * P.src_head_stride;
-  if (P.expand_clen > 0 && P.src_score) {
-    const float* gsc = P.src_score + (size_t)bq * P.src_batch_stride + (size_t)hq * P.src_head_stride;
+  const float* gsc = nullptr;
+  if (P.src_score)
+    gsc = P.src_score + (size_t)bq * P.src_batch_stride + (size_t)hq * P.src_head_stride;
+  if (!GIVEN && P.expand_clen > 0 && gsc) {
     for (int i = tid; i < P.n_src; i += kMergeThreads) {
       const float si = gsc[i];
       const int ii = gsrc[i];
@@ -206,34 +210,45 @@ gather_flash_kernel(const __grid_constant__ GatherParams P) {
   for (int i = 0; i < 8; ++i) acc[i] = 0.f;
   // the trip count is the same for every lane: the shuffles below need the whole warp
   for (int base = 0; base < n; base += kRowsPerIter * UN) {
-    uint4 kk[UN], vv[UN];
+    uint4 kk[GIVEN ? 1 : UN], vv[UN];
+    float given[GIVEN ? UN : 1];
     bool ok[UN];
 #pragma unroll
     for (int u = 0; u < UN; ++u) {
       const int e = base + warp * 2 + half + kRowsPerIter * u;
-      const int tok = (e < n) ? token_of(lo + e) : -1;
-      ok[u] = (unsigned)tok < (unsigned)P.m.n_tokens;
-      if (e < n && !ok[u] && l16 == 0) atomicOr(P.m.status, kStatusBadId);
+      const int raw = (e < n) ? token_of(lo + e) : -1;
+      const int tok = raw - P.m.id_shift;
+      ok[u] = raw >= 0 && (unsigned)tok < (unsigned)P.m.n_tokens;
+      // an empty slot (-1) is skipped silently; any other id outside the cache is reported
+      if (e < n && raw >= 0 && !ok[u] && l16 == 0) atomicOr(P.m.status, kStatusBadId);
       const size_t off = ok[u] ? (size_t)tok * P.m.v_token_stride : 0;
-      kk[u] = ok[u] ? ldg128_nc(kb + off) : make_uint4(0u, 0u, 0u, 0u);
+      if constexpr (GIVEN) {
+        given[u] = ok[u] ? gsc[lo + e] * P.m.scale_log2e : 0.f;
+      } else {
+        kk[u] = ok[u] ? ldg128_nc(kb + off) : make_uint4(0u, 0u, 0u, 0u);
+      }
       vv[u] = ok[u] ? ldg128_nc(vb + off) : make_uint4(0u, 0u, 0u, 0u);
     }
     float x[UN];
     float bm = -INFINITY;
 #pragma unroll
     for (int u = 0; u < UN; ++u) {
-      const uint32_t w[4] = {kk[u].x, kk[u].y, kk[u].z, kk[u].w};
       float a = 0.f;
+      if constexpr (GIVEN) {
+        a = given[u];
+      } else {
+        const uint32_t w[4] = {kk[u].x, kk[u].y, kk[u].z, kk[u].w};
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float2 f = h2f2(w[i]);
-        a = fmaf(f.x, qf[2 * i], a);
-        a = fmaf(f.y, qf[2 * i + 1], a);
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = h2f2(w[i]);
+          a = fmaf(f.x, qf[2 * i], a);
+          a = fmaf(f.y, qf[2 * i + 1], a);
+        }
+        a += __shfl_xor_sync(0xffffffffu, a, 8);
+        a += __shfl_xor_sync(0xffffffffu, a, 4);
+        a += __shfl_xor_sync(0xffffffffu, a, 2);
+        a += __shfl_xor_sync(0xffffffffu, a, 1);
       }
-      a += __shfl_xor_sync(0xffffffffu, a, 8);
-      a += __shfl_xor_sync(0xffffffffu, a, 4);
-      a += __shfl_xor_sync(0xffffffffu, a, 2);
-      a += __shfl_xor_sync(0xffffffffu, a, 1);
       x[u] = ok[u] ? a : -INFINITY;
       bm = fmaxf(bm, x[u]);
     }
@@ -328,7 +343,9 @@ size_t gather_flash_smem_bytes(int n_src) {
 cudaError_t launch_gather_flash(const GatherParams& P, int rows, size_t smem, cudaStream_t stream) {
   // long lists: eight rows in flight hide the DRAM latency; short ones: four, more CTAs per SM
   const int un = ceil_div(P.n_entries, P.m.cluster) >= 512 ? 8 : 4;
-  auto kern = un == 8 ? gather_flash_kernel<8> : gather_flash_kernel<4>;
+  const bool given = P.expand_clen == 0 && P.src_score != nullptr;
+  auto kern = given ? (un == 8 ? gather_flash_kernel<8, true> : gather_flash_kernel<4, true>)
+                    : (un == 8 ? gather_flash_kernel<8, false> : gather_flash_kernel<4, false>);
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   cudaLaunchConfig_t cfg = {};
