@@ -39,6 +39,24 @@ def test_random_shapes(B, Hq, Hkv, N, k, per_batch):
     check_topk_attention(q, k_, v, k, sm_scale=1.0)
 
 
+@pytest.mark.parametrize("B,Hq,Hkv,N,k,S,per_batch", [
+    (1, 8, 8, 1024, 64, 1, False),
+    (2, 8, 2, 4096, 128, 1, False),       # GQA 4
+    (3, 4, 4, 777, 777, 1, True),         # k == N
+    (1, 2, 1, 130, 1, 1, False),
+    (5, 6, 3, 2049, 33, 1, False),        # three batch rows... one cache, two heads per kv head
+    (4, 32, 32, 8192, 128, 4, False),     # the reference extension's shape: 4 chunks of 2048
+    (2, 8, 8, 4096, 1024, 2, True),
+])
+def test_short_segments_on_both_paths(B, Hq, Hkv, N, k, S, per_batch, monkeypatch):
+    """Segments of at most 4096 keys go through the score-everything kernel; the streaming kernel
+    stays reachable (RA_NO_DENSE_SELECT) and must agree with the oracle on the same inputs."""
+    q, k_, v = rand_case(B, Hq, Hkv, N, per_batch, seed=N + k + S)
+    check_topk_attention(q, k_, v, k, sm_scale=0.7, num_segments=S)
+    monkeypatch.setenv("RA_NO_DENSE_SELECT", "1")
+    check_topk_attention(q, k_, v, k, sm_scale=0.7, num_segments=S)
+
+
 @pytest.mark.parametrize("scale", [0.25, 1.0 / math.sqrt(128), 2.0])
 def test_softmax_scale(scale):
     q, k, v = rand_case(2, 8, 8, 4096, True, seed=5)

@@ -23,7 +23,7 @@ LIB = os.path.join(LIBDIR, "libtopk_attn_b200.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 CU_SOURCES = ["api.cu", "scan_select.cu", "merge_attend.cu", "gather_attend.cu", "flash_decode.cu",
-              "center_select.cu"]
+              "center_select.cu", "dense_select.cu"]
 
 
 def _newer(target: str, deps) -> bool:

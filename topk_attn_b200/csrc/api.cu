@@ -12,6 +12,7 @@
 #include <tuple>
 
 #include "center_select.cuh"
+#include "dense_select.cuh"
 #include "flash_decode.cuh"
 #include "gather_attend.cuh"
 #include "merge_attend.cuh"
@@ -446,6 +447,48 @@ int run(const ra_params* p, bool attend, const PartIds* ext = nullptr) {
   }
   cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
   unsigned* status = static_cast<unsigned*>(p->workspace);
+  // Short segments: score every key into shared memory and select afterwards (no candidate lists),
+  // then one pass over the V rows of the lists.
+  const int seg_len = s.n / s.segments;
+  int dense_bshare = 1;
+  if (!s.per_batch)
+    for (int b = 1; b <= s.batch; ++b)
+      if (s.batch % b == 0 && b * c.group <= 4) dense_bshare = b;
+  // (one query per K row and one segment: the fused single launch of the scan kernel is quicker)
+  if (!ext && seg_len <= kDenseMaxSeg && c.group <= 4 && (s.segments > 1 || dense_bshare * c.group > 1) &&
+      !getenv("RA_NO_DENSE_SELECT")) {
+    const int bshare = dense_bshare;
+    const int nq_valid = bshare * c.group, nq = next_pow2(nq_valid);
+    const size_t lists = (size_t)s.batch * s.hq * s.segments * s.topk;
+    float* l_score = reinterpret_cast<float*>(static_cast<char*>(p->workspace) + kStatusBytes);
+    int* l_idx = reinterpret_cast<int*>(l_score + lists);
+    DenseSelectParams dp;
+    memset(&dp, 0, sizeof dp);
+    dp.q = static_cast<const __half*>(p->q); dp.k = static_cast<const __half*>(p->k);
+    dp.batch_stride = p->kv_batch_stride; dp.token_stride = p->kv_token_stride;
+    dp.head_stride = p->kv_head_stride;
+    dp.batch = s.batch; dp.hq = s.hq; dp.hkv = s.hkv; dp.group = c.group;
+    dp.bshare = bshare; dp.nq_valid = nq_valid;
+    dp.seg_len = seg_len; dp.segments = s.segments; dp.topk = s.topk;
+    int cl = 1;
+    while (cl < kDenseMaxCluster && seg_len > 512 * cl) cl <<= 1;
+    dp.cluster = cl; dp.per = (ceil_div(seg_len, cl) + 3) & ~3;
+    dp.index_base = p->index_base;
+    dp.out_idx = p->out_indices ? p->out_indices : l_idx;
+    dp.out_score = p->out_scores ? p->out_scores : l_score;
+    if (verbose)
+      fprintf(stderr, "[topk_attn_b200] plan: dense select nq=%d(valid %d) cluster=%d seg_len=%d\n", nq,
+              nq_valid, cl, seg_len);
+    cudaError_t e = launch_dense_select(dp, nq, stream);
+    if (e != cudaSuccess) return cuda_fail(e, "dense_select launch");
+    if (!attend) return RA_OK;
+    const long long per_row = (long long)s.segments * s.topk;
+    return run_gather(static_cast<const __half*>(p->q), nullptr, static_cast<const __half*>(p->v),
+                      static_cast<__half*>(p->out), p->out_lse, s.batch, s.hq, s.hkv, s.n,
+                      p->kv_batch_stride, p->kv_token_stride, p->kv_head_stride, dp.out_idx,
+                      dp.out_score, (long long)s.hq * per_row, per_row, (int)per_row, 0, nullptr,
+                      p->sm_scale, status, true, stream, p->index_base);
+  }
   const int parts = s.segments * pl.nsplit;
   const bool two_stage = parts > 1;
   float* ws_score = reinterpret_cast<float*>(static_cast<char*>(p->workspace) + kStatusBytes);

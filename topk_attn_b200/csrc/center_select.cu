@@ -14,28 +14,11 @@
 #include <cooperative_groups.h>
 
 #include "center_select.cuh"
+#include "radix_winners.cuh"
 
 namespace cg = cooperative_groups;
 
 namespace ra {
-
-namespace {
-
-struct CenterCtrl {
-  unsigned hist[256];
-  unsigned wmin[kCenterThreads / 32], wmax[kCenterThreads / 32];
-  unsigned long long base;   // lower edge of the active interval of composites
-  unsigned long long range;  // its width - 1
-  int need;                  // winners still to take from the active interval
-  int done;
-  int nwin, nown;
-};
-
-__device__ __forceinline__ unsigned long long composite(uint32_t key, int idx) {
-  return ((unsigned long long)key << 32) | (uint32_t)~idx;
-}
-
-}  // namespace
 
 __global__ void __launch_bounds__(kCenterThreads)
 center_select_kernel(const __grid_constant__ CenterSelectParams P) {
@@ -43,7 +26,7 @@ center_select_kernel(const __grid_constant__ CenterSelectParams P) {
   cg::cluster_group cluster = cg::this_cluster();
   const int C = P.cluster;
   const int crank = C > 1 ? (int)cluster.block_rank() : 0;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tid = threadIdx.x;
   const int hw = tid >> 4, l16 = tid & 15;
   const int row = blockIdx.x / C;
   const int h = row % P.heads;
@@ -53,13 +36,8 @@ center_select_kernel(const __grid_constant__ CenterSelectParams P) {
   uint32_t* keys = reinterpret_cast<uint32_t*>(smem_raw);          // [n_pad]
   int* winners = reinterpret_cast<int*>(keys + n_pad);             // [topc]
   int2* own = reinterpret_cast<int2*>(winners + ((P.topc + 1) & ~1));  // [topc] (rank, id)
-  __shared__ CenterCtrl ctrl;
-
-  if (tid == 0) {
-    ctrl.nwin = 0;
-    ctrl.nown = 0;
-    ctrl.done = 0;
-  }
+  __shared__ WinnerCtrl ctrl;
+  if (tid == 0) ctrl.nown = 0;
 
   // ---- scores of this CTA's slice, pushed into every CTA of the cluster ----
   const uint4 qraw = *reinterpret_cast<const uint4*>(P.q + (size_t)row * kHeadDim + l16 * 8);
@@ -105,93 +83,8 @@ center_select_kernel(const __grid_constant__ CenterSelectParams P) {
   if (C > 1) cluster.sync(); else __syncthreads();
   // from here on a CTA touches its own shared memory only
 
-  // ---- range of the keys ----
-  {
-    uint32_t mn = 0xffffffffu, mx = 0u;
-    for (int i = tid; i < n; i += kCenterThreads) {
-      const uint32_t k = keys[i];
-      mn = min(mn, k);
-      mx = max(mx, k);
-    }
-    mn = __reduce_min_sync(0xffffffffu, mn);
-    mx = __reduce_max_sync(0xffffffffu, mx);
-    if (lane == 0) {
-      ctrl.wmin[warp] = mn;
-      ctrl.wmax[warp] = mx;
-    }
-    if (tid < 256) ctrl.hist[tid] = 0u;
-    __syncthreads();
-    if (tid == 0) {
-      for (int w = 0; w < kCenterThreads / 32; ++w) {
-        mn = min(mn, ctrl.wmin[w]);
-        mx = max(mx, ctrl.wmax[w]);
-      }
-      ctrl.base = (unsigned long long)mn << 32;
-      ctrl.range = (((unsigned long long)mx << 32) | 0xffffffffull) - ctrl.base;
-      ctrl.need = P.topc;
-    }
-    __syncthreads();
-  }
-
-  // ---- radix descent to the topc-th largest composite: at most 8 digits of 8 bits ----
-  unsigned long long base = ctrl.base, range = ctrl.range;
-  for (int it = 0; it < 9; ++it) {
-    const int bits = 64 - __clzll(range | 1ull);
-    const int shift = max(0, bits - 8);
-    for (int i = tid; i < n; i += kCenterThreads) {
-      const unsigned long long c = composite(keys[i], i);
-      if (c >= base && c - base <= range) atomicAdd(&ctrl.hist[(unsigned)((c - base) >> shift)], 1u);
-    }
-    __syncthreads();
-    if (warp == 0) {
-      // lane l owns bins 255-8l .. 248-8l; walk from the top until `need` composites are covered
-      const unsigned need = (unsigned)ctrl.need;   // read by every lane before the shuffles below
-      unsigned cnt[8], s = 0;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        cnt[j] = ctrl.hist[255 - 8 * lane - j];
-        s += cnt[j];
-      }
-      unsigned incl = s;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const unsigned t = __shfl_up_sync(0xffffffffu, incl, o);
-        if (lane >= o) incl += t;
-      }
-      unsigned above = incl - s;
-      if (above < need && need <= incl) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          if (above < need && need <= above + cnt[j]) {
-            const int b = 255 - 8 * lane - j;
-            ctrl.base = base + ((unsigned long long)b << shift);
-            ctrl.range = shift ? ((1ull << shift) - 1ull) : 0ull;
-            ctrl.need = (int)(need - above);
-            ctrl.done = (cnt[j] == need - above) ? 1 : 0;   // the whole bin wins: exact cut
-            above = need;                                    // stop the walk
-          } else {
-            above += cnt[j];
-          }
-        }
-      }
-    }
-    __syncthreads();
-    base = ctrl.base;
-    range = ctrl.range;
-    const int done = ctrl.done;
-    if (tid < 256) ctrl.hist[tid] = 0u;
-    __syncthreads();
-    if (done) break;
-  }
-  // every composite >= base is a winner, and there are exactly topc of them
-
-  // ---- winners, their ranks, outputs of the winners in this CTA's slice ----
-  for (int i = tid; i < n; i += kCenterThreads)
-    if (composite(keys[i], i) >= base) {
-      const int slot = atomicAdd(&ctrl.nwin, 1);
-      if (slot < P.topc) winners[slot] = i;
-    }
-  __syncthreads();
+  select_winners<kCenterThreads>(keys, n, P.topc, ctrl, winners);
+  // ---- ranks and outputs of the winners in this CTA's slice ----
   const int nwin = min(ctrl.nwin, P.topc);
   // eight lanes per winner count the winners ahead of it
   for (int w0 = 0; w0 < nwin; w0 += kCenterThreads / 8) {   // same trip count for all threads
