@@ -120,6 +120,10 @@ def make_workload(name: str, device):
         return w
     if name == "cfg4":
         return W.sharded_long_context_shard(0, 1, device=device)
+    if name == "legacy":         # the reference extension's own test shape: 4 chunks of 2048, top-128 each
+        w = W.legacy_test_case(device=device)
+        w.topk, w.num_segments = 128, 4
+        return w
     raise SystemExit(f"workload {name} is not available in this bench")
 
 
@@ -137,6 +141,10 @@ def cpu_sample(workload: str):
         return W.dense_flash_decoding(device="cpu", batch=1), "one batch row of cfg1 (N=32768, 32 q / 8 kv heads)"
     if workload == "cfg3":
         return W.centroid_retrieval(device="cpu"), "cfg3 in full"
+    if workload == "legacy":
+        w = W.legacy_test_case()
+        w.topk, w.num_segments = 128, 4
+        return w, "the extension's test shape in full (B=4, N=8192, 4 chunks, top-128)"
     raise SystemExit(f"no CPU sample for {workload}")
 
 
@@ -293,8 +301,10 @@ def run_ours(args):
     q, k, v = w.q, w.k, w.v
     out = torch.empty_like(q)
     kind = "dense" if w.num_splits else ("centroid" if w.centers is not None else "topk")
-    kernel_name = {"dense": "flash_decode_kernel", "centroid": "scan_select_kernel + gather_attend_kernel",
+    kernel_name = {"dense": "flash_decode_kernel", "centroid": "center_select_kernel + gather_flash_kernel",
                    "topk": "scan_select_kernel"}[kind]
+    if args.workload == "legacy":
+        kernel_name = "dense_select_kernel + gather_flash_kernel"
 
     def op(q_in):
         if kind == "dense":
