@@ -77,22 +77,44 @@ dense_select_kernel(const __grid_constant__ DenseSelectParams P) {
         t = fmaf(a.y, qf[qi][1], t); t = fmaf(b.x, qf[qi][2], t); t = fmaf(b.y, qf[qi][3], t);
         t = fmaf(c.x, qf[qi][4], t); t = fmaf(c.y, qf[qi][5], t); t = fmaf(d.x, qf[qi][6], t);
         t = fmaf(d.y, qf[qi][7], t);
-        t += __shfl_xor_sync(0xffffffffu, t, 8);
-        t += __shfl_xor_sync(0xffffffffu, t, 4);
-        t += __shfl_xor_sync(0xffffffffu, t, 2);
-        t += __shfl_xor_sync(0xffffffffu, t, 1);
         s[qi] = t;
       }
-      // the NQ x C stores of this row are dealt over the 16 lanes that hold its sums
+      // Transposing reduction over the 16 lanes of the row: each exchange halves the number of
+      // queries a lane carries, so lane l ends with the full sum of query l / (16 / NQ).
+      float tot;
+      if constexpr (NQ == 4) {
+        const bool up8 = l16 & 8, up4 = l16 & 4;
+        float a0 = up8 ? s[2] : s[0], a1 = up8 ? s[3] : s[1];
+        const float b0 = up8 ? s[0] : s[2], b1 = up8 ? s[1] : s[3];
+        a0 += __shfl_xor_sync(0xffffffffu, b0, 8);
+        a1 += __shfl_xor_sync(0xffffffffu, b1, 8);
+        tot = up4 ? a1 : a0;
+        const float give = up4 ? a0 : a1;
+        tot += __shfl_xor_sync(0xffffffffu, give, 4);
+      } else if constexpr (NQ == 2) {
+        const bool up8 = l16 & 8;
+        tot = up8 ? s[1] : s[0];
+        const float give = up8 ? s[0] : s[1];
+        tot += __shfl_xor_sync(0xffffffffu, give, 8);
+        tot += __shfl_xor_sync(0xffffffffu, tot, 4);
+      } else {
+        tot = s[0];
+        tot += __shfl_xor_sync(0xffffffffu, tot, 8);
+        tot += __shfl_xor_sync(0xffffffffu, tot, 4);
+      }
+      tot += __shfl_xor_sync(0xffffffffu, tot, 2);
+      tot += __shfl_xor_sync(0xffffffffu, tot, 1);
+      // the 16 / NQ lanes that hold a query's sum deal its C stores among themselves
       if (r < hi) {
-        for (int x = l16; x < NQ * C; x += 16) {
-          const int qi = x % NQ, c2 = x / NQ;
-          float v = s[0];
-#pragma unroll
-          for (int j = 1; j < NQ; ++j) v = (qi == j) ? s[j] : v;
-          uint32_t* dst = &keys[(size_t)qi * n_pad + r];
-          if (C > 1) dst = cluster.map_shared_rank(dst, c2);
-          *dst = score_key(v);
+        constexpr int kLanesPerQuery = 16 / NQ;
+        const int qi = l16 / kLanesPerQuery;
+        uint32_t* dst = &keys[(size_t)qi * n_pad + r];
+        const uint32_t key = score_key(tot);
+        if (C > 1) {
+          for (int c2 = l16 % kLanesPerQuery; c2 < C; c2 += kLanesPerQuery)
+            *cluster.map_shared_rank(dst, c2) = key;
+        } else if (l16 % kLanesPerQuery == 0) {
+          *dst = key;
         }
       }
     }
