@@ -33,6 +33,22 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 
+class nvtx_range:
+    """NVTX range around one phase of the harness, the way the reference's profiling scripts mark
+    theirs (torch_topk_nvtx.py:102-123, baseline_1.py:32-41,133-143)."""
+
+    def __init__(self, name: str):
+        self.name = name
+
+    def __enter__(self):
+        if torch.cuda.is_available():
+            torch.cuda.nvtx.range_push(self.name)
+
+    def __exit__(self, *exc):
+        if torch.cuda.is_available():
+            torch.cuda.nvtx.range_pop()
+
+
 def measured_peak_gbs():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -251,21 +267,25 @@ def phase_breakdown(step, steps):
     (gemv_profile_split.cu: GEMV alone, then with the selection): the same launch repeated with
     parts of the kernel switched off through the library's RA_DEBUG_FLAGS tuning aid (1 = no
     scoring, 4 = no list appends, 8 = no list cuts, 16 = return before select + softmax.V).  The
-    outputs of those launches are meaningless; only their durations are used."""
+    outputs of those launches are meaningless; only their durations are used.  The switches exist
+    only in the tuning build of the library, which these launches go through."""
+    from topk_attn_b200 import capi
+
     def timed(flags):
         if flags:
             os.environ["RA_DEBUG_FLAGS"] = str(flags)
         else:
             os.environ.pop("RA_DEBUG_FLAGS", None)
-        for _ in range(3):
-            step()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
-        e0.record()
-        for _ in range(steps):
-            step()
-        e1.record()
-        torch.cuda.synchronize()
+        with capi.tuning_library(), nvtx_range(f"phase flags={flags}"):
+            for _ in range(3):
+                step()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(steps):
+                step()
+            e1.record()
+            torch.cuda.synchronize()
         return e0.elapsed_time(e1) * 1e3 / steps
     try:
         stream = timed(1 | 4 | 8 | 16)
@@ -317,24 +337,34 @@ def run_ours(args):
     def step():
         op(q)
 
-    for _ in range(max(args.warmup, 3)):
-        step()
-    ops.check_status(dev)
-    torch.cuda.synchronize()
-    small = w.algorithmic_bytes() <= (256 << 20)     # would sit in the 126 MB L2
     from topk_attn_b200 import capi
     count = capi.lib().ra_launch_count                # kernels launched by the library so far
     sampler = ClockSampler(physical_gpu_index(local))
+    sampler.start()
+    with nvtx_range("warmup"):
+        # the asked-for warm-up steps, then more until the GPU has been busy for 0.3 s, so that the
+        # clock sampler sees the clocks under load even when the timed region is short
+        t_w = time.perf_counter()
+        for _ in range(max(args.warmup, 3)):
+            step()
+        torch.cuda.synchronize()
+        while time.perf_counter() - t_w < 0.3:
+            for _ in range(10):
+                step()
+            torch.cuda.synchronize()
+    ops.check_status(dev)
+    torch.cuda.synchronize()
+    small = w.algorithmic_bytes() <= (256 << 20)     # would sit in the 126 MB L2
     if not small:
-        sampler.start()
         evs = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
         torch.cuda.synchronize()
         c0 = count()
-        evs[0].record()
-        for i in range(args.steps):
-            step()
-            evs[i + 1].record()
-        torch.cuda.synchronize()
+        with nvtx_range("timed steps"):
+            evs[0].record()
+            for i in range(args.steps):
+                step()
+                evs[i + 1].record()
+            torch.cuda.synchronize()
         gpu_launches = count() - c0
         clocks = sampler.stop()
         total_ms = evs[0].elapsed_time(evs[-1])
@@ -357,7 +387,6 @@ def run_ours(args):
             gpu_launches = (count() - c0) * args.steps   # every replay runs the captured launches
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
-        sampler.start()
         pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
                  for _ in range(args.steps)]
         for a, bq in pairs:
@@ -384,12 +413,13 @@ def run_ours(args):
         out_host.copy_(out, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
-    for _ in range(3):
-        e2e_step()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        e2e_step()
-    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    with nvtx_range("end-to-end steps"):
+        for _ in range(3):
+            e2e_step()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e_step()
+        e2e_s = (time.perf_counter() - t0) / e2e_steps
 
     tokens = w.batch * w.n_tokens
     alg_bytes = w.algorithmic_bytes()
@@ -400,7 +430,8 @@ def run_ours(args):
         cw, what, cpu_t = None, "skipped (--no-cpu)", None
     else:
         cw, what = cpu_sample(args.workload)
-        cpu_t = time_cpu_oracle(cw, 2)
+        with nvtx_range("cpu baseline"):
+            cpu_t = time_cpu_oracle(cw, 2)
     line = {
         "metric": "tokens_scanned_per_s", "value": tokens / (per_ms * 1e-3), "unit": "tokens/s",
         "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
@@ -433,9 +464,27 @@ def run_ours(args):
     traffic_file = os.path.join(ROOT, "profiles", "traffic.json")
     if os.path.exists(traffic_file):
         try:
-            line["roofline"]["traffic"] = json.load(open(traffic_file)).get(args.workload)
+            t = json.load(open(traffic_file)).get(args.workload)
+            if isinstance(t, dict):
+                line["roofline"]["traffic"] = t.get("bytes")
+                line["roofline"]["traffic_source"] = t.get("source")
+            else:
+                line["roofline"]["traffic"] = t
         except Exception:
             pass
+    if args.workload == "cfg2" and not args.no_cfg4:
+        # configuration 4 on this one GPU: the base of the strong-scaling series that
+        # `--gpus 2|4|8` continues; same record, same on-device check of the result
+        from topk_attn_b200 import sharded
+        del w, q, k, v, out, q_dev
+        torch.cuda.empty_cache()
+        with nvtx_range("cfg4 on one GPU"):
+            line["cfg4_strong"] = sharded.bench_long_context(0, 1, dev, min(args.steps, 100),
+                                                             args.warmup, peak)
+        if not line["cfg4_strong"]["parity"]["ok"]:
+            print(json.dumps(line))
+            raise SystemExit("parity check of configuration 4 failed: " +
+                             json.dumps(line["cfg4_strong"]["parity"]))
     print(json.dumps(line))
 
 
@@ -447,6 +496,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling)")
+    ap.add_argument("--no-cfg4", action="store_true",
+                    help="skip the configuration-4 strong-scaling record that follows the headline run")
     ap.add_argument("--phases", action="store_true",
                     help="also time the fused kernel with selection / attention switched off")
     args = ap.parse_args()

@@ -98,3 +98,64 @@ def test_extension_module_is_built_with_the_reference_names():
              ("", "_global", "_pipelined", "_pipelined_global", "_two_kernels", "_gather_baseline")
              for k in (32, 128, 256, 512, 1024)]
     assert all(hasattr(mod, n) for n in names)
+
+
+def _planner_max_parts(seg_len, topk):
+    """The planner's own acceptance rule for cutting a context into parts, restated: tile heights
+    16..128, at most 16 parts, the tile-rounded part holds k keys and the last part is not empty."""
+    best = 1
+    for tile in (16, 32, 64, 128):
+        for nsplit in range(2, 17):
+            part = -(-(-(-seg_len // nsplit)) // tile) * tile
+            if part < topk:
+                break
+            if part * (nsplit - 1) >= seg_len:
+                continue
+            best = max(best, nsplit)
+    return best
+
+
+def test_workspace_bound_covers_every_plan_the_planner_accepts():
+    """ra_workspace_bytes() must hold the candidate lists of the largest part count any plan may
+    pick, also for context lengths that are no multiple of the split granularity."""
+    from topk_attn_b200 import capi
+    lib = capi.lib()
+    p = capi.RaParams()
+    p.head_dim, p.kv_head_stride, p.num_segments, p.sm_scale = 128, 128, 1, 1.0
+    cases = 0
+    for B, Hq, Hkv in ((1, 32, 32), (1, 32, 8), (2, 8, 8), (4, 16, 2)):
+        p.batch, p.num_q_heads, p.num_kv_heads, p.kv_token_stride = B, Hq, Hkv, Hkv * 128
+        for n in (2000, 4097, 20000, 36000, 65536, 100003, 131072):
+            for k in (1, 32, 500, 2048, 4096):
+                if k > n:
+                    continue
+                p.num_tokens, p.topk = n, k
+                need = lib.ra_workspace_bytes(C.byref(p))
+                lists = B * Hq * _planner_max_parts(n, k) * k * 8
+                assert need >= 256 + lists, (B, Hq, Hkv, n, k, need, lists)
+                cases += 1
+    assert cases > 100
+
+
+def test_tuning_library_is_built_and_default_ignores_overrides():
+    from topk_attn_b200 import capi
+    assert os.path.exists(capi.TUNING_LIB_PATH)
+    default = capi.lib()
+    with capi.tuning_library() as t:
+        assert capi.lib() is t and t is not default
+        assert t.ra_version() == default.ra_version()
+    assert capi.lib() is default
+
+
+def test_setup_ra_build_ext_leaves_an_importable_module():
+    """The reference's flow: `python setup_ra.py build_ext --inplace`, then
+    `import retrieval_attention_cpp` from that directory (retrieval_attn/setup_ra.py:4-24,
+    test_ra.py:80-85)."""
+    import subprocess
+    import sys
+    pkg = os.path.join(ROOT, "topk_attn_b200")
+    subprocess.check_call([sys.executable, "setup_ra.py", "build_ext", "--inplace"], cwd=pkg,
+                          stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
+    code = ("import torch, retrieval_attention_cpp as m; "
+            "assert hasattr(m, 'retrieval_attention_128') and hasattr(m, 'retrieval_attention_pipelined_global_1024')")
+    subprocess.check_call([sys.executable, "-c", code], cwd=pkg)

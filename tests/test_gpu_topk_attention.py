@@ -50,11 +50,14 @@ def test_random_shapes(B, Hq, Hkv, N, k, per_batch):
 ])
 def test_short_segments_on_both_paths(B, Hq, Hkv, N, k, S, per_batch, monkeypatch):
     """Segments of at most 4096 keys go through the score-everything kernel; the streaming kernel
-    stays reachable (RA_NO_DENSE_SELECT) and must agree with the oracle on the same inputs."""
+    stays reachable in the tuning build of the library (RA_NO_DENSE_SELECT) and must agree with the
+    oracle on the same inputs."""
+    from topk_attn_b200 import capi
     q, k_, v = rand_case(B, Hq, Hkv, N, per_batch, seed=N + k + S)
     check_topk_attention(q, k_, v, k, sm_scale=0.7, num_segments=S)
     monkeypatch.setenv("RA_NO_DENSE_SELECT", "1")
-    check_topk_attention(q, k_, v, k, sm_scale=0.7, num_segments=S)
+    with capi.tuning_library():
+        check_topk_attention(q, k_, v, k, sm_scale=0.7, num_segments=S)
 
 
 @pytest.mark.parametrize("scale", [0.25, 1.0 / math.sqrt(128), 2.0])
@@ -145,15 +148,48 @@ def test_selection_only_matches_fused_lists():
     O.check_topk_scores(s, idx.cpu(), sc.cpu(), 700)
 
 
-def test_repeat_gives_same_selection_and_close_output():
+@pytest.mark.parametrize("B,Hq,Hkv,N,topk,S,per_batch", [
+    (2, 8, 8, 20000, 512, 1, True),       # streaming kernel, one launch
+    (1, 8, 8, 65536, 512, 1, False),      # context cut into parts + second stage
+    (1, 32, 8, 40000, 1024, 1, False),    # stored scores
+    (4, 32, 32, 8192, 128, 4, False),     # short segments
+    (2, 8, 8, 32768, 300, 4, True),       # segmented selection on the streaming kernel
+])
+def test_repeat_gives_the_same_bits(B, Hq, Hkv, N, topk, S, per_batch):
+    """Winners are dealt in a fixed order (ascending token id inside a CTA, CTAs in rank order) and
+    ties go to the lower id, so a repeated call returns the same lists in the same order and the
+    same output bits."""
     from topk_attn_b200 import ops
-    q, k, v = rand_case(2, 8, 8, 20000, True, seed=17)
+    q, k, v = rand_case(B, Hq, Hkv, N, per_batch, seed=17)
     dev = torch.device("cuda:0")
-    a = ops.topk_attention(q.to(dev), k.to(dev), v.to(dev), 512, return_indices=True)
-    b = ops.topk_attention(q.to(dev), k.to(dev), v.to(dev), 512, return_indices=True)
+    qd, kd, vd = q.to(dev), k.to(dev), v.to(dev)
+    a = ops.topk_attention(qd, kd, vd, topk, num_segments=S, return_indices=True)
+    b = ops.topk_attention(qd, kd, vd, topk, num_segments=S, return_indices=True)
     ops.check_status(dev)
-    assert torch.equal(a[1].sort(-1).values, b[1].sort(-1).values)
-    assert torch.allclose(a[0].float(), b[0].float(), atol=1e-3, rtol=1e-2)
+    assert torch.equal(a[1], b[1]) and torch.equal(a[2], b[2])
+    assert torch.equal(a[0], b[0])
+
+
+def test_ties_go_to_the_lowest_ids():
+    """Small-integer scores: hundreds of exact ties at the k-th score.  The selection is the first k
+    keys in the order (score descending, id ascending), exactly."""
+    from topk_attn_b200 import ops
+    N, H, k = 30000, 4, 2000
+    g = torch.Generator().manual_seed(9)
+    q = torch.zeros(1, H, 128)
+    q[:, :, 0] = 1.0
+    kk = torch.zeros(N, H, 128)
+    kk[:, :, 0] = torch.randint(0, 25, (N, H), generator=g).float()
+    v = torch.randn(N, H, 128, generator=g)
+    q, kk, v = q.half(), kk.half(), v.half()
+    dev = torch.device("cuda:0")
+    out, idx, sc = ops.topk_attention(q.to(dev), kk.to(dev), v.to(dev), k, sm_scale=0.05,
+                                      return_indices=True)
+    ops.check_status(dev)
+    s = O.full_scores(q, kk)                                   # exact small integers
+    order = torch.sort(s, dim=-1, descending=True, stable=True).indices[..., :k]
+    assert torch.equal(idx.cpu().long().sort(-1).values, order.sort(-1).values)
+    O.check_output(O.gathered_attention(q, kk, v, idx.cpu().long(), 0.05), out)
 
 
 def test_golden_legacy_outputs(golden_dir):
@@ -199,12 +235,59 @@ def test_bad_arguments_are_rejected():
     assert capi.lib().ra_topk_attention(None) == capi.RA_ERR_INVALID_ARGUMENT
 
 
-def test_global_candidate_lists(monkeypatch, capfd):
-    """Four queries per K row with k = 4096 need more list space than shared memory has: the lists
-    move to the workspace.  The plan line proves that this path ran."""
-    monkeypatch.setenv("RA_FORCE_QSPLIT", "1")
+def test_candidate_lists_with_several_queries_per_row(monkeypatch, capfd):
+    """The streaming kernel with tensor-core scoring and per-query candidate lists (the route of
+    segmented selections on long inputs) stays reachable for a global selection in the tuning
+    build; the plan line proves that this path ran."""
+    from topk_attn_b200 import capi
+    monkeypatch.setenv("RA_NO_SCORE_STORE", "1")
     monkeypatch.setenv("RA_VERBOSE", "1")
     q, k, v = rand_case(1, 8, 2, 50048, False, seed=21)
-    check_topk_attention(q, k, v, 4096, sm_scale=0.7)
+    with capi.tuning_library():
+        check_topk_attention(q, k, v, 1024, sm_scale=0.7)
     err = capfd.readouterr().err
-    assert "glists=1" in err, err[-400:]
+    assert "nq=4" in err and "score store" not in err, err[-400:]
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,N,k", [
+    (1, 8, 8, 20000, 2048),      # context length that is no multiple of the split granularity
+    (1, 4, 4, 36000, 4096),
+    (1, 16, 2, 2000, 32),        # eight queries per row
+    (1, 8, 2, 20000, 500),       # stored scores and histograms
+])
+def test_exact_size_workspace_is_never_overrun(B, Hq, Hkv, N, k):
+    """A caller that allocates exactly ra_workspace_bytes() must be safe: a guard pattern behind
+    the workspace stays untouched and the result still matches the oracle."""
+    import ctypes as C
+    from topk_attn_b200 import capi
+    lib = capi.lib()
+    dev = torch.device("cuda:0")
+    q, k_, v = rand_case(B, Hq, Hkv, N, False, seed=N)
+    qd, kd, vd = q.to(dev), k_.to(dev), v.to(dev)
+    out = torch.empty_like(qd)
+    idx = torch.empty(B, Hq, k, dtype=torch.int32, device=dev)
+    sc = torch.empty(B, Hq, k, dtype=torch.float32, device=dev)
+    p = capi.RaParams()
+    p.q, p.k, p.v, p.out = qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), out.data_ptr()
+    p.batch, p.num_q_heads, p.num_kv_heads, p.head_dim, p.num_tokens = B, Hq, Hkv, 128, N
+    p.kv_batch_stride, p.kv_token_stride, p.kv_head_stride = 0, Hkv * 128, 128
+    p.topk, p.num_segments, p.sm_scale = k, 1, 1.0
+    p.out_indices, p.out_scores = idx.data_ptr(), sc.data_ptr()
+    p.stream = torch.cuda.current_stream().cuda_stream
+    need = lib.ra_workspace_bytes(C.byref(p))
+    guard = 1 << 20
+    buf = torch.zeros(need + guard + 256, dtype=torch.uint8, device=dev)
+    off = (-buf.data_ptr()) % 256
+    buf[off + need:].fill_(0xAB)
+    p.workspace, p.workspace_bytes = buf.data_ptr() + off, need
+    capi.check(lib.ra_topk_attention(C.byref(p)))
+    capi.check(lib.ra_check_status(p.workspace, p.stream))
+    assert bool((buf[off + need:] == 0xAB).all()), "a kernel wrote past ra_workspace_bytes()"
+    s = O.full_scores(q, k_)
+    ref, _, _ = O.topk_sparse_attention(q, k_, v, k, 1.0, scores=s)
+    O.check_index_sets(s, idx.cpu(), k)
+    O.check_output(ref, out)
+    # a workspace that only holds the status block is refused when the plan needs lists
+    p.workspace_bytes = 256
+    st = lib.ra_topk_attention(C.byref(p))
+    assert st in (capi.RA_OK, capi.RA_ERR_WORKSPACE)

@@ -22,8 +22,11 @@ LIBDIR = os.path.join(PKG, "lib")
 LIB = os.path.join(LIBDIR, "libtopk_attn_b200.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
-CU_SOURCES = ["api.cu", "scan_select.cu", "merge_attend.cu", "gather_attend.cu", "flash_decode.cu",
-              "center_select.cu", "dense_select.cu"]
+TUNING_LIB = os.path.join(LIBDIR, "libtopk_attn_b200_tuning.so")
+CU_SOURCES = ["api.cu", "scan_select.cu", "scan_store.cu", "select_stored.cu", "merge_attend.cu",
+              "gather_attend.cu", "flash_decode.cu", "center_select.cu", "dense_select.cu"]
+# sources that read the route / phase overrides when compiled with -DRA_TUNING
+TUNING_SOURCES = ["api.cu", "scan_select.cu"]
 
 
 def _newer(target: str, deps) -> bool:
@@ -41,18 +44,14 @@ def _all_deps():
     return deps
 
 
-def build_library(force: bool = False, verbose: bool = False) -> str:
-    os.makedirs(LIBDIR, exist_ok=True)
-    objdir = os.path.join(PKG, "build")
+def _compile(sources, objdir, extra, deps, force, verbose):
     os.makedirs(objdir, exist_ok=True)
-    deps = _all_deps()
-    objs = []
-    procs = []
-    for src in CU_SOURCES:
+    objs, procs = [], []
+    for src in sources:
         obj = os.path.join(objdir, src.replace(".cu", ".o"))
         objs.append(obj)
         if force or _newer(obj, deps):
-            cmd = [NVCC, *ARCH, "-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC",
+            cmd = [NVCC, *ARCH, "-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", *extra,
                    "-I", os.path.join(ROOT, "include"), "-I", CSRC, "-c",
                    os.path.join(CSRC, src), "-o", obj]
             if verbose:
@@ -61,9 +60,23 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
     for src, pr in procs:
         if pr.wait() != 0:
             raise RuntimeError(f"nvcc failed on {src}")
-    if force or procs or _newer(LIB, objs):
-        cmd = [NVCC, *ARCH, "-shared", "-o", LIB, *objs, "-cudart", "static"]
-        subprocess.check_call(cmd)
+    return objs, bool(procs)
+
+
+def build_library(force: bool = False, verbose: bool = False) -> str:
+    """The C-ABI library, and beside it the tuning build: the same kernels with the route and
+    phase overrides (RA_FORCE_*, RA_NO_*, RA_DEBUG_FLAGS) compiled in, for A/B tests and the
+    bench's phase profile.  The default library reads no such variable."""
+    os.makedirs(LIBDIR, exist_ok=True)
+    deps = _all_deps()
+    objs, fresh = _compile(CU_SOURCES, os.path.join(PKG, "build"), [], deps, force, verbose)
+    if force or fresh or _newer(LIB, objs):
+        subprocess.check_call([NVCC, *ARCH, "-shared", "-o", LIB, *objs, "-cudart", "static"])
+    tobjs, tfresh = _compile(TUNING_SOURCES, os.path.join(PKG, "build", "tuning"), ["-DRA_TUNING"],
+                             deps, force, False)
+    tall = tobjs + [o for o, src in zip(objs, CU_SOURCES) if src not in TUNING_SOURCES]
+    if force or fresh or tfresh or _newer(TUNING_LIB, tall):
+        subprocess.check_call([NVCC, *ARCH, "-shared", "-o", TUNING_LIB, *tall, "-cudart", "static"])
     return LIB
 
 
@@ -92,7 +105,7 @@ def build_extension(force: bool = False) -> str:
     tlib = os.path.join(os.path.dirname(torch.__file__), "lib")
     cmd += ["-L", tlib, "-lc10", "-ltorch_cpu", "-ltorch", "-ltorch_python", "-lc10_cuda",
             "-L", LIBDIR, "-ltopk_attn_b200",
-            f"-Wl,-rpath,{tlib}", "-Wl,-rpath,$ORIGIN/lib"]
+            f"-Wl,-rpath,{tlib}", "-Wl,-rpath,$ORIGIN/lib", f"-Wl,-rpath,{LIBDIR}"]
     subprocess.check_call(cmd)
     return out
 

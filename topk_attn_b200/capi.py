@@ -5,11 +5,13 @@ import of any operator fails loudly; there is no Python or CPU fallback.
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes as C
 import os
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG, "lib", "libtopk_attn_b200.so")
+TUNING_LIB_PATH = os.path.join(_PKG, "lib", "libtopk_attn_b200_tuning.so")
 
 RA_OK = 0
 RA_ERR_INVALID_ARGUMENT = 1
@@ -128,6 +130,27 @@ def lib() -> C.CDLL:
         _lib = C.CDLL(LIB_PATH)
         _declare(_lib)
     return _lib
+
+
+_tuning_lib = None
+
+
+@contextlib.contextmanager
+def tuning_library():
+    """Inside the block every operator runs on the tuning build of the library, the one that
+    honours the route and phase overrides (RA_FORCE_*, RA_NO_*, RA_DEBUG_FLAGS, RA_VERBOSE per
+    call).  For A/B tests and phase timing; the default library ignores those variables."""
+    global _lib, _tuning_lib
+    if _tuning_lib is None:
+        if not os.path.exists(TUNING_LIB_PATH):
+            raise ImportError(f"{TUNING_LIB_PATH} is missing: run `python -m topk_attn_b200.build`")
+        _tuning_lib = C.CDLL(TUNING_LIB_PATH)
+        _declare(_tuning_lib)
+    prev, _lib = _lib, _tuning_lib
+    try:
+        yield _tuning_lib
+    finally:
+        _lib = prev
 
 
 def _declare(l: C.CDLL) -> None:

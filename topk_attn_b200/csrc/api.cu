@@ -17,6 +17,7 @@
 #include "gather_attend.cuh"
 #include "merge_attend.cuh"
 #include "scan_select.cuh"
+#include "scan_store.cuh"
 
 namespace ra {
 int scan_max_active_clusters(int hg, int nq, int cluster, size_t smem, int threads);
@@ -71,21 +72,56 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
+// Route and geometry overrides (RA_FORCE_*, RA_NO_*, RA_DEBUG_FLAGS) exist only in a library built
+// with -DRA_TUNING (lib/libtopk_attn_b200_tuning.so, used by the A/B tests and the phase profile
+// of the bench); the default build reads no environment variable on the call path.
+#ifdef RA_TUNING
+const char* tuning_env(const char* name) { return getenv(name); }
+bool verbose_plan() { return getenv("RA_VERBOSE") != nullptr; }
+#else
+const char* tuning_env(const char*) { return nullptr; }
+bool verbose_plan() {
+  static const bool v = getenv("RA_VERBOSE") != nullptr;   // read once, when first asked
+  return v;
+}
+#endif
+
+// Multiprocessors of the current device (queried once per device).
+int sm_count() {
+  static std::mutex mu;
+  static int cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    (void)cudaGetLastError();
+    return 148;
+  }
+  std::lock_guard<std::mutex> g(mu);
+  if (!cached[dev]) {
+    int v = 0;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) {
+      (void)cudaGetLastError();
+      v = 148;
+    }
+    cached[dev] = v;
+  }
+  return cached[dev];
+}
+
+// Parameters of the planner's time model: what the whole device and one multiprocessor stream from
+// HBM.  They rank launch geometries against each other; absolute accuracy is not needed.
+constexpr double kModelHbmBytesPerSec = 6.5e12;
+constexpr double kModelSmBytesPerSec = 75e9;
+
 constexpr size_t kSmemBudget = 227 * 1024;
 constexpr size_t kStatusBytes = 256;
 constexpr int kMaxSplit = 16;  // parts one head's context may be cut into
 
-// Candidate lists of nl queries x k keys that may not fit in shared memory next to the pipeline.
-constexpr int kMaxSpillGrid = 304;
-constexpr int kSpillCapFactor = 4;  // capacity of a global candidate list in units of k
-static bool lists_may_spill(int nl, int topk) { return (size_t)nl * topk * 16 > 96 * 1024; }
 
 struct Plan {
   bool ok = false;
   int hg = 0, nq = 0, bshare = 1, nq_valid = 1, qsplit = 1, nq_cta = 1;
   int cluster = 1, nsplit = 1, cap = 0, nstages = 0, per = 0, part_len = 0, grid = 0;
   int groups = 2, rendezvous = 4;
-  bool global_lists = false;  // candidate lists live in the workspace instead of shared memory
   size_t smem = 0;
   // second stage (only when parts > 1)
   int cluster2 = 1, cap2 = 0, per2 = 0;
@@ -115,10 +151,52 @@ bool combo_built(int hg, int nq) {
   return false;
 }
 
+// Most parts the planner may cut one segment into: the largest nsplit that make_plan() accepts for
+// any tile height (its own predicate: the tile-rounded part holds k keys and the last part is not
+// empty).
+int max_parts(int seg_len, int topk) {
+  int best = 1;
+  for (int T : {16, 32, 64, 128})
+    for (int nsplit = 2; nsplit <= kMaxSplit; ++nsplit) {
+      const int part_len = ceil_div(ceil_div(seg_len, nsplit), T) * T;
+      if (part_len < topk) break;
+      if ((long long)part_len * (nsplit - 1) >= seg_len) continue;
+      best = std::max(best, nsplit);
+    }
+  return best;
+}
+
+// Queries that share a K row: batch rows on one shared cache times the GQA group, at most 8.
+int shared_queries(const Shape& s, int* bshare_out = nullptr) {
+  const int group = s.hq / s.hkv;
+  int bshare = 1;
+  if (!s.per_batch && !(s.fused_ok & 2))
+    for (int b = 1; b <= s.batch; ++b)
+      if (s.batch % b == 0 && b * group <= 8) bshare = b;
+  if (bshare_out) *bshare_out = bshare;
+  return bshare * group;
+}
+
+// Layout of the workspace: [status block][candidate lists of `parts` parts][stored score keys and
+// coarse histograms].  Offsets are multiples of 256 bytes.
+size_t cand_bytes(const Shape& s, int parts) {
+  return ((size_t)s.batch * s.hq * parts * s.topk * 8 + 255) & ~size_t(255);
+}
+int store_pitch(int n) { return (n + 127) & ~127; }
+size_t store_keys_bytes(const Shape& s) {
+  return ((size_t)s.batch * s.hq * store_pitch(s.n) * 4 + 255) & ~size_t(255);
+}
+size_t store_hist_bytes(const Shape& s, int parts) {
+  return (size_t)s.batch * s.hq * parts * kHistBins * 4;
+}
+// The score-store route is taken for one global selection with several queries per K row (see
+// run_store); its scratch replaces the candidate lists.
+bool store_shape(const Shape& s) { return s.segments == 1 && !(s.fused_ok & 6) && shared_queries(s) > 1; }
+
 // Second-stage geometry for m_total candidates per row with `topk` winners.
 bool plan_merge(int m_total, int topk, Plan& pl) {
   int f_c2 = 0;
-  if (const char* f = getenv("RA_FORCE_MERGE_CLUSTER")) f_c2 = atoi(f);
+  if (const char* f = tuning_env("RA_FORCE_MERGE_CLUSTER")) f_c2 = atoi(f);
   for (int c2 : {1, 2, 4, 8}) {
     if (f_c2 && c2 != f_c2) continue;
     const int cap2 = ceil_div(m_total, c2), per2 = ceil_div(topk, c2);
@@ -139,7 +217,7 @@ bool plan_merge(int m_total, int topk, Plan& pl) {
 // form.
 cudaError_t dispatch_merge(MergeParams& mp, int rows, const Plan& pl, cudaStream_t stream) {
   const size_t one = merge_attend_cta_smem_bytes(mp.m_total, mp.m.topk);
-  if (one <= kSmemBudget && !getenv("RA_FORCE_MERGE_CLUSTER")) {
+  if (one <= kSmemBudget && !tuning_env("RA_FORCE_MERGE_CLUSTER")) {
     mp.m.cluster = 1;
     return launch_merge_attend_cta(mp, rows, one, stream);
   }
@@ -160,20 +238,15 @@ Plan make_plan(const Shape& s) {
   Plan best;
   // RA_FORCE_PLAN="hg,cluster,nsplit" pins the geometry (0 = free); for tuning only
   int f_hg = 0, f_cluster = 0, f_nsplit = 0, f_stages = 0;
-  if (const char* f = getenv("RA_FORCE_PLAN"))
+  if (const char* f = tuning_env("RA_FORCE_PLAN"))
     sscanf(f, "%d,%d,%d,%d", &f_hg, &f_cluster, &f_nsplit, &f_stages);
-  const int group = s.hq / s.hkv;
-  int bshare = 1;
   const bool own_parts = (s.fused_ok & 2) != 0;
-  if (!s.per_batch && !own_parts) {
-    for (int b = 1; b <= s.batch; ++b)
-      if (s.batch % b == 0 && b * group <= 8) bshare = b;
-  }
-  const int nq_valid = bshare * group;
+  int bshare = 1;
+  const int nq_valid = shared_queries(s, &bshare);
   const int seg_len = s.n / s.segments;
-  const double hbm = 6.5e12, per_sm = 75e9;
+  const double hbm = kModelHbmBytesPerSec, per_sm = kModelSmBytesPerSec;
   int f_qsplit = 0;
-  if (const char* f = getenv("RA_FORCE_QSPLIT")) f_qsplit = atoi(f);
+  if (const char* f = tuning_env("RA_FORCE_QSPLIT")) f_qsplit = atoi(f);
   for (int qsplit : {1, 2, 4, 8})
   for (int hg : {8, 4, 2, 1}) {
     if (nq_valid % qsplit || (f_qsplit && qsplit != f_qsplit)) continue;
@@ -185,7 +258,7 @@ Plan make_plan(const Shape& s) {
     if (s.head_major && hg != 1) continue;
     if (f_hg && hg != f_hg) continue;
     // several queries per K row are scored on the tensor cores, one kv head per CTA
-    if (nq > 1 && hg != 1 && !getenv("RA_NO_MMA")) continue;
+    if (nq > 1 && hg != 1 && !tuning_env("RA_NO_MMA")) continue;
     const int nl = hg * nq, T = kTileRows / hg;
     const int groups = (s.batch / bshare) * (s.hkv / hg) * s.segments * qsplit;
     for (int cluster : {1, 2, 4, 8, 16}) {
@@ -211,7 +284,6 @@ Plan make_plan(const Shape& s) {
         Geo geos[4];
         int ngeo = 0;
         static const double kSlow[4] = {1.0, 1.05, 1.2, 1.35};
-        bool glists = false;
         // one query per K row: scoring is latency-bound, two warp groups and deep rings help;
         // several queries per row (tensor-core scoring): one group and roomier lists win
         static const int kGeo1[4][2] = {{2, 6}, {2, 4}, {1, 3}, {1, 2}};
@@ -236,19 +308,10 @@ Plan make_plan(const Shape& s) {
           }
           if (ngeo && (tiles > 32 || f_stages)) break;
         }
-        // Several large lists per CTA leave too little room next to the pipeline: they move to
-        // global memory (deep pipeline, capacity 4k, few cuts).
-        if (nq > 1 && lists_may_spill(nl, s.topk) && !getenv("RA_NO_GLOBAL_LISTS") &&
-            
-            groups * nsplit * cluster <= kMaxSpillGrid && (size_t)kMaxStages * kStageBytes >= scratch) {
-          geos[0] = Geo{kMaxStages, kSpillCapFactor * s.topk, 2, 4, 1.0};
-          ngeo = 1;
-          glists = true;
-        }
         for (int gx = 0; gx < ngeo; ++gx) {
         const int nstages = geos[gx].nstages, cap = geos[gx].cap, cgroups = geos[gx].cgroups,
                   rdv = geos[gx].rdv;
-        const size_t smem = scan_smem_bytes(glists ? 0 : nl, cap, nstages);
+        const size_t smem = scan_smem_bytes(nl, cap, nstages);
         const int nclusters = groups * nsplit;
         const int active = scan_max_active_clusters(hg, nq, cluster, smem, 32 * (8 * cgroups + 1));
         if (active <= 0) continue;
@@ -277,7 +340,7 @@ Plan make_plan(const Shape& s) {
         pl.hg = hg; pl.nq = nq; pl.bshare = bshare; pl.nq_valid = nq_valid;
         pl.qsplit = qsplit; pl.nq_cta = nq_cta;
         pl.cluster = cluster; pl.nsplit = nsplit; pl.cap = cap; pl.nstages = nstages;
-        pl.groups = cgroups; pl.rendezvous = rdv; pl.global_lists = glists;
+        pl.groups = cgroups; pl.rendezvous = rdv;
         pl.per = per; pl.part_len = part_len; pl.grid = nclusters * cluster; pl.smem = smem;
         pl.cost = cost;
         if (two_stage && !plan_merge(s.segments * nsplit * s.topk,
@@ -348,19 +411,9 @@ int check_params(const ra_params* p, bool need_v, bool need_out, Checked& c) {
 // Device-independent upper bound of the scratch any plan for this shape may use.
 size_t workspace_bound(const Shape& s) {
   const int seg_len = s.n / s.segments;
-  int maxsplit = 1;
-  if (s.segments == 1) maxsplit = std::max(1, std::min(kMaxSplit, seg_len / std::max(s.topk, 128)));
-  size_t w = kStatusBytes + (size_t)s.batch * s.hq * s.segments * maxsplit * s.topk * 8;
-  w = (w + 255) & ~size_t(255);
-  // global candidate lists are only used when several queries share a K row
-  const int group = s.hq / s.hkv;
-  int bshare = 1;
-  if (!s.per_batch && !(s.fused_ok & 2))
-    for (int b = 1; b <= s.batch; ++b)
-      if (s.batch % b == 0 && b * group <= 8) bshare = b;
-  const int nq_valid = bshare * group;
-  if (nq_valid > 1 && lists_may_spill(next_pow2(nq_valid), s.topk))
-    w += (size_t)kMaxSpillGrid * next_pow2(nq_valid) * kSpillCapFactor * s.topk * 8;
+  const int maxsplit = s.segments == 1 ? max_parts(seg_len, s.topk) : 1;
+  size_t w = kStatusBytes + cand_bytes(s, s.segments * maxsplit);
+  if (store_shape(s)) w = std::max(w, kStatusBytes + store_keys_bytes(s) + store_hist_bytes(s, kMaxSplit));
   return w;
 }
 
@@ -415,7 +468,11 @@ struct PartIds {
   int expand_clen = 0;
   int* expand_out = nullptr;
   int* expand_ids = nullptr;
+  // status block of the caller's workspace when p->workspace is only an inner slice of it
+  unsigned* status = nullptr;
 };
+
+int run_store(const ra_params* p, const Shape& s, int group, bool attend, unsigned* status);
 
 int run(const ra_params* p, bool attend, const PartIds* ext = nullptr) {
   Checked c;
@@ -427,26 +484,9 @@ int run(const ra_params* p, bool attend, const PartIds* ext = nullptr) {
   // scan kernel itself must produce the final winners)
   s.fused_ok = 1 | ((ext && ext->ids) ? 2 : 0) | ((ext && ext->expand_out) ? 4 : 0);
   const int real_tokens = (ext && ext->ids) ? ext->real_tokens : s.n;
-  const Plan pl = make_plan(s);
-  if (!pl.ok) return unsupported("no launch geometry fits these sizes");
-  const bool verbose = getenv("RA_VERBOSE") != nullptr;
-  static thread_local Shape last_shown = {};
-  const bool show = verbose && ((last_shown < s) || (s < last_shown));
-  if (show) last_shown = s;
-  if (show)
-    fprintf(stderr,
-            "[topk_attn_b200] plan: hg=%d nq=%d(valid %d, qsplit %d) bshare=%d cluster=%d nsplit=%d cap=%d "
-            "stages=%d groups=%d rdv=%d glists=%d per=%d part_len=%d grid=%d smem=%zu | merge: cluster=%d cap=%d smem=%zu | "
-            "model %.1f us\n",
-            pl.hg, pl.nq, pl.nq_valid, pl.qsplit, pl.bshare, pl.cluster, pl.nsplit, pl.cap, pl.nstages, pl.groups,
-            pl.rendezvous, (int)pl.global_lists, pl.per,
-            pl.part_len, pl.grid, pl.smem, pl.cluster2, pl.cap2, pl.smem2, pl.cost * 1e6);
-  if (p->workspace_bytes < workspace_bound(s)) {
-    g_last_error = "workspace smaller than ra_workspace_bytes()";
-    return RA_ERR_WORKSPACE;
-  }
+  const bool verbose = verbose_plan();
   cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
-  unsigned* status = static_cast<unsigned*>(p->workspace);
+  unsigned* status = (ext && ext->status) ? ext->status : static_cast<unsigned*>(p->workspace);
   // Short segments: score every key into shared memory and select afterwards (no candidate lists),
   // then one pass over the V rows of the lists.
   const int seg_len = s.n / s.segments;
@@ -456,10 +496,14 @@ int run(const ra_params* p, bool attend, const PartIds* ext = nullptr) {
       if (s.batch % b == 0 && b * c.group <= 4) dense_bshare = b;
   // (one query per K row and one segment: the fused single launch of the scan kernel is quicker)
   if (!ext && seg_len <= kDenseMaxSeg && c.group <= 4 && (s.segments > 1 || dense_bshare * c.group > 1) &&
-      !getenv("RA_NO_DENSE_SELECT")) {
+      !tuning_env("RA_NO_DENSE_SELECT")) {
     const int bshare = dense_bshare;
     const int nq_valid = bshare * c.group, nq = next_pow2(nq_valid);
     const size_t lists = (size_t)s.batch * s.hq * s.segments * s.topk;
+    if (p->workspace_bytes < kStatusBytes + lists * 8) {
+      g_last_error = "workspace smaller than ra_workspace_bytes()";
+      return RA_ERR_WORKSPACE;
+    }
     float* l_score = reinterpret_cast<float*>(static_cast<char*>(p->workspace) + kStatusBytes);
     int* l_idx = reinterpret_cast<int*>(l_score + lists);
     DenseSelectParams dp;
@@ -489,15 +533,36 @@ int run(const ra_params* p, bool attend, const PartIds* ext = nullptr) {
                       dp.out_score, (long long)s.hq * per_row, per_row, (int)per_row, 0, nullptr,
                       p->sm_scale, status, true, stream, p->index_base);
   }
+  // Several queries per K row and one global selection: scores are stored and selected afterwards.
+  if (!ext && store_shape(s) && !tuning_env("RA_NO_SCORE_STORE")) return run_store(p, s, c.group, attend, status);
+
+  const Plan pl = make_plan(s);
+  if (!pl.ok) return unsupported("no launch geometry fits these sizes");
+  static thread_local Shape last_shown = {};
+  const bool show = verbose && ((last_shown < s) || (s < last_shown));
+  if (show) last_shown = s;
+  if (show)
+    fprintf(stderr,
+            "[topk_attn_b200] plan: hg=%d nq=%d(valid %d, qsplit %d) bshare=%d cluster=%d nsplit=%d cap=%d "
+            "stages=%d groups=%d rdv=%d per=%d part_len=%d grid=%d smem=%zu | merge: cluster=%d cap=%d smem=%zu | "
+            "model %.1f us\n",
+            pl.hg, pl.nq, pl.nq_valid, pl.qsplit, pl.bshare, pl.cluster, pl.nsplit, pl.cap, pl.nstages, pl.groups,
+            pl.rendezvous, pl.per,
+            pl.part_len, pl.grid, pl.smem, pl.cluster2, pl.cap2, pl.smem2, pl.cost * 1e6);
   const int parts = s.segments * pl.nsplit;
   const bool two_stage = parts > 1;
+  // the candidate lists of this plan must fit in what the caller gave
+  if (p->workspace_bytes < kStatusBytes + (two_stage ? cand_bytes(s, parts) : 0)) {
+    g_last_error = "workspace smaller than ra_workspace_bytes()";
+    return RA_ERR_WORKSPACE;
+  }
   float* ws_score = reinterpret_cast<float*>(static_cast<char*>(p->workspace) + kStatusBytes);
   int* ws_idx = reinterpret_cast<int*>(ws_score + (size_t)s.batch * s.hq * parts * s.topk);
 
   ScanParams sp;
   memset(&sp, 0, sizeof sp);
   // several queries per K row (GQA group, batch rows on one cache): score on the tensor cores
-  const bool swizzled = pl.hg == 1 && pl.nq > 1 && !getenv("RA_NO_MMA");
+  const bool swizzled = pl.hg == 1 && pl.nq > 1 && !tuning_env("RA_NO_MMA");
   st = encode_kmap(&sp.kmap, p, s, pl.hg, swizzled, real_tokens);
   sp.swizzled = swizzled;
   if (st != RA_OK) return st;
@@ -509,16 +574,12 @@ int run(const ra_params* p, bool attend, const PartIds* ext = nullptr) {
     sp.m.expand_clen = ext->expand_clen; sp.m.expand_out = ext->expand_out;
     sp.m.expand_ids = ext->expand_ids;
   }
-  if (pl.global_lists) {
-    const size_t cand_bytes = ((size_t)kStatusBytes + (size_t)s.batch * s.hq * parts * s.topk * 8 + 255) & ~size_t(255);
-    sp.list_ws = static_cast<unsigned char*>(p->workspace) + cand_bytes;
-  }
   sp.group = c.group; sp.bshare = pl.bshare; sp.nq_valid = pl.nq_valid;
   sp.qsplit = pl.qsplit; sp.nq_cta = pl.nq_cta;
   sp.kv_per_batch = s.per_batch;
   sp.cap = pl.cap; sp.nstages = pl.nstages; sp.groups = pl.groups; sp.rendezvous = pl.rendezvous; sp.nparts = parts; sp.part_len = pl.part_len;
   sp.head_major = s.head_major;
-  if (const char* d = getenv("RA_DEBUG_FLAGS")) sp.debug = atoi(d);
+  if (const char* d = tuning_env("RA_DEBUG_FLAGS")) sp.debug = atoi(d);
   MergeArgs& m = sp.m;
   m.topk = s.topk; m.per = pl.per; m.cluster = pl.cluster;
   m.hq_total = s.hq; m.list_pitch = parts * s.topk; m.list_off = 0;
@@ -581,6 +642,110 @@ int run(const ra_params* p, bool attend, const PartIds* ext = nullptr) {
   mp.m_total = parts * s.topk; mp.cap = pl.cap2; mp.group = c.group;
   e = dispatch_merge(mp, s.batch * s.hq, pl, stream);
   if (e != cudaSuccess) return cuda_fail(e, "merge_attend launch");
+  return RA_OK;
+}
+
+// Several queries per K row, one global selection: scan_store_kernel streams K once and stores every
+// score, select_stored_kernel picks the exact top-k per (batch row, query head) from the stored
+// scores and attends over the winners (or writes them out when attend is false).
+int run_store(const ra_params* p, const Shape& s, int group, bool attend, unsigned* status) {
+  int bshare = 1;
+  const int nq_valid = shared_queries(s, &bshare);
+  const int rows = s.batch * s.hq;
+  const int items = (s.batch / bshare) * s.hkv;   // (batch group, kv head) pairs, each a row of CTAs
+  const int sms = sm_count();
+  // parts of the token axis per item: the count with the lowest modelled stream time
+  int nparts = 1, part_len = store_pitch(s.n);
+  double best = 1e30;
+  for (int ns = 1; ns <= kMaxSplit; ++ns) {
+    const int len = ceil_div(ceil_div(s.n, ns), kTileRows) * kTileRows;
+    if (ns > 1 && (long long)len * (ns - 1) >= s.n) continue;
+    const int grid = items * ns, live = std::min(grid, sms), waves = ceil_div(grid, sms);
+    const double rate = std::min(kModelSmBytesPerSec, kModelHbmBytesPerSec / live);
+    const double cost = waves * ((double)ceil_div(len, kTileRows) * kStageBytes / rate + 4e-6);
+    if (cost < best) {
+      best = cost;
+      nparts = ns;
+      part_len = len;
+    }
+  }
+  if (const char* f = tuning_env("RA_FORCE_STORE_PARTS")) {
+    const int ns = atoi(f);
+    const int len = ceil_div(ceil_div(s.n, std::max(ns, 1)), kTileRows) * kTileRows;
+    if (ns >= 1 && ns <= kMaxSplit && (ns == 1 || (long long)len * (ns - 1) < s.n)) {
+      nparts = ns;
+      part_len = len;
+    }
+  }
+  const size_t need = kStatusBytes + store_keys_bytes(s) + store_hist_bytes(s, nparts);
+  if (p->workspace_bytes < need) {
+    g_last_error = "workspace smaller than ra_workspace_bytes()";
+    return RA_ERR_WORKSPACE;
+  }
+  char* ws = static_cast<char*>(p->workspace);
+  uint32_t* keys_ws = reinterpret_cast<uint32_t*>(ws + kStatusBytes);
+  uint32_t* hist_ws = reinterpret_cast<uint32_t*>(ws + kStatusBytes + store_keys_bytes(s));
+  cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
+
+  StoreParams sp;
+  memset(&sp, 0, sizeof sp);
+  int st = encode_kmap(&sp.kmap, p, s, 1, true, s.n);
+  if (st != RA_OK) return st;
+  sp.q = static_cast<const __half*>(p->q);
+  sp.status = status;
+  sp.keys_ws = keys_ws; sp.hist_ws = hist_ws;
+  sp.batch = s.batch; sp.hq = s.hq; sp.hkv = s.hkv; sp.n_tokens = s.n; sp.n_pad = store_pitch(s.n);
+  sp.group = group; sp.bshare = bshare; sp.nq_valid = nq_valid; sp.kv_per_batch = s.per_batch;
+  sp.nstages = nq_valid <= 4 ? 6 : 4;
+  sp.groups = 2;
+  sp.nparts = nparts; sp.part_len = part_len;
+
+  // selection: a cluster of CTAs per row when there are few rows, each with a candidate list as
+  // large as shared memory allows
+  int c2 = 1;
+  while (c2 < kSelMaxCluster && rows * c2 * 2 <= sms && ceil_div(s.n, c2 * 2) >= 4096) c2 <<= 1;
+  int per2 = 0, cap2 = 0;
+  size_t fixed = 0;
+  for (;; c2 <<= 1) {
+    per2 = ceil_div(s.topk, c2);
+    fixed = select_stored_fixed_smem_bytes(per2);
+    cap2 = fixed < kSmemBudget ? (int)std::min<size_t>(16384, (kSmemBudget - fixed) / 8) : 0;
+    if (cap2 >= s.topk + 512 || c2 >= kSelMaxCluster) break;
+  }
+  if (cap2 < s.topk + 512) return unsupported("topk too large for the stored-score selection");
+  if (verbose_plan()) {
+    static thread_local Shape last_shown = {};
+    if ((last_shown < s) || (s < last_shown)) {
+      last_shown = s;
+      fprintf(stderr,
+              "[topk_attn_b200] plan: score store nq=%d bshare=%d parts=%d part_len=%d grid=%d stages=%d | "
+              "select: cluster=%d cap=%d per=%d | model %.1f us\n",
+              nq_valid, bshare, nparts, part_len, items * nparts, sp.nstages, c2, cap2, per2, best * 1e6);
+    }
+  }
+  cudaError_t e = launch_scan_store(sp, items * nparts, scan_store_smem_bytes(nq_valid, sp.nstages), stream);
+  if (e != cudaSuccess) return cuda_fail(e, "scan_store launch");
+
+  SelectStoredParams qp;
+  memset(&qp, 0, sizeof qp);
+  MergeArgs& m = qp.m;
+  m.topk = s.topk; m.per = per2; m.cluster = c2;
+  m.out_mode = attend ? kOutFinal : kOutNone;
+  m.hq_total = s.hq; m.list_pitch = s.topk; m.list_off = 0; m.index_base = p->index_base;
+  m.own_lo = 0; m.own_hi = 0x7fffffff; m.id_shift = 0;
+  m.n_tokens = s.n; m.status = status;
+  m.sel_idx = p->out_indices; m.sel_score = p->out_scores;
+  m.v = static_cast<const __half*>(p->v);
+  m.v_batch_stride = p->kv_batch_stride; m.v_token_stride = p->kv_token_stride;
+  m.v_head_stride = p->kv_head_stride;
+  m.out = static_cast<__half*>(p->out); m.out_lse = p->out_lse; m.out_partial = nullptr;
+  m.scale_log2e = p->sm_scale * kLog2e; m.sm_scale = p->sm_scale;
+  qp.keys_ws = keys_ws; qp.hist_ws = hist_ws;
+  qp.n_tokens = s.n; qp.n_pad = sp.n_pad; qp.nparts = nparts;
+  qp.chunk = ceil_div(ceil_div(s.n, c2), kTileRows) * kTileRows;
+  qp.cap = cap2; qp.group = group;
+  e = launch_select_stored(qp, rows, fixed + (size_t)cap2 * 8, stream);
+  if (e != cudaSuccess) return cuda_fail(e, "select_stored launch");
   return RA_OK;
 }
 
@@ -682,7 +847,7 @@ static bool plan_gather(int n_entries, int n_src, int rows, int& cluster, int& c
                         size_t& smem) {
   // enough CTAs to fill the machine, not more than 16 rows of K per thread and CTA
   int want = 1;
-  while (want < 8 && (rows * want < 148 || ceil_div(n_entries, want) > 4096)) want <<= 1;
+  while (want < 8 && (rows * want < sm_count() || ceil_div(n_entries, want) > 4096)) want <<= 1;
   for (int c = want; c <= 8; c <<= 1) {
     cap = ceil_div(n_entries, c);
     per = ceil_div(n_entries, c);
@@ -775,7 +940,7 @@ static int center_select(const void* q, const void* centers, int batch, int head
   cp.heads = heads; cp.csz = csz; cp.topc = topc; cp.clen = clen;
   int cluster = 1;
   while (cluster < kCenterMaxCluster && csz > 256 * cluster) cluster <<= 1;
-  if (const char* f = getenv("RA_CENTER_CLUSTER")) {   // tuning aid
+  if (const char* f = tuning_env("RA_CENTER_CLUSTER")) {
     const int c = atoi(f);
     if (c == 1 || c == 2 || c == 4 || c == 8) cluster = c;
   }
@@ -821,7 +986,7 @@ int ra_center_only_topk(const ra_center_params* p) {
   sp.kv_head_stride = (int64_t)p->num_centers * kHeadDim;
   sp.topk = p->top_clusters; sp.num_segments = 1; sp.sm_scale = 1.f;
   sp.workspace = p->workspace; sp.workspace_bytes = tail; sp.stream = p->stream;
-  if (p->num_centers <= kCenterMaxCsz && !getenv("RA_NO_CENTER_SELECT")) {
+  if (p->num_centers <= kCenterMaxCsz && !tuning_env("RA_NO_CENTER_SELECT")) {
     int* ids = p->out_cluster_ids ? p->out_cluster_ids : c_ids;
     int st = center_select(p->q, p->centers, p->batch, p->num_heads, p->num_centers, p->top_clusters,
                            p->cluster_len, ids, c_score, attend ? nullptr : p->out_indices,
@@ -916,7 +1081,7 @@ int ra_two_level_topk(const ra_two_level_params* p) {
   sp.out_indices = c_ids; sp.out_scores = c_score;
   sp.workspace = ws; sp.workspace_bytes = coarse; sp.stream = p->stream;
   int* sorted = p->out_cluster_ids ? p->out_cluster_ids : c_sorted;
-  if (p->num_centers <= kCenterMaxCsz && !getenv("RA_NO_CENTER_SELECT")) {
+  if (p->num_centers <= kCenterMaxCsz && !tuning_env("RA_NO_CENTER_SELECT")) {
     // steps 1 and 2 in one launch
     int st = center_select(p->q, p->centers, p->batch, p->num_heads, p->num_centers, p->top_clusters,
                            p->cluster_len, sorted, nullptr, nullptr, stream);
@@ -941,7 +1106,9 @@ int ra_two_level_topk(const ra_two_level_params* p) {
   fp.sm_scale = p->sm_scale > 0.f ? p->sm_scale : 1.f;
   fp.out_indices = p->out_indices; fp.out_scores = p->out_scores;
   fp.workspace = ws + coarse; fp.workspace_bytes = fine; fp.stream = p->stream;
-  PartIds ext = {sorted, p->num_tokens};
+  PartIds ext;
+  ext.ids = sorted; ext.real_tokens = p->num_tokens;
+  ext.status = static_cast<unsigned*>(p->workspace);   // one status block for every stage
   return run(&fp, attend, &ext);
 }
 
@@ -965,12 +1132,12 @@ int ra_kv_append(void* k_cache, void* v_cache, const void* new_k, const void* ne
   return RA_OK;
 }
 
-// Effective split geometry: split_len is a multiple of the 128-token tile.
-static void flash_geometry(int batch, int hkv, int n, int asked, int& splits, int& split_len) {
+// Effective split geometry: split_len is a multiple of the 128-token tile.  With asked == 0 the
+// library picks about four work items per multiprocessor, never less than two tiles per item.
+static void flash_geometry(int batch, int hkv, int n, int asked, int sms, int& splits, int& split_len) {
   int want = asked;
   if (want <= 0) {
-    // about four work items per SM, never less than two tiles per item
-    want = std::max(1, ceil_div(4 * 148, batch * hkv));
+    want = std::max(1, ceil_div(4 * sms, batch * hkv));
     want = std::min(want, std::max(1, n / (2 * kFdTile)));
   }
   want = std::max(1, std::min(want, ceil_div(n, kFdTile)));
@@ -982,7 +1149,15 @@ size_t ra_flash_workspace_bytes(int32_t batch, int32_t num_q_heads, int32_t num_
                                 int32_t num_tokens, int32_t num_splits) {
   if (batch < 1 || num_q_heads < 1 || num_kv_heads < 1 || num_tokens < 1) return 0;
   int splits, split_len;
-  flash_geometry(batch, num_kv_heads, num_tokens, num_splits, splits, split_len);
+  // device-independent: when the library chooses the splits, room for the count it would pick on a
+  // device with 256 multiprocessors (the count never exceeds the `want` it starts from)
+  constexpr int kMaxSms = 256;
+  flash_geometry(batch, num_kv_heads, num_tokens, num_splits, kMaxSms, splits, split_len);
+  if (num_splits <= 0) {
+    int want = std::max(1, ceil_div(4 * kMaxSms, batch * num_kv_heads));
+    want = std::min(want, std::max(1, num_tokens / (2 * kFdTile)));
+    splits = std::max(splits, std::min(want, ceil_div(num_tokens, kFdTile)));
+  }
   return kStatusBytes + (size_t)splits * batch * num_q_heads * (kHeadDim + 2) * sizeof(float);
 }
 
@@ -1035,7 +1210,7 @@ int ra_flash_decoding(const ra_dense_params* p) {
     }
   }
   int splits, split_len;
-  flash_geometry(p->batch, p->num_kv_heads, p->num_tokens, p->num_splits, splits, split_len);
+  flash_geometry(p->batch, p->num_kv_heads, p->num_tokens, p->num_splits, sm_count(), splits, split_len);
   fp.q = static_cast<const __half*>(p->q);
   fp.partials = reinterpret_cast<float*>(static_cast<char*>(p->workspace) + kStatusBytes);
   fp.status = static_cast<unsigned*>(p->workspace);
@@ -1045,11 +1220,7 @@ int ra_flash_decoding(const ra_dense_params* p) {
   fp.nstages = kFdMaxStages;
   fp.num_items = p->batch * p->num_kv_heads * splits;
   fp.scale_log2e = p->sm_scale * kLog2e;
-  static int sms = [] {
-    int dev = 0, v = 148;
-    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
-    return v;
-  }();
+  const int sms = sm_count();
   const int grid = std::min(fp.num_items, sms);
   cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
   cudaError_t e = launch_flash_decode(fp, grid, flash_decode_smem_bytes(fp.nstages), stream);

@@ -17,22 +17,33 @@
 #include <map>
 #include <mutex>
 #include <string>
+#include <utility>
+#include <vector>
 
 #include "topk_attn_b200.h"
 
 namespace {
 
-// Scratch is owned here (torch's caching allocator), one buffer per device, grown on demand; the
-// C ABI itself never allocates.
-torch::Tensor workspace_for(size_t bytes, const torch::Device& dev) {
+// Scratch is owned here (torch's caching allocator), one buffer per (device, stream), grown on
+// demand; the C ABI itself never allocates.  The entry points are asynchronous on torch's current
+// stream, so calls on two streams of one device must not share scratch.  A buffer that is replaced
+// by a larger one hands over its status block (the sticky bits a kernel may have set) in stream
+// order, and stays alive until the process ends because launches still in flight may use it.
+torch::Tensor workspace_for(size_t bytes, const torch::Device& dev, cudaStream_t stream) {
   static std::mutex mu;
-  static std::map<int, torch::Tensor> cache;
+  static std::map<std::pair<int, cudaStream_t>, torch::Tensor> cache;
+  static std::vector<torch::Tensor> retired;
   std::lock_guard<std::mutex> g(mu);
-  auto it = cache.find(dev.index());
+  const auto key = std::make_pair((int)dev.index(), stream);
+  auto it = cache.find(key);
   if (it == cache.end() || (size_t)it->second.numel() < bytes) {
     auto t = torch::zeros({(int64_t)std::max<size_t>(bytes, 1 << 20)},
                           torch::TensorOptions().dtype(torch::kUInt8).device(dev));
-    cache[dev.index()] = t;
+    if (it != cache.end()) {
+      cudaMemcpyAsync(t.data_ptr(), it->second.data_ptr(), 256, cudaMemcpyDeviceToDevice, stream);
+      retired.push_back(it->second);
+    }
+    cache[key] = t;
     return t;
   }
   return it->second;
@@ -92,7 +103,7 @@ ra_params make_params(const torch::Tensor& q, const torch::Tensor& k, const torc
 void attach_workspace(ra_params& p, const torch::Device& dev, torch::Tensor& keep) {
   size_t need = ra_workspace_bytes(&p);
   if (need == 0) need = 256;  // the entry point reports what is wrong with the shape
-  keep = workspace_for(need, dev);
+  keep = workspace_for(need, dev, static_cast<cudaStream_t>(p.stream));
   p.workspace = keep.data_ptr();
   p.workspace_bytes = (size_t)keep.numel();
 }

@@ -16,20 +16,35 @@ namespace ra {
 
 namespace cg = cooperative_groups;
 
+constexpr int kDetWords = 2048;          // bitmap words of one window of the ordered deal
+constexpr int kDetWindow = kDetWords * 32;
+constexpr int kTagByPosition = 0x7fffffff;   // tag_lo value: a candidate's tag is its list position
+
 struct MergeScratch {
   int hist[2][kMaxLists][256];
   int ghist[kMaxLists][256];
   uint32_t prefix[kMaxLists];
   int remaining[kMaxLists];
   uint32_t counts[kMaxLists][4];  // n_gt, n_eq, best key — read by the other CTAs
-  int ctr_gt[kMaxLists], ctr_eq[kMaxLists];
-  int off_gt[kMaxLists], off_eq[kMaxLists], take_eq[kMaxLists], total_sel[kMaxLists];
+  int off_win[kMaxLists], take_eq[kMaxLists], total_sel[kMaxLists];
   uint32_t maxkey[kMaxLists];
+  // ordered deal: one bit per candidate tag of the current window, exclusive popcount prefix per
+  // word, warp totals of the block scan, and the tag up to which copies of the k-th key are taken
+  uint32_t bits[kDetWords];
+  int wpre[kDetWords];
+  int wsum[kMaxWarps + 2];
+  int cut_tag, cut_found;
   float red[kMaxWarps][kHeadDim];
   float lred[kMaxWarps];
   float o_part[kMaxLists][kHeadDim];  // read by the other CTAs
   float l_part[kMaxLists];            // read by the other CTAs
 };
+
+// Shared memory the cluster code needs in every CTA: its scratch block and the dealt winners of
+// nl lists (per = ceil(topk / cluster) slots each).
+__host__ __device__ inline size_t select_scratch_bytes(int nl, int per) {
+  return (sizeof(MergeScratch) + (size_t)nl * per * 8 + 127) & ~size_t(127);
+}
 
 enum OutMode : int {
   kOutNone = 0,     // only the winner lists are written
@@ -134,13 +149,60 @@ __device__ __forceinline__ void warp_find_digit(const int* hist, int remaining, 
   new_remaining = __shfl_sync(0xffffffffu, nr, src);
 }
 
+// Exclusive prefix of the popcounts of bits[0..nw) into wpre[0..nw); returns their total.  Called
+// by all nthr threads of the CTA (nthr a multiple of 32); wsum holds kMaxWarps + 2 ints.  Ends
+// with the CTA synchronised.
+__device__ __forceinline__ int bitmap_prefix(const uint32_t* bits, int* wpre, int* wsum, int nw,
+                                             int tid, int nthr) {
+  const int lane = tid & 31, warp = tid >> 5, nwarps = nthr >> 5;
+  const int wpt = (nw + nthr - 1) / nthr;
+  const int w0 = min(nw, tid * wpt), w1 = min(nw, w0 + wpt);
+  int s = 0;
+  for (int w = w0; w < w1; ++w) s += __popc(bits[w]);
+  int incl = s;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const int n = __shfl_up_sync(0xffffffffu, incl, off);
+    if (lane >= off) incl += n;
+  }
+  if (lane == 31) wsum[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    const int v = lane < nwarps ? wsum[lane] : 0;
+    int inc = v;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int n = __shfl_up_sync(0xffffffffu, inc, off);
+      if (lane >= off) inc += n;
+    }
+    wsum[lane] = inc - v;
+    if (lane == 31) wsum[kMaxWarps] = inc;
+  }
+  __syncthreads();
+  int run = wsum[warp] + incl - s;
+  for (int w = w0; w < w1; ++w) {
+    wpre[w] = run;
+    run += __popc(bits[w]);
+  }
+  const int total = wsum[kMaxWarps];
+  __syncthreads();
+  return total;
+}
+
 // keys/idxs: NL lists of capacity `cap` in this CTA's shared memory with cnt[l] entries each.
 // scratch: shared memory of at least sizeof(MergeScratch) + NL*per*8 bytes, at the same
 // offset in every CTA of the cluster.  dest(l) gives the ListDest of list l.
+//
+// The winners are dealt in a fixed order, so that the same candidates always give the same lists and
+// the same output bits: every candidate has a tag that is unique inside its CTA and lies in
+// [0, tag_range) -- its id minus tag_lo (CTA c of a cluster holds an ascending range of ids), or
+// its position in the list when tag_lo == kTagByPosition.  Winners are ordered by (CTA rank,
+// tag); among copies of the k-th key the first ones in that order are taken.
 template <int NL, typename DestFn>
 __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char* scratch,
                                       const uint32_t* keys, const int* idxs, const int* cnt,
-                                      int cap, const MergeArgs& A, DestFn dest) {
+                                      int cap, const MergeArgs& A, DestFn dest,
+                                      int tag_lo = kTagByPosition, int tag_range = 0) {
   MergeScratch* ms = reinterpret_cast<MergeScratch*>(scratch);
   const int per = A.per, k = A.topk, C = A.cluster;
   uint32_t* sel_key = reinterpret_cast<uint32_t*>(scratch + sizeof(MergeScratch));
@@ -158,8 +220,6 @@ __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char*
     ms->counts[tid][0] = 0u;
     ms->counts[tid][1] = 0u;
     ms->counts[tid][2] = 0u;
-    ms->ctr_gt[tid] = 0;
-    ms->ctr_eq[tid] = 0;
   }
   __syncthreads();
 
@@ -235,24 +295,23 @@ __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char*
   if (tid < NL) {
     const int l = tid;
     const int need_eq = ms->remaining[l];
-    int total_gt = 0, off_gt = 0, eq_before = 0, eq_taken = 0, my_take = 0, off_take = 0;
+    // copies of the k-th key are taken in CTA order; winners of CTA c start at the sum of the
+    // winners of the CTAs before it
+    int total = 0, eq_before = 0, my_take = 0, off_win = 0;
     uint32_t mx = 0u;
     for (int c = 0; c < C; ++c) {
       const uint32_t* rc = cluster.map_shared_rank(&ms->counts[l][0], c);
       const int g = (int)rc[0], e = (int)rc[1];
       mx = max(mx, rc[2]);
-      if (c < crank) off_gt += g;
-      total_gt += g;
       const int take = max(0, min(e, need_eq - eq_before));
-      if (c < crank) off_take += take;
+      if (c < crank) off_win += g + take;
       if (c == crank) my_take = take;
-      eq_taken += take;
+      total += g + take;
       eq_before += e;
     }
-    ms->off_gt[l] = off_gt;
-    ms->off_eq[l] = total_gt + off_take;
+    ms->off_win[l] = off_win;
     ms->take_eq[l] = my_take;
-    ms->total_sel[l] = min(k, total_gt + eq_taken);
+    ms->total_sel[l] = min(k, total);
     ms->maxkey[l] = mx;
   }
   __syncthreads();
@@ -268,30 +327,78 @@ __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char*
     }
     __syncthreads();
   } else {
-  // deal the winners evenly: global position p goes to CTA p / per, slot p % per
-#pragma unroll
+  // deal the winners evenly and in order: global position p goes to CTA p / per, slot p % per
+  const int trange = (tag_lo == kTagByPosition) ? cap : max(tag_range, 1);
+#pragma unroll 1
   for (int l = 0; l < NL; ++l) {
     const int n = min(cnt[l], cap);
     const uint32_t kth = ms->prefix[l];
     const uint32_t* kl = keys + (size_t)l * cap;
     const int* il = idxs + (size_t)l * cap;
-    const int off_gt = ms->off_gt[l], off_eq = ms->off_eq[l], take_eq = ms->take_eq[l];
-    for_each_key(kl, n, tid, nthr, [&](uint32_t key, int i) {
-      int p = -1;
-      if (key > kth) {
-        p = off_gt + atomicAdd(&ms->ctr_gt[l], 1);
-      } else if (key == kth) {
-        const int e = atomicAdd(&ms->ctr_eq[l], 1);
-        if (e < take_eq) p = off_eq + e;
+    const int off_win = ms->off_win[l], take_eq = ms->take_eq[l];
+    const int n_eq = (int)ms->counts[l][1];
+    auto tag_of = [&](int i) { return tag_lo == kTagByPosition ? i : il[i] - tag_lo; };
+    // tag up to which this CTA takes copies of the k-th key
+    int cut = take_eq >= n_eq ? 0x7fffffff : -1;
+    if (take_eq > 0 && take_eq < n_eq) {   // uniform over the CTA
+      if (tid == 0) ms->cut_found = 0;
+      int seen = 0;
+      for (int wlo = 0; wlo < trange; wlo += kDetWindow) {
+        for (int w = tid; w < kDetWords; w += nthr) ms->bits[w] = 0u;
+        __syncthreads();
+        for_each_key(kl, n, tid, nthr, [&](uint32_t key, int i) {
+          const unsigned t = (unsigned)(tag_of(i) - wlo);
+          if (key == kth && t < (unsigned)kDetWindow) atomicOr(&ms->bits[t >> 5], 1u << (t & 31));
+        });
+        __syncthreads();
+        const int total = bitmap_prefix(ms->bits, ms->wpre, ms->wsum, kDetWords, tid, nthr);
+        if (seen + total >= take_eq) {
+          const int need = take_eq - seen;   // 1-based rank inside this window
+          for (int w = tid; w < kDetWords; w += nthr) {
+            const int before = ms->wpre[w];
+            const uint32_t word = ms->bits[w];
+            if (before < need && need <= before + __popc(word)) {
+              ms->cut_tag = wlo + 32 * w + (int)__fns(word, 0, need - before);
+              ms->cut_found = 1;
+            }
+          }
+        }
+        seen += total;
+        __syncthreads();
+        if (ms->cut_found) break;
       }
-      if (p >= 0 && p < k) {
-        const int dst = p / per, slot = p - dst * per;
-        uint32_t* rk = cluster.map_shared_rank(sel_key, dst);
-        int* ri = cluster.map_shared_rank(sel_idx, dst);
-        rk[(size_t)l * per + slot] = key;
-        ri[(size_t)l * per + slot] = il[i];
-      }
-    });
+      cut = ms->cut_tag;
+      __syncthreads();
+    }
+    int base = 0;
+    for (int wlo = 0; wlo < trange; wlo += kDetWindow) {
+      for (int w = tid; w < kDetWords; w += nthr) ms->bits[w] = 0u;
+      __syncthreads();
+      for_each_key(kl, n, tid, nthr, [&](uint32_t key, int i) {
+        const int tg = tag_of(i);
+        const unsigned t = (unsigned)(tg - wlo);
+        if ((key > kth || (key == kth && tg <= cut)) && t < (unsigned)kDetWindow)
+          atomicOr(&ms->bits[t >> 5], 1u << (t & 31));
+      });
+      __syncthreads();
+      const int total = bitmap_prefix(ms->bits, ms->wpre, ms->wsum, kDetWords, tid, nthr);
+      for_each_key(kl, n, tid, nthr, [&](uint32_t key, int i) {
+        const int tg = tag_of(i);
+        const unsigned t = (unsigned)(tg - wlo);
+        if ((key > kth || (key == kth && tg <= cut)) && t < (unsigned)kDetWindow) {
+          const int p = off_win + base + ms->wpre[t >> 5] + __popc(ms->bits[t >> 5] & ((1u << (t & 31)) - 1u));
+          if (p < k) {
+            const int dst = p / per, slot = p - dst * per;
+            uint32_t* rk = cluster.map_shared_rank(sel_key, dst);
+            int* ri = cluster.map_shared_rank(sel_idx, dst);
+            rk[(size_t)l * per + slot] = key;
+            ri[(size_t)l * per + slot] = il[i];
+          }
+        }
+      });
+      base += total;
+      __syncthreads();
+    }
   }
   cluster.sync();
   }

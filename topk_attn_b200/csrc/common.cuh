@@ -161,6 +161,13 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// Phase-timing switches of the scan kernel exist only in RA_TUNING builds of the library.
+#ifdef RA_TUNING
+#define RA_DEBUG(P, bit) ((P).debug & (bit))
+#else
+#define RA_DEBUG(P, bit) 0
+#endif
+
 // host-side count of kernel launches (read through ra_launch_count)
 extern std::atomic<unsigned long long> g_launch_count;
 inline void note_launch() { g_launch_count.fetch_add(1, std::memory_order_relaxed); }

@@ -1,0 +1,86 @@
+// Exchange step of the sequence-sharded path without a collective library: every rank stores its
+// piece (its k proposals per head, later its partial output) straight into a slot of every peer's
+// receive buffer with ordinary stores over peer-mapped memory, then raises a flag on each peer; the
+// consumer waits for the flags of all ranks before its next kernel reads the slots.
+//
+//   exchange_push_kernel   copies `bytes` from a local buffer to the same slot on each peer and,
+//                          after the last CTA has finished, writes the current epoch to this
+//                          rank's flag on every peer (release at system scope).
+//   exchange_wait_kernel   one thread per flag: waits until it holds the current epoch (acquire at
+//                          system scope).  Every wait is bounded by wall time; a wait that runs out
+//                          sets the timeout bit of the status word and the kernel returns, so the
+//                          context stays usable and the host learns of it from ra_check_status().
+//
+// The epoch lives in device memory and is advanced by the last wait of a step, so a captured CUDA
+// graph of the step can be replayed without changing any kernel argument.  Only plain loads and
+// stores touch peer memory: no multicast, no bulk-tensor copies.  The reference is single-device;
+// the in-GPU mechanism this generalises is the cluster-wide max/sum exchange through distributed
+// shared memory of baseline_1.cu:549-598.
+#include "exchange.cuh"
+
+namespace ra {
+
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__global__ void __launch_bounds__(kPushThreads)
+exchange_push_kernel(const __grid_constant__ PushParams P) {
+  const size_t stride = (size_t)gridDim.x * kPushThreads;
+  for (size_t i = (size_t)blockIdx.x * kPushThreads + threadIdx.x; i < P.n16; i += stride) {
+    const uint4 v = P.src[i];
+#pragma unroll 1
+    for (int p = 0; p < P.npeers; ++p)
+      if (P.dst[p] != P.src) P.dst[p][i] = v;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned arrived = atomicAdd(P.done, 1u);
+    if (arrived == gridDim.x - 1) {
+      // every CTA's stores are fenced and counted: publish
+      *P.done = 0u;   // ready for the next launch (kernel boundaries order it)
+      __threadfence_system();
+      const unsigned e = *P.epoch;
+      for (int p = 0; p < P.npeers; ++p) st_release_sys(P.flag[p], e);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kMaxPeers)
+exchange_wait_kernel(const unsigned* flags, int n, unsigned* epoch, int advance,
+                     unsigned long long limit_ns, unsigned* status) {
+  const unsigned want = *epoch;
+  if ((int)threadIdx.x < n) {
+    const unsigned long long t0 = global_timer_ns();
+    // flags only grow; compare as a signed distance so that a wrapped counter still works
+    while ((int)(ld_acquire_sys(flags + threadIdx.x) - want) < 0) {
+      if (global_timer_ns() - t0 > limit_ns) {
+        atomicOr(status, kStatusTimeout);
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  if (advance && threadIdx.x == 0) *epoch = want + 1u;
+}
+
+cudaError_t launch_exchange_push(const PushParams& P, int grid, cudaStream_t stream) {
+  note_launch();
+  exchange_push_kernel<<<grid, kPushThreads, 0, stream>>>(P);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_exchange_wait(const unsigned* flags, int n, unsigned* epoch, int advance,
+                                 unsigned long long limit_ns, unsigned* status, cudaStream_t stream) {
+  note_launch();
+  exchange_wait_kernel<<<1, kMaxPeers, 0, stream>>>(flags, n, epoch, advance, limit_ns, status);
+  return cudaGetLastError();
+}
+
+}  // namespace ra

@@ -118,7 +118,8 @@ constexpr int kMergeCtaThreads = 1024;
 struct MergeCtaCtrl {
   int hist[256];
   uint32_t kmin, kmax;
-  int digit, remaining, wpos, eqc;
+  int digit, remaining, wpos, eqc, cut;
+  int wsum[kMaxWarps + 2];
   float lred[32];
 };
 
@@ -136,6 +137,8 @@ merge_attend_cta_kernel(const __grid_constant__ MergeParams P) {
   int* widx = reinterpret_cast<int*>(wkey + k);
   float* red = reinterpret_cast<float*>(widx + k);         // [32][128]
   MergeCtaCtrl* ctrl = reinterpret_cast<MergeCtaCtrl*>(red + 32 * kHeadDim);
+  uint32_t* bits = reinterpret_cast<uint32_t*>(ctrl + 1);   // one bit per candidate
+  int* wpre = reinterpret_cast<int*>(bits + ((n + 31) >> 5));
 
   if (tid == 0) {
     ctrl->kmin = 0xffffffffu;
@@ -194,19 +197,54 @@ merge_attend_cta_kernel(const __grid_constant__ MergeParams P) {
   }
   const uint32_t kth = base + prefix;
   const int need_eq = remaining;
-  // winners: keys above the k-th, and need_eq of its ties
+  // Winners in a fixed order, so that every rank that merges the same candidates picks the same keys
+  // and the same input always gives the same output bits: candidates are ranked by their position
+  // in the candidate array (ranks in order, each rank's list in the order it was written); of the
+  // copies of the k-th key the first need_eq are taken.
+  const int nwords = (n + 31) >> 5;
+  int n_eq = 0;
+  for (int i = tid; i < n; i += kMergeCtaThreads) n_eq += keys[i] == kth;
+#pragma unroll
+  for (int off = 16; off; off >>= 1) n_eq += __shfl_xor_sync(0xffffffffu, n_eq, off);
+  if (lane == 0 && n_eq) atomicAdd(&ctrl->eqc, n_eq);
+  __syncthreads();
+  n_eq = ctrl->eqc;
+  int cut = need_eq >= n_eq ? 0x7fffffff : -1;
+  if (need_eq > 0 && need_eq < n_eq) {
+    for (int w = tid; w < nwords; w += kMergeCtaThreads) bits[w] = 0u;
+    __syncthreads();
+    for (int i = tid; i < n; i += kMergeCtaThreads)
+      if (keys[i] == kth) atomicOr(&bits[i >> 5], 1u << (i & 31));
+    __syncthreads();
+    bitmap_prefix(bits, wpre, ctrl->wsum, nwords, tid, kMergeCtaThreads);
+    for (int w = tid; w < nwords; w += kMergeCtaThreads) {
+      const int before = wpre[w];
+      const uint32_t word = bits[w];
+      if (before < need_eq && need_eq <= before + __popc(word))
+        ctrl->cut = 32 * w + (int)__fns(word, 0, need_eq - before);
+    }
+    __syncthreads();
+    cut = ctrl->cut;
+  }
+  for (int w = tid; w < nwords; w += kMergeCtaThreads) bits[w] = 0u;
+  __syncthreads();
   for (int i = tid; i < n; i += kMergeCtaThreads) {
     const uint32_t key = keys[i];
-    bool keep = key > kth;
-    if (!keep && key == kth) keep = atomicAdd(&ctrl->eqc, 1) < need_eq;
-    if (keep) {
-      const int p = atomicAdd(&ctrl->wpos, 1);
+    if (key > kth || (key == kth && i <= cut)) atomicOr(&bits[i >> 5], 1u << (i & 31));
+  }
+  __syncthreads();
+  const int total_win = bitmap_prefix(bits, wpre, ctrl->wsum, nwords, tid, kMergeCtaThreads);
+  for (int i = tid; i < n; i += kMergeCtaThreads) {
+    const uint32_t key = keys[i];
+    if (key > kth || (key == kth && i <= cut)) {
+      const int p = wpre[i >> 5] + __popc(bits[i >> 5] & ((1u << (i & 31)) - 1u));
       if (p < k) {
         wkey[p] = key;
         widx[p] = idxs[i];
       }
     }
   }
+  if (tid == 0) ctrl->wpos = total_win;
   __syncthreads();
   const int nw = min(ctrl->wpos, k);
   if (P.m.sel_idx) {
@@ -292,7 +330,8 @@ merge_attend_cta_kernel(const __grid_constant__ MergeParams P) {
 }
 
 size_t merge_attend_cta_smem_bytes(int m_total, int topk) {
-  return (size_t)m_total * 8 + (size_t)topk * 8 + 32 * kHeadDim * 4 + sizeof(MergeCtaCtrl) + 64;
+  return (size_t)m_total * 8 + (size_t)topk * 8 + 32 * kHeadDim * 4 + sizeof(MergeCtaCtrl) +
+         (size_t)((m_total + 31) / 32) * 8 + 64;
 }
 
 cudaError_t launch_merge_attend_cta(const MergeParams& P, int rows, size_t smem, cudaStream_t stream) {

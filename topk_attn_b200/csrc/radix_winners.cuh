@@ -6,7 +6,12 @@
 
 namespace ra {
 
+constexpr int kWinnerWords = 256;   // one bit per key: up to 8192 keys
+
 struct WinnerCtrl {
+  unsigned bits[kWinnerWords];
+  int wpre[kWinnerWords];
+  int wtot[kWinnerWords / 32];
   unsigned hist[256];
   unsigned wmin[32], wmax[32];
   unsigned long long base;   // lower edge of the active interval of composites
@@ -24,6 +29,7 @@ __device__ __forceinline__ unsigned long long composite(uint32_t key, int idx) {
 // visible to the CTA.  On return winners[0 .. topc) hold the indices of the topc largest
 // composites in no particular order, ctrl.nwin == topc, and the CTA is synchronised.  A caller
 // that selects again with the same ctrl synchronises the CTA once more before the next call.
+// n is at most 32 * kWinnerWords.
 template <int NT>
 __device__ void select_winners(const uint32_t* keys, int n, int topc, WinnerCtrl& ctrl, int* winners) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -109,11 +115,43 @@ __device__ void select_winners(const uint32_t* keys, int n, int topc, WinnerCtrl
     __syncthreads();
     if (done) break;
   }
-  // every composite >= base is a winner, and there are exactly topc of them
-
+  // every composite >= base is a winner, and there are exactly topc of them; they are listed in
+  // ascending index order (one bit per key, popcount prefix), so the list is the same on every run
+  const int nwords = (n + 31) >> 5;
+  for (int w = tid; w < nwords; w += NT) ctrl.bits[w] = 0u;
+  __syncthreads();
+  for (int i = tid; i < n; i += NT)
+    if (composite(keys[i], i) >= base) atomicOr(&ctrl.bits[i >> 5], 1u << (i & 31));
+  __syncthreads();
+  {
+    // exclusive popcount prefix over at most kWinnerWords words: warp w scans words 32w .. 32w+31
+    const int w = tid;
+    const unsigned word = w < nwords ? ctrl.bits[w] : 0u;
+    const int c = __popc(word);
+    int incl = c;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += t;
+    }
+    if (w < kWinnerWords) ctrl.wpre[w] = incl - c;
+    if (lane == 31 && warp < kWinnerWords / 32) ctrl.wtot[warp] = incl;
+    __syncthreads();
+    if (tid == 0) {
+      int run = 0;
+      for (int j = 0; j < kWinnerWords / 32; ++j) {
+        const int t = ctrl.wtot[j];
+        ctrl.wtot[j] = run;
+        run += t;
+      }
+      ctrl.nwin = min(run, topc);
+    }
+    __syncthreads();
+  }
   for (int i = tid; i < n; i += NT)
     if (composite(keys[i], i) >= base) {
-      const int slot = atomicAdd(&ctrl.nwin, 1);
+      const int w = i >> 5;
+      const int slot = ctrl.wtot[w >> 5] + ctrl.wpre[w] + __popc(ctrl.bits[w] & ((1u << (i & 31)) - 1u));
       if (slot < topc) winners[slot] = i;
     }
   __syncthreads();

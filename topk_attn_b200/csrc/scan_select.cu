@@ -35,6 +35,8 @@ struct Ctrl {
   uint32_t kmax[kMaxLists], base[kMaxLists], prefix[kMaxLists], mask[kMaxLists];
   int shift[kMaxLists], remaining[kMaxLists], state[kMaxLists];
   int wpos, eqc;
+  uint32_t tie_pre;   // radix descent over the inverted ids of the copies of a cut's k-th key
+  int tie_rem;
   int timeout;
 };
 enum CutState : int { kCutIdle = 0, kCutRun = 1, kCutInclusive = 2, kCutExact = 3 };
@@ -133,6 +135,45 @@ __device__ void compact_lists(uint32_t* keys, int* idxs, Ctrl* ctrl, int need, i
       ctrl->eqc = 0;
     }
     consumer_sync(nct);
+    // Exact cut: of the copies of the k-th key the need_eq with the lowest ids stay (later tokens
+    // never beat an equal earlier one, so the final selection prefers low ids as well).  They are
+    // the need_eq largest inverted ids, found by a radix descent over the copies.
+    uint32_t inv_cut = 0u;
+    if (!inclusive) {
+      int ties = 0;
+      for_each_key(kl, n, tid, nct, [&](uint32_t key, int) { ties += key == kth; });
+#pragma unroll
+      for (int off = 16; off; off >>= 1) ties += __shfl_xor_sync(0xffffffffu, ties, off);
+      if (lane == 0 && ties) atomicAdd(&ctrl->eqc, ties);
+      consumer_sync(nct);
+      if (ctrl->eqc > need_eq) {   // the same for every thread
+        uint32_t pre = 0u, msk = 0u;
+        int remain = need_eq;
+#pragma unroll 1
+        for (int sh = 24; sh >= 0; sh -= 8) {
+          for (int i = tid; i < 256; i += nct) ctrl->hist[l][i] = 0;
+          consumer_sync(nct);
+          for_each_key(kl, n, tid, nct, [&](uint32_t key, int i) {
+            const uint32_t inv = ~(uint32_t)il[i];
+            if (key == kth && (inv & msk) == pre) atomicAdd(&ctrl->hist[l][(inv >> sh) & 255], 1);
+          });
+          consumer_sync(nct);
+          if (warp == 0) {
+            int d, nr;
+            warp_find_digit(ctrl->hist[l], remain, lane, d, nr);
+            if (lane == 0) {
+              ctrl->tie_pre = pre | ((uint32_t)d << sh);
+              ctrl->tie_rem = nr;
+            }
+          }
+          consumer_sync(nct);
+          pre = ctrl->tie_pre;
+          remain = ctrl->tie_rem;
+          msk |= 255u << sh;
+        }
+        inv_cut = pre;
+      }
+    }
     constexpr int E = 8;
 #pragma unroll 1
     for (int cb = 0; cb < n; cb += nct * E) {
@@ -149,8 +190,8 @@ __device__ void compact_lists(uint32_t* keys, int* idxs, Ctrl* ctrl, int need, i
       for (int e = 0; e < E; ++e) {
         const int i = cb + e * nct + tid;
         if (i < n) {
-          bool keep = inclusive ? (kk[e] >= kth) : (kk[e] > kth);
-          if (!inclusive && kk[e] == kth) keep = atomicAdd(&ctrl->eqc, 1) < need_eq;
+          const bool keep = inclusive ? (kk[e] >= kth)
+                                      : (kk[e] > kth || (kk[e] == kth && ~(uint32_t)ii[e] >= inv_cut));
           if (keep) {
             const int p = atomicAdd(&ctrl->wpos, 1);
             kl[p] = kk[e];
@@ -215,15 +256,11 @@ scan_select_kernel(const __grid_constant__ ScanParams P) {
   const int cap = P.cap, k = P.m.topk;
 
   unsigned char* stages = smem;
-  // Candidate lists: in shared memory behind the stages, or — when k times the queries per row is
-  // too large for that — in this CTA's slice of the workspace (they are written rarely once the
-  // thresholds have risen and stay in L2).
+  // candidate lists and control block behind the stages
   unsigned char* after_stages = smem + (size_t)P.nstages * kStageBytes;
-  uint32_t* keys = P.list_ws ? reinterpret_cast<uint32_t*>(P.list_ws + (size_t)blockIdx.x * NL * cap * 8)
-                             : reinterpret_cast<uint32_t*>(after_stages);
+  uint32_t* keys = reinterpret_cast<uint32_t*>(after_stages);
   int* idxs = reinterpret_cast<int*>(keys + (size_t)NL * cap);
-  Ctrl* ctrl = P.list_ws ? reinterpret_cast<Ctrl*>(after_stages)
-                         : reinterpret_cast<Ctrl*>(idxs + (size_t)NL * cap);
+  Ctrl* ctrl = reinterpret_cast<Ctrl*>(idxs + (size_t)NL * cap);
 
   // which part of which (batch group, kv-head group) this cluster owns
   int cid = blockIdx.x / C;
@@ -382,7 +419,7 @@ scan_select_kernel(const __grid_constant__ ScanParams P) {
         if constexpr (MODE == 2) {
           const uint32_t tbase = stage0 + (uint32_t)s * kStageBytes;
           float c[4] = {0.f, 0.f, 0.f, 0.f};
-          if (!(P.debug & 1)) {
+          if (!RA_DEBUG(P, 1)) {
 #pragma unroll
             for (int kk = 0; kk < 8; ++kk) {
               uint32_t a[4];
@@ -400,7 +437,7 @@ scan_select_kernel(const __grid_constant__ ScanParams P) {
             const int tok = tok_lo + 8 * (jv >> 1);
             const uint32_t key = score_key(c[jv]);
             const bool pass = qi < P.nq_cta && q0 + qi < P.nq_valid && tok < part_hi &&
-                              key > thr2[jv & 1] && !(P.debug & 4);
+                              key > thr2[jv & 1] && !RA_DEBUG(P, 4);
             const unsigned bal = __ballot_sync(0xffffffffu, pass);
             if (bal) {
               const unsigned mym = bal & tmask;
@@ -422,7 +459,7 @@ scan_select_kernel(const __grid_constant__ ScanParams P) {
         } else {
         const uint32_t base = stage0 + (uint32_t)s * kStageBytes + row_off;
         float part_sum[NQ][4];
-        if (!(P.debug & 1)) {
+        if (!RA_DEBUG(P, 1)) {
 #pragma unroll
           for (int p = 0; p < 4; ++p) {
             const uint32_t addr = base + (uint32_t)(p * 4 * HG * kRowBytes);
@@ -484,7 +521,7 @@ scan_select_kernel(const __grid_constant__ ScanParams P) {
 #pragma unroll
         for (int v = 0; v < NV; ++v) {
           const uint32_t key = score_key(mine[v]);
-          const bool pass = my_valid[v] && in_range && key > my_thr[v] && !(P.debug & 4);
+          const bool pass = my_valid[v] && in_range && key > my_thr[v] && !RA_DEBUG(P, 4);
           const unsigned bal = __ballot_sync(0xffffffffu, pass);
           if (bal) {
             const unsigned mym = bal & grp_mask;
@@ -513,7 +550,7 @@ scan_select_kernel(const __grid_constant__ ScanParams P) {
         int need = 0;
 #pragma unroll
         for (int l = 0; l < NL; ++l)
-          if (ctrl->cnt[l] > cap - R * G * T && !(P.debug & 8)) need |= 1 << l;
+          if (ctrl->cnt[l] > cap - R * G * T && !RA_DEBUG(P, 8)) need |= 1 << l;
         consumer_sync(nct);
         if (need) {
           compact_lists<NL>(keys, idxs, ctrl, need, k, cap, accept, tid, nct);
@@ -529,7 +566,7 @@ scan_select_kernel(const __grid_constant__ ScanParams P) {
   }
   __syncthreads();
 
-  if (P.debug & 16) return;  // tuning aid: time the scan without the merge
+  if (RA_DEBUG(P, 16)) return;  // tuning aid: time the scan without the merge
   // ------------------------------------------------------------------ cluster merge
   // The pipeline stages are free now and become the merge scratch.
   MergeArgs A = P.m;
@@ -543,7 +580,8 @@ scan_select_kernel(const __grid_constant__ ScanParams P) {
     d.hq = (h0 + lh) * P.group + (q0 + qi) % P.group;
     return d;
   };
-  cluster_select_attend<NL>(cluster, stages, keys, idxs, ctrl->cnt, cap, A, dest);
+  cluster_select_attend<NL>(cluster, stages, keys, idxs, ctrl->cnt, cap, A, dest, tok_begin,
+                            max(my_ntiles, 1) * T);
 }
 
 size_t scan_smem_bytes(int nl, int cap, int nstages) {
@@ -555,7 +593,9 @@ size_t merge_scratch_bytes(int nl, int per) { return sizeof(MergeScratch) + (siz
 template <int HG, int NQ>
 static cudaError_t launch_one(const ScanParams& P, int grid, size_t smem, cudaStream_t stream) {
   auto kern = scan_select_kernel<HG, NQ, 1>;
+#ifdef RA_TUNING
   if (P.debug & 2) kern = scan_select_kernel<HG, NQ, 0>;
+#endif
   if constexpr (HG == 1 && NQ > 1) {
     if (P.swizzled) kern = scan_select_kernel<1, NQ, 2>;
   }

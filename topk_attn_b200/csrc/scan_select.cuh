@@ -9,7 +9,6 @@ struct ScanParams {
   MergeArgs m;               // selection / output arguments (list_off is set per cluster)
   const __half* q;           // [B,Hq,128]
   unsigned* status;          // one word, bit 0 = a bounded wait gave up
-  unsigned char* list_ws;    // optional: global memory for the candidate lists, grid * NL * cap * 8 bytes
   const int* part_ids;       // optional [B,Hq,nparts]: which slice of length part_len each part is
   int batch, hq, hkv, n_tokens;
   int group;                 // hq / hkv
@@ -26,7 +25,7 @@ struct ScanParams {
   int part_len;              // tokens per part
   int head_major;            // 1: table is [H, N, 128] (centroids); one head per CTA
   int swizzled;              // 1: tiles are two 64-dim halves with the 128-byte swizzle (tensor-core scoring)
-  int debug;                 // tuning aid: bit 0 = stream the tiles but skip the scoring
+  int debug;                 // RA_TUNING builds only: bits switch parts of the kernel off (phase timing)
 };
 
 size_t scan_smem_bytes(int nl, int cap, int nstages);

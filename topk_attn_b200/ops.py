@@ -21,14 +21,22 @@ def _stream_ptr() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+_retired = []
+
+
 def workspace(nbytes: int, device: torch.device) -> Tensor:
     """A cached, zero-initialised scratch buffer of at least ``nbytes`` on ``device`` (one per
-    device and stream).  Allocation happens here, outside the C ABI, never per call."""
+    device and stream).  Allocation happens here, outside the C ABI, never per call.  When a
+    larger buffer replaces a smaller one it inherits the status block (the sticky bits kernels set)
+    in stream order, and the old buffer is kept alive because launches in flight may still use it."""
     key = (device.index if device.index is not None else torch.cuda.current_device(), _stream_ptr())
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
-        ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
-        _workspaces[key] = ws
+        new = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        if ws is not None:
+            new[:256].copy_(ws[:256])
+            _retired.append(ws)
+        _workspaces[key] = ws = new
     return ws
 
 

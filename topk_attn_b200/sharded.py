@@ -115,59 +115,209 @@ def _exchange(self, idx: Tensor, sc: Tensor) -> None:
 ShardedTopkAttention.exchange_candidates = _exchange
 
 
+def local_scores(q: Tensor, k: Tensor) -> Tensor:
+    """fp32 q.K^T of this rank's shard by plain torch on the device: [B,Hq,n]."""
+    B, Hq, _ = q.shape
+    Hkv = k.size(-2)
+    grp = Hq // Hkv
+    rows = []
+    for b in range(B):
+        kb = k[b] if k.dim() == 4 else k
+        per_head = [q[b, h * grp:(h + 1) * grp].float() @ kb[:, h, :].float().t() for h in range(Hkv)]
+        rows.append(torch.cat(per_head, 0))
+    return torch.stack(rows)
+
+
+def verify_winners(q: Tensor, k: Tensor, v: Tensor, out: Tensor, gidx: Tensor, gsc: Tensor,
+                   topk: int, sm_scale: float, index_base: int, world: int, band: float = 1e-3) -> dict:
+    """Check one step's result on the ranks themselves with plain torch operations on each device
+    (no library code): ``out`` is this rank's final output, ``gidx``/``gsc`` the global winners as
+    this rank's merge selected them.  Verdicts:
+
+    * ``ranks_agree`` -- every rank holds bit-identical outputs and winner sets;
+    * ``selection`` -- against this rank's own fp32 q.K^T: every local key scoring more than
+      ``band`` above the k-th winner is among the winners, no owned winner scores more than ``band``
+      below it, reported scores match within ``band``, and the owned winners of all ranks add up to
+      exactly k distinct ids per (row, head);
+    * ``output`` -- ``out`` equals softmax.V recomputed from the winners (every rank mixes the V rows
+      it owns in torch, partial sums are all-reduced) within rtol 1e-2 / atol 1e-3.
+    """
+    B, Hq, _ = q.shape
+    n = k.size(-3)
+    Hkv = k.size(-2)
+    grp = Hq // Hkv
+    dev = q.device
+    res = {}
+    multi = world > 1 and dist.is_initialized()
+    if multi:
+        outs = [torch.empty_like(out) for _ in range(world)]
+        dist.all_gather(outs, out.contiguous())
+        sets = [torch.empty_like(gidx) for _ in range(world)]
+        dist.all_gather(sets, gidx.sort(-1).values.contiguous())
+        res["ranks_agree"] = bool(all(torch.equal(o, outs[0]) for o in outs) and
+                                  all(torch.equal(x, sets[0]) for x in sets))
+    else:
+        res["ranks_agree"] = True
+    s = local_scores(q, k)
+    ids = gidx.long()
+    mine = (ids >= index_base) & (ids < index_base + n)
+    kth = gsc.min(-1, keepdim=True).values
+    slot = torch.where(mine, ids - index_base, torch.full_like(ids, n))
+    member = torch.zeros(B, Hq, n + 1, dtype=torch.bool, device=dev).scatter_(-1, slot, True)[..., :n]
+    got = torch.cat([s, torch.zeros(B, Hq, 1, device=dev)], -1).gather(-1, slot)
+    missed = bool(((s > kth + band) & ~member).any())
+    low = bool((mine & (got < kth - band)).any())
+    score_err = float(((got - gsc).abs() * mine).max())
+    srt = ids.sort(-1).values
+    distinct = bool((srt[..., 1:] != srt[..., :-1]).all())
+    owned = mine.sum(-1).to(torch.int64)
+    if multi:
+        dist.all_reduce(owned)
+    res["selection"] = bool(not missed and not low and score_err <= band and distinct and
+                            bool((owned == topk).all()))
+    m = (gsc * sm_scale).max(-1, keepdim=True).values
+    w = torch.exp(gsc * sm_scale - m) * mine
+    num = torch.zeros(B, Hq, 128, device=dev)
+    row = slot.clamp(max=n - 1)
+    for b in range(B):
+        vb = v[b] if v.dim() == 4 else v
+        for h in range(Hq):
+            num[b, h] = w[b, h] @ vb[row[b, h], h // grp].float()
+    den = w.sum(-1)
+    if multi:
+        dist.all_reduce(num)
+        dist.all_reduce(den)
+    ref = num / den.unsqueeze(-1)
+    res["output"] = bool(torch.allclose(out.float(), ref, rtol=1e-2, atol=1e-3))
+    res["max_abs_err"] = float((out.float() - ref).abs().max())
+    res["ok"] = bool(res["ranks_agree"] and res["selection"] and res["output"])
+    if multi:
+        flag = torch.tensor([1 if res["ok"] else 0], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        res["ok"] = bool(flag.item())
+    return res
+
+
+def verify_sharded_step(op: "ShardedTopkAttention", q: Tensor, k: Tensor, v: Tensor,
+                        index_base: int) -> dict:
+    """One untimed sharded step and its check (see verify_winners)."""
+    from . import ops
+    out = op.step(q, k, v, index_base)
+    B, Hq, _ = q.shape
+    cand_sc, cand_idx, _ = op._buffers(B, Hq, q.device)
+    _, gidx, gsc = ops.merge_attend(cand_sc, cand_idx, v, op.topk, op.sm_scale, index_base,
+                                    partial=True, return_indices=True)
+    ops.check_status(q.device)
+    return verify_winners(q, k, v, out, gidx, gsc, op.topk, op.sm_scale, index_base, op.world)
+
+
+def time_sharded(op: "ShardedTopkAttention", q: Tensor, k: Tensor, v: Tensor, index_base: int,
+                 steps: int, warmup: int):
+    """Device time of ``steps`` sharded steps, max over ranks, and the share of the local scan.
+    Returns (ms per step, scan ms per step, launches of this rank in the timed region)."""
+    from . import capi, ops
+    dev = q.device
+    B, Hq, _ = q.shape
+    for _ in range(max(warmup, 3)):
+        op.step(q, k, v, index_base)
+    ops.check_status(dev)
+    if op.world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sel = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+           for _ in range(steps)]
+    launches0 = capi.lib().ra_launch_count()
+    e0.record()
+    for i in range(steps):
+        # the scan is the dominant kernel: time it separately inside the step
+        cand_sc, cand_idx, partials = op._buffers(B, Hq, dev)
+        sel[i][0].record()
+        idx, sc = op.local_candidates(q, k, index_base)
+        sel[i][1].record()
+        op.exchange_candidates(idx, sc)
+        part = op.backend.merge_partial(cand_sc, cand_idx, v, op.topk, op.sm_scale, index_base)
+        if op.world > 1:
+            _all_gather(partials, part, op.group)
+        else:
+            partials[0].copy_(part)
+        op.backend.combine(partials)
+    e1.record()
+    launches = capi.lib().ra_launch_count() - launches0
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if op.world > 1:
+        dist.barrier()
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    scan_ms = sum(a.elapsed_time(b) for a, b in sel) / steps
+    ops.check_status(dev)
+    return t.item() / steps, scan_ms, launches
+
+
+def bench_long_context(rank: int, world: int, dev, steps: int, warmup: int, peak_gbs: float) -> dict:
+    """Configuration 4 (1 048 576 tokens, 32 query / 8 kv heads, k = 4096) cut over ``world`` ranks:
+    total work is fixed, so the time per step should fall as ranks are added (strong scaling).  On
+    one GPU the step is the single fused call; on several it is the sharded step.  Every record
+    carries the verdict of a check of its own result (verify_winners)."""
+    from . import ops, workloads as W
+    w = W.sharded_long_context_shard(rank, world, device=dev)
+    q, k, v = w.q, w.k, w.v
+    n_local = w.n_tokens
+    base = rank * n_local
+    if world == 1:
+        out, gidx, gsc = ops.topk_attention(q, k, v, w.topk, w.sm_scale, return_indices=True)
+        ops.check_status(dev)
+        parity = verify_winners(q, k, v, out, gidx, gsc, w.topk, w.sm_scale, 0, 1)
+        out = torch.empty_like(q)
+        for _ in range(max(warmup, 3)):
+            ops.topk_attention(q, k, v, w.topk, w.sm_scale, out=out)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            ops.topk_attention(q, k, v, w.topk, w.sm_scale, out=out)
+        e1.record()
+        torch.cuda.synchronize()
+        ops.check_status(dev)
+        per_ms = e0.elapsed_time(e1) / steps
+        scan_ms = per_ms
+    else:
+        op = ShardedTopkAttention(w.topk, w.sm_scale)
+        parity = verify_sharded_step(op, q, k, v, base)
+        per_ms, scan_ms, _ = time_sharded(op, q, k, v, base, steps, warmup)
+    n_total = world * n_local
+    alg_per_gpu = w.kv_bytes_scanned() + q.size(1) * w.topk * 128 * 2 // world
+    return {"workload": "cfg4: B1 Hq32/Hkv8 N1048576 k4096, tokens cut over the ranks",
+            "n_gpus": world, "context": n_total, "context_per_gpu": n_local, "scaling": "strong",
+            "us_per_step": per_ms * 1e3, "tokens_per_s": n_total / (per_ms * 1e-3),
+            "scan_us": scan_ms * 1e3, "exchange_us": (per_ms - scan_ms) * 1e3,
+            "roofline_frac_step": alg_per_gpu / (per_ms * 1e-3) / 1e9 / peak_gbs,
+            "algorithmic_bytes_per_gpu": alg_per_gpu, "parity": parity}
+
+
 def bench(args, rank: int, local: int, world: int, ClockSampler, measured_peak_gbs) -> None:
-    """`bench.py --gpus N` for N > 1: weak scaling, every rank holds a 131072-token shard of each
-    of the 4 sequences (32 heads, k = 2048).  Timed on the device, max over ranks."""
+    """`bench.py --gpus N` for N > 1.  The headline line is weak scaling of configuration 2: every
+    rank holds a 131072-token shard of each of the 4 sequences (32 heads, k = 2048), timed on the
+    device, max over ranks.  The same process then runs configuration 4 strong-scaled
+    (bench_long_context) and adds it as ``cfg4_strong``.  Both results are checked on the ranks
+    before they are timed; a failed check fails the run."""
     from . import ops, workloads as W
     dev = torch.device("cuda", local)
     strong = args.workload == "cfg4"
     if strong:
-        # configuration 4: 1 048 576 tokens in total (32 query / 8 kv heads, k = 4096) cut over the
-        # ranks, so the work per rank shrinks as ranks are added
         w = W.sharded_long_context_shard(rank, world, device=dev)
     else:
         w = W.fused_topk_128k_shard(rank, world, device=dev)
     q, k, v = w.q, w.k, w.v
     op = ShardedTopkAttention(w.topk, w.sm_scale)
     n_local = w.n_tokens
+    base = rank * n_local
 
-    def step():
-        return op.step(q, k, v)
-
-    for _ in range(max(args.warmup, 3)):
-        step()
-    ops.check_status(dev)
+    parity = verify_sharded_step(op, q, k, v, base)
     sampler = ClockSampler(local)
-    dist.barrier()
-    torch.cuda.synchronize()
     sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sel = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
-           for _ in range(args.steps)]
-    from . import capi
-    launches0 = capi.lib().ra_launch_count()
-    e0.record()
-    for i in range(args.steps):
-        # the scan is the dominant kernel: time it separately inside the step
-        B, Hq, _ = q.shape
-        cand_sc, cand_idx, partials = op._buffers(B, Hq, dev)
-        sel[i][0].record()
-        idx, sc = op.local_candidates(q, k, rank * n_local)
-        sel[i][1].record()
-        op.exchange_candidates(idx, sc)
-        part = op.backend.merge_partial(cand_sc, cand_idx, v, op.topk, op.sm_scale, rank * n_local)
-        _all_gather(partials, part)
-        op.backend.combine(partials)
-    e1.record()
-    launches = capi.lib().ra_launch_count() - launches0      # this rank's, in the timed region
-    torch.cuda.synchronize()
-    dist.barrier()
+    per_ms, scan_ms, launches = time_sharded(op, q, k, v, base, args.steps, args.warmup)
     clocks = sampler.stop()
-    t = torch.tensor([e0.elapsed_time(e1)], device=dev)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    per_ms = t.item() / args.steps
-    scan_ms = sum(a.elapsed_time(b) for a, b in sel) / args.steps
-    ops.check_status(dev)
 
     q_host = q.cpu().pin_memory()
     out_host = torch.empty_like(q_host).pin_memory()
@@ -175,7 +325,7 @@ def bench(args, rank: int, local: int, world: int, ClockSampler, measured_peak_g
 
     def e2e_step():
         q_dev.copy_(q_host, non_blocking=True)
-        o = op.step(q_dev, k, v)
+        o = op.step(q_dev, k, v, base)
         out_host.copy_(o, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
@@ -188,11 +338,18 @@ def bench(args, rank: int, local: int, world: int, ClockSampler, measured_peak_g
     te = torch.tensor([(time.perf_counter() - t0) / args.steps], device=dev)
     dist.all_reduce(te, op=dist.ReduceOp.MAX)
     e2e_s = te.item()
+    tokens = world * w.batch * n_local
+    alg = w.algorithmic_bytes()
+    heads_q, heads_kv, batch, bkv, topk = q.size(1), k.size(-2), w.batch, w.bkv, w.topk
+    peak, kind = measured_peak_gbs()
+
+    long_ctx = None
+    if not strong and not args.no_cfg4:
+        del w, q, k, v, op, q_dev
+        torch.cuda.empty_cache()
+        long_ctx = bench_long_context(rank, world, dev, min(args.steps, 100), args.warmup, peak)
 
     if rank == 0:
-        tokens = world * w.batch * n_local
-        peak, kind = measured_peak_gbs()
-        alg = w.algorithmic_bytes()
         achieved = alg / (scan_ms * 1e-3) / 1e9
         line = {
             "metric": "tokens_scanned_per_s", "value": tokens / (per_ms * 1e-3), "unit": "tokens/s",
@@ -201,21 +358,30 @@ def bench(args, rank: int, local: int, world: int, ClockSampler, measured_peak_g
             "scaling": "strong" if strong else "weak", "vs_baseline": None,
             "dtype": "f16 inputs, f32 accumulate",
             "data": "synthetic",
-            "config": {"workload": "cfg4 token-sharded" if strong else "cfg2 token-sharded", "batch": w.batch, "heads_q": q.size(1),
-                       "heads_kv": k.size(-2), "head_dim": 128, "context": world * n_local,
-                       "context_per_gpu": n_local, "topk": w.topk, "caches": w.bkv,
+            "config": {"workload": "cfg4 token-sharded" if strong else "cfg2 token-sharded",
+                       "batch": batch, "heads_q": heads_q,
+                       "heads_kv": heads_kv, "head_dim": 128, "context": world * n_local,
+                       "context_per_gpu": n_local, "topk": topk, "caches": bkv,
                        "l2": "inputs_exceed_l2", "collectives": "nccl all_gather x2"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_kind": kind + " (burst copy)",
                          "algorithmic_bytes": alg, "traffic": None,
-                         "kernel": "scan_select_kernel (per rank)", "scan_us": scan_ms * 1e3},
+                         "kernel": "scan kernel of one rank", "scan_us": scan_ms * 1e3,
+                         "exchange_us": (per_ms - scan_ms) * 1e3},
             "cpu_baseline": None,
             "e2e": {"value": tokens / e2e_s, "unit": "tokens/s", "us_per_step": e2e_s * 1e6,
                     "h2d_bytes_per_step": q_host.numel() * 2,
                     "d2h_bytes_per_step": out_host.numel() * 2},
             "gpu_launches": launches * world,
             "clocks": clocks,
+            "parity": parity,
         }
-        print(json.dumps(line))
+        if long_ctx is not None:
+            line["cfg4_strong"] = long_ctx
+        print(json.dumps(line), flush=True)
+    ok = parity["ok"] and (long_ctx is None or long_ctx["parity"]["ok"])
     dist.barrier()
     dist.destroy_process_group()
+    if not ok:
+        raise SystemExit("parity check failed on the ranks: " + json.dumps(
+            {"cfg2": parity, "cfg4": long_ctx["parity"] if long_ctx else None}))
