@@ -122,6 +122,7 @@ struct Plan {
   int hg = 0, nq = 0, bshare = 1, nq_valid = 1, qsplit = 1, nq_cta = 1;
   int cluster = 1, nsplit = 1, cap = 0, nstages = 0, per = 0, part_len = 0, grid = 0;
   int groups = 2, rendezvous = 4;
+  int det_words = 32;  // bitmap words of the ordered deal in the scan kernel's scratch
   size_t smem = 0;
   // second stage (only when parts > 1)
   int cluster2 = 1, cap2 = 0, per2 = 0;
@@ -273,14 +274,17 @@ Plan make_plan(const Shape& s) {
         const int tiles = ceil_div(part_len, T);
         if (cluster > 1 && tiles < cluster) continue;
         const int per = ceil_div(s.topk, cluster);
-        const size_t scratch = merge_scratch_bytes(nl, per);
+        // scratch of the cluster select in the freed pipeline stages; the bitmap of the ordered
+        // deal covers a CTA's token slab in one window when the stages have room for it
+        const size_t scratch = merge_scratch_bytes(nl, per, 32);
+        const int slab_tokens = ceil_div(tiles, cluster) * T;
         // stages, consumer groups, check interval and list capacity within the shared-memory
         // budget: the deepest pipeline whose lists still hold k keys plus the keys that may arrive
         // between two overflow checks
         // Long parts take the deepest pipeline that fits.  Short parts (a few tiles) are bound by
         // fixed costs and by how many CTAs run at once: the shallower geometries, which leave room
         // for two CTAs per SM, compete as well, at a penalty on their stream time.
-        struct Geo { int nstages, cap, cgroups, rdv; double slow; };
+        struct Geo { int nstages, cap, cgroups, rdv; double slow; int det; };
         Geo geos[4];
         int ngeo = 0;
         static const double kSlow[4] = {1.0, 1.05, 1.2, 1.35};
@@ -302,7 +306,8 @@ Plan make_plan(const Shape& s) {
             const int c = std::min(fit, 2 * s.topk + margin);
             const int want = (st > 4) ? (3 * s.topk) / 2 + margin : s.topk + margin + 64;
             if (c >= std::min(want, 2 * s.topk + margin)) {
-              geos[ngeo++] = Geo{st, c, g2, r, kSlow[gi]};
+              const int room = (int)(((size_t)st * kStageBytes - merge_scratch_bytes(nl, per, 0)) / 8) & ~31;
+              geos[ngeo++] = Geo{st, c, g2, r, kSlow[gi], std::min(det_words_for(slab_tokens), room)};
               break;
             }
           }
@@ -340,7 +345,7 @@ Plan make_plan(const Shape& s) {
         pl.hg = hg; pl.nq = nq; pl.bshare = bshare; pl.nq_valid = nq_valid;
         pl.qsplit = qsplit; pl.nq_cta = nq_cta;
         pl.cluster = cluster; pl.nsplit = nsplit; pl.cap = cap; pl.nstages = nstages;
-        pl.groups = cgroups; pl.rendezvous = rdv;
+        pl.groups = cgroups; pl.rendezvous = rdv; pl.det_words = geos[gx].det;
         pl.per = per; pl.part_len = part_len; pl.grid = nclusters * cluster; pl.smem = smem;
         pl.cost = cost;
         if (two_stage && !plan_merge(s.segments * nsplit * s.topk,
@@ -581,7 +586,7 @@ int run(const ra_params* p, bool attend, const PartIds* ext = nullptr) {
   sp.head_major = s.head_major;
   if (const char* d = tuning_env("RA_DEBUG_FLAGS")) sp.debug = atoi(d);
   MergeArgs& m = sp.m;
-  m.topk = s.topk; m.per = pl.per; m.cluster = pl.cluster;
+  m.topk = s.topk; m.per = pl.per; m.cluster = pl.cluster; m.det_words = pl.det_words;
   m.hq_total = s.hq; m.list_pitch = parts * s.topk; m.list_off = 0;
   m.index_base = two_stage ? 0 : p->index_base;
   m.own_lo = 0; m.own_hi = 0x7fffffff; m.id_shift = 0;
@@ -625,7 +630,7 @@ int run(const ra_params* p, bool attend, const PartIds* ext = nullptr) {
   memset(&mp, 0, sizeof mp);
   mp.m = sp.m;
   mp.m.topk = lists_final ? s.segments * s.topk : s.topk;
-  mp.m.per = pl.per2; mp.m.cluster = pl.cluster2;
+  mp.m.per = pl.per2; mp.m.cluster = pl.cluster2; mp.m.det_words = det_words_for(pl.cap2);
   mp.m.list_pitch = mp.m.topk; mp.m.list_off = 0;
   mp.m.out_mode = attend ? kOutFinal : kOutNone;
   if (lists_final) {
@@ -704,11 +709,13 @@ int run_store(const ra_params* p, const Shape& s, int group, bool attend, unsign
   // large as shared memory allows
   int c2 = 1;
   while (c2 < kSelMaxCluster && rows * c2 * 2 <= sms && ceil_div(s.n, c2 * 2) >= 4096) c2 <<= 1;
-  int per2 = 0, cap2 = 0;
+  int per2 = 0, cap2 = 0, det2 = 32, chunk2 = 0;
   size_t fixed = 0;
   for (;; c2 <<= 1) {
     per2 = ceil_div(s.topk, c2);
-    fixed = select_stored_fixed_smem_bytes(per2);
+    chunk2 = ceil_div(ceil_div(s.n, c2), kTileRows) * kTileRows;
+    det2 = det_words_for(chunk2);
+    fixed = select_stored_fixed_smem_bytes(per2, det2);
     cap2 = fixed < kSmemBudget ? (int)std::min<size_t>(16384, (kSmemBudget - fixed) / 8) : 0;
     if (cap2 >= s.topk + 512 || c2 >= kSelMaxCluster) break;
   }
@@ -729,7 +736,7 @@ int run_store(const ra_params* p, const Shape& s, int group, bool attend, unsign
   SelectStoredParams qp;
   memset(&qp, 0, sizeof qp);
   MergeArgs& m = qp.m;
-  m.topk = s.topk; m.per = per2; m.cluster = c2;
+  m.topk = s.topk; m.per = per2; m.cluster = c2; m.det_words = det2;
   m.out_mode = attend ? kOutFinal : kOutNone;
   m.hq_total = s.hq; m.list_pitch = s.topk; m.list_off = 0; m.index_base = p->index_base;
   m.own_lo = 0; m.own_hi = 0x7fffffff; m.id_shift = 0;
@@ -742,7 +749,7 @@ int run_store(const ra_params* p, const Shape& s, int group, bool attend, unsign
   m.scale_log2e = p->sm_scale * kLog2e; m.sm_scale = p->sm_scale;
   qp.keys_ws = keys_ws; qp.hist_ws = hist_ws;
   qp.n_tokens = s.n; qp.n_pad = sp.n_pad; qp.nparts = nparts;
-  qp.chunk = ceil_div(ceil_div(s.n, c2), kTileRows) * kTileRows;
+  qp.chunk = chunk2;
   qp.cap = cap2; qp.group = group;
   e = launch_select_stored(qp, rows, fixed + (size_t)cap2 * 8, stream);
   if (e != cudaSuccess) return cuda_fail(e, "select_stored launch");
@@ -1255,7 +1262,7 @@ int ra_merge_attend(const ra_merge_params* p) {
   MergeParams mp;
   memset(&mp, 0, sizeof mp);
   MergeArgs& m = mp.m;
-  m.topk = p->topk; m.per = pl.per2; m.cluster = pl.cluster2;
+  m.topk = p->topk; m.per = pl.per2; m.cluster = pl.cluster2; m.det_words = det_words_for(pl.cap2);
   m.out_mode = p->out_partial ? kOutPartial : (p->out ? kOutFinal : kOutNone);
   m.hq_total = p->num_q_heads; m.list_pitch = p->topk; m.list_off = 0; m.index_base = 0;
   m.own_lo = p->own_base; m.own_hi = p->own_base + p->num_tokens; m.id_shift = p->own_base;

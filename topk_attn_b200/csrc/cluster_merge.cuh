@@ -16,8 +16,7 @@ namespace ra {
 
 namespace cg = cooperative_groups;
 
-constexpr int kDetWords = 2048;          // bitmap words of one window of the ordered deal
-constexpr int kDetWindow = kDetWords * 32;
+constexpr int kMaxDetWords = 8192;       // most bitmap words of one window of the ordered deal
 constexpr int kTagByPosition = 0x7fffffff;   // tag_lo value: a candidate's tag is its list position
 
 struct MergeScratch {
@@ -28,10 +27,9 @@ struct MergeScratch {
   uint32_t counts[kMaxLists][4];  // n_gt, n_eq, best key — read by the other CTAs
   int off_win[kMaxLists], take_eq[kMaxLists], total_sel[kMaxLists];
   uint32_t maxkey[kMaxLists];
-  // ordered deal: one bit per candidate tag of the current window, exclusive popcount prefix per
-  // word, warp totals of the block scan, and the tag up to which copies of the k-th key are taken
-  uint32_t bits[kDetWords];
-  int wpre[kDetWords];
+  // ordered deal: warp totals of the block scan and the tag up to which copies of the k-th key are
+  // taken (the bitmap itself -- one bit per candidate tag of the current window and an exclusive
+  // popcount prefix per word -- follows the dealt winners, MergeArgs::det_words words of each)
   int wsum[kMaxWarps + 2];
   int cut_tag, cut_found;
   float red[kMaxWarps][kHeadDim];
@@ -40,10 +38,15 @@ struct MergeScratch {
   float l_part[kMaxLists];            // read by the other CTAs
 };
 
-// Shared memory the cluster code needs in every CTA: its scratch block and the dealt winners of
-// nl lists (per = ceil(topk / cluster) slots each).
-__host__ __device__ inline size_t select_scratch_bytes(int nl, int per) {
-  return (sizeof(MergeScratch) + (size_t)nl * per * 8 + 127) & ~size_t(127);
+// Shared memory the cluster code needs in every CTA: its scratch block, the dealt winners of nl
+// lists (per = ceil(topk / cluster) slots each) and the bitmap window of the ordered deal.
+__host__ __device__ inline size_t select_scratch_bytes(int nl, int per, int det_words) {
+  return ((sizeof(MergeScratch) + (size_t)nl * per * 8 + 127) & ~size_t(127)) + (size_t)det_words * 8;
+}
+// Bitmap words that cover `range` candidate tags in one window (fewer words: several windows).
+__host__ __device__ inline int det_words_for(int range) {
+  const int w = (range + 31) / 32;
+  return w < 32 ? 32 : (w > kMaxDetWords ? kMaxDetWords : ((w + 31) & ~31));
 }
 
 enum OutMode : int {
@@ -63,6 +66,7 @@ struct MergeArgs {
   int index_base;
   int own_lo, own_hi;  // only winners with own_lo <= id < own_hi are mixed (id before index_base)
   int id_shift;        // subtracted from an id to address V (ids of another shard's frame)
+  int det_words;       // bitmap words of the ordered deal's window (0 with select_all + local_deal)
   int select_all;      // 1: every candidate is a winner (topk == number of candidates)
   int local_deal;      // with select_all: CTA c already holds winners c*per .. c*per+cnt-1, keep them
   int expand_clen;     // > 0 with expand_out: winners are cluster ids, written out expanded
@@ -97,6 +101,11 @@ __device__ __forceinline__ void for_each_key(const uint32_t* keys, int n, int ti
       if (i < n) f(kk[e], i);
     }
   }
+}
+
+// Barrier over the cluster; a cluster of one CTA needs only the CTA barrier.
+__device__ __forceinline__ void cluster_barrier(cg::cluster_group& cluster, int C) {
+  if (C > 1) cluster.sync(); else __syncthreads();
 }
 
 // One list's destination: batch row, query head, kv head, and whether it is in use.
@@ -198,15 +207,23 @@ __device__ __forceinline__ int bitmap_prefix(const uint32_t* bits, int* wpre, in
 // [0, tag_range) -- its id minus tag_lo (CTA c of a cluster holds an ascending range of ids), or
 // its position in the list when tag_lo == kTagByPosition.  Winners are ordered by (CTA rank,
 // tag); among copies of the k-th key the first ones in that order are taken.
+//
+// A caller that already knows that the k-th key lies in [sel_base, sel_base + 2^sel_shift) and that
+// sel_above candidates of the whole cluster lie above that interval passes the three values: the
+// radix select then only counts the keys inside the interval (fewer passes, well spread bins).
 template <int NL, typename DestFn>
 __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char* scratch,
                                       const uint32_t* keys, const int* idxs, const int* cnt,
                                       int cap, const MergeArgs& A, DestFn dest,
-                                      int tag_lo = kTagByPosition, int tag_range = 0) {
+                                      int tag_lo = kTagByPosition, int tag_range = 0,
+                                      uint32_t sel_base = 0u, int sel_shift = 32, int sel_above = 0) {
   MergeScratch* ms = reinterpret_cast<MergeScratch*>(scratch);
   const int per = A.per, k = A.topk, C = A.cluster;
   uint32_t* sel_key = reinterpret_cast<uint32_t*>(scratch + sizeof(MergeScratch));
   int* sel_idx = reinterpret_cast<int*>(sel_key + (size_t)NL * per);
+  uint32_t* det_bits = reinterpret_cast<uint32_t*>(scratch + select_scratch_bytes(NL, per, 0));
+  int* det_pre = reinterpret_cast<int*>(det_bits + A.det_words);
+  const int det_window = A.det_words * 32;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int nthr = blockDim.x, nwarps = nthr >> 5;
   const int crank = (int)cluster.block_rank();
@@ -216,32 +233,39 @@ __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char*
   for (int i = tid; i < NL * per; i += nthr) sel_idx[i] = -1;
   if (tid < kMaxLists) {
     ms->prefix[tid] = 0u;
-    ms->remaining[tid] = k;
+    ms->remaining[tid] = k - sel_above;
     ms->counts[tid][0] = 0u;
     ms->counts[tid][1] = 0u;
     ms->counts[tid][2] = 0u;
   }
   __syncthreads();
 
-  // radix select, most significant byte first; one cluster barrier per pass
-  uint32_t mask = 0u;
+  // radix select inside [sel_base, sel_base + 2^sel_shift), most significant digit first, up to 8
+  // bits per pass; one cluster barrier per pass.  `prefix` holds the digits found so far of
+  // (k-th key - sel_base), `mask` the bits they cover (and the bits above the interval, which are
+  // zero for every key inside it).
   int buf = 0;
   if (A.select_all) {
     if (tid < kMaxLists) ms->remaining[tid] = 0;  // threshold key 0: everything is above it
     __syncthreads();
   }
+  int cur = A.select_all ? 0 : sel_shift;
+  uint32_t mask = cur >= 32 ? 0u : ~((1u << cur) - 1u);
 #pragma unroll 1
-  for (int shift = A.select_all ? -1 : 24; shift >= 0; shift -= 8) {
+  while (cur > 0) {
+    const int ns = max(0, cur - 8);
+    const uint32_t dmask = (1u << (cur - ns)) - 1u;
 #pragma unroll
     for (int l = 0; l < NL; ++l) {
       const int n = min(cnt[l], cap);
       const uint32_t pre = ms->prefix[l];
       const uint32_t* kl = keys + (size_t)l * cap;
       for_each_key(kl, n, tid, nthr, [&](uint32_t key, int) {
-        if ((key & mask) == pre) atomicAdd(&ms->hist[buf][l][(key >> shift) & 255], 1);
+        const uint32_t rel = key - sel_base;
+        if (key >= sel_base && (rel & mask) == pre) atomicAdd(&ms->hist[buf][l][(rel >> ns) & dmask], 1);
       });
     }
-    cluster.sync();
+    cluster_barrier(cluster, C);
     for (int item = tid; item < NL * 256; item += nthr) {
       const int l = item >> 8, bin = item & 255;
       int sum = 0;
@@ -257,15 +281,19 @@ __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char*
       int d, nr;
       warp_find_digit(ms->ghist[l], ms->remaining[l], lane, d, nr);
       if (lane == 0) {
-        ms->prefix[l] |= (uint32_t)d << shift;
+        ms->prefix[l] |= (uint32_t)d << ns;
         ms->remaining[l] = nr;
       }
     }
     __syncthreads();
-    mask |= 255u << shift;
+    mask = ns > 0 ? ~((1u << ns) - 1u) : 0xffffffffu;
+    cur = ns;
     buf ^= 1;
   }
+  if (tid < kMaxLists) ms->prefix[tid] += sel_base;   // from here on: the k-th key itself
+  __syncthreads();
 
+  RA_STAMP(A.status, 4);
   // my candidates above / equal to the k-th key, and my best key
 #pragma unroll
   for (int l = 0; l < NL; ++l) {
@@ -291,7 +319,7 @@ __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char*
       atomicMax(&ms->counts[l][2], mx);
     }
   }
-  cluster.sync();
+  cluster_barrier(cluster, C);
   if (tid < NL) {
     const int l = tid;
     const int need_eq = ms->remaining[l];
@@ -315,6 +343,7 @@ __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char*
     ms->maxkey[l] = mx;
   }
   __syncthreads();
+  RA_STAMP(A.status, 5);
   if (A.select_all && A.local_deal) {
     // nothing to deal: the lists were filled evenly and every entry wins
 #pragma unroll
@@ -343,20 +372,20 @@ __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char*
     if (take_eq > 0 && take_eq < n_eq) {   // uniform over the CTA
       if (tid == 0) ms->cut_found = 0;
       int seen = 0;
-      for (int wlo = 0; wlo < trange; wlo += kDetWindow) {
-        for (int w = tid; w < kDetWords; w += nthr) ms->bits[w] = 0u;
+      for (int wlo = 0; wlo < trange; wlo += det_window) {
+        for (int w = tid; w < A.det_words; w += nthr) det_bits[w] = 0u;
         __syncthreads();
         for_each_key(kl, n, tid, nthr, [&](uint32_t key, int i) {
           const unsigned t = (unsigned)(tag_of(i) - wlo);
-          if (key == kth && t < (unsigned)kDetWindow) atomicOr(&ms->bits[t >> 5], 1u << (t & 31));
+          if (key == kth && t < (unsigned)det_window) atomicOr(&det_bits[t >> 5], 1u << (t & 31));
         });
         __syncthreads();
-        const int total = bitmap_prefix(ms->bits, ms->wpre, ms->wsum, kDetWords, tid, nthr);
+        const int total = bitmap_prefix(det_bits, det_pre, ms->wsum, A.det_words, tid, nthr);
         if (seen + total >= take_eq) {
           const int need = take_eq - seen;   // 1-based rank inside this window
-          for (int w = tid; w < kDetWords; w += nthr) {
-            const int before = ms->wpre[w];
-            const uint32_t word = ms->bits[w];
+          for (int w = tid; w < A.det_words; w += nthr) {
+            const int before = det_pre[w];
+            const uint32_t word = det_bits[w];
             if (before < need && need <= before + __popc(word)) {
               ms->cut_tag = wlo + 32 * w + (int)__fns(word, 0, need - before);
               ms->cut_found = 1;
@@ -371,22 +400,22 @@ __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char*
       __syncthreads();
     }
     int base = 0;
-    for (int wlo = 0; wlo < trange; wlo += kDetWindow) {
-      for (int w = tid; w < kDetWords; w += nthr) ms->bits[w] = 0u;
+    for (int wlo = 0; wlo < trange; wlo += det_window) {
+      for (int w = tid; w < A.det_words; w += nthr) det_bits[w] = 0u;
       __syncthreads();
       for_each_key(kl, n, tid, nthr, [&](uint32_t key, int i) {
         const int tg = tag_of(i);
         const unsigned t = (unsigned)(tg - wlo);
-        if ((key > kth || (key == kth && tg <= cut)) && t < (unsigned)kDetWindow)
-          atomicOr(&ms->bits[t >> 5], 1u << (t & 31));
+        if ((key > kth || (key == kth && tg <= cut)) && t < (unsigned)det_window)
+          atomicOr(&det_bits[t >> 5], 1u << (t & 31));
       });
       __syncthreads();
-      const int total = bitmap_prefix(ms->bits, ms->wpre, ms->wsum, kDetWords, tid, nthr);
+      const int total = bitmap_prefix(det_bits, det_pre, ms->wsum, A.det_words, tid, nthr);
       for_each_key(kl, n, tid, nthr, [&](uint32_t key, int i) {
         const int tg = tag_of(i);
         const unsigned t = (unsigned)(tg - wlo);
-        if ((key > kth || (key == kth && tg <= cut)) && t < (unsigned)kDetWindow) {
-          const int p = off_win + base + ms->wpre[t >> 5] + __popc(ms->bits[t >> 5] & ((1u << (t & 31)) - 1u));
+        if ((key > kth || (key == kth && tg <= cut)) && t < (unsigned)det_window) {
+          const int p = off_win + base + det_pre[t >> 5] + __popc(det_bits[t >> 5] & ((1u << (t & 31)) - 1u));
           if (p < k) {
             const int dst = p / per, slot = p - dst * per;
             uint32_t* rk = cluster.map_shared_rank(sel_key, dst);
@@ -400,9 +429,10 @@ __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char*
       __syncthreads();
     }
   }
-  cluster.sync();
+  cluster_barrier(cluster, C);
   }
 
+  RA_STAMP(A.status, 6);
   // Centroid retrieval: the winners are cluster ids.  Rank every local winner among all k winners
   // of its list (descending score, ties by id; the peers' winners are read through distributed
   // shared memory) and write the clusters' member tokens in that order.
@@ -432,7 +462,7 @@ __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char*
         for (int i = lane; i < A.expand_clen; i += 32) dst[i] = t0 + i;
       }
     }
-    cluster.sync();  // nobody leaves or reuses its winner slots while a peer still ranks against them
+    cluster_barrier(cluster, C);  // nobody leaves or reuses its winner slots while a peer still ranks against them
     if (A.out_mode == kOutNone && !A.sel_idx) return;
   }
 
@@ -519,8 +549,9 @@ __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char*
     __syncthreads();
   }
 
+  RA_STAMP(A.status, 7);
   if (A.out_mode != kOutNone) {
-    cluster.sync();
+    cluster_barrier(cluster, C);
     const int dper = kHeadDim / C;  // the cluster size divides 128
     for (int item = tid; item < NL * dper; item += nthr) {
       const int l = item / dper, d = crank * dper + item % dper;
@@ -550,8 +581,9 @@ __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char*
         }
       }
     }
-    cluster.sync();  // nobody leaves while a peer may still read its shared memory
+    cluster_barrier(cluster, C);  // nobody leaves while a peer may still read its shared memory
   }
+  RA_STAMP(A.status, 8);
 }
 
 }  // namespace ra

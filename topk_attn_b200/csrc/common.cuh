@@ -108,6 +108,23 @@ __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, u
       "r"(c3)
       : "memory");
 }
+// The same load with an L2 eviction hint: rows that are read exactly once (a K stream) are marked
+// evict-first so that they do not push out data the next kernel re-reads (stored scores, V rows).
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ void tma_load_4d_hint(void* dst, const CUtensorMap* map, uint64_t* bar,
+                                                 int c0, int c1, int c2, int c3, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint "
+      "[%0], [%1, {%3, %4, %5, %6}], [%2], %7;"
+      ::"r"(smem_u32(dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2),
+      "r"(c3), "l"(policy)
+      : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
@@ -166,6 +183,20 @@ __device__ __forceinline__ float fast_exp2(float x) {
 #define RA_DEBUG(P, bit) ((P).debug & (bit))
 #else
 #define RA_DEBUG(P, bit) 0
+#endif
+
+// Phase stamps (RA_TUNING builds only): thread 0 of CTA 0 writes the wall clock into 64-bit slot
+// 4 + slot of the 256-byte status block, for reading back after the launch.
+#ifdef RA_TUNING
+#define RA_STAMP(status, slot)                                                              \
+  do {                                                                                      \
+    if (blockIdx.x == 0 && threadIdx.x == 0)                                                \
+      reinterpret_cast<unsigned long long*>(status)[4 + (slot)] = ra::global_timer_ns();    \
+  } while (0)
+#else
+#define RA_STAMP(status, slot) \
+  do {                         \
+  } while (0)
 #endif
 
 // host-side count of kernel launches (read through ra_launch_count)

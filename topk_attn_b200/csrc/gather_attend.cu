@@ -25,7 +25,7 @@ gather_attend_kernel(const __grid_constant__ GatherParams P) {
   const int bq = row / P.m.hq_total, hq = row % P.m.hq_total;
   const int hkv = hq / P.group;
 
-  const size_t scratch_bytes = (sizeof(MergeScratch) + (size_t)P.m.per * 8 + 127) & ~size_t(127);
+  const size_t scratch_bytes = select_scratch_bytes(1, P.m.per, 0);
   uint32_t* keys = reinterpret_cast<uint32_t*>(smem + scratch_bytes);
   int* idxs = reinterpret_cast<int*>(keys + P.cap);
   int* cnt = idxs + P.cap;
@@ -429,7 +429,7 @@ cudaError_t launch_kv_append(__half* kc, __half* vc, const __half* nk, const __h
 }
 
 size_t gather_attend_smem_bytes(int per, int cap, int n_src) {
-  return ((sizeof(MergeScratch) + (size_t)per * 8 + 127) & ~size_t(127)) + (size_t)cap * 8 + 16 +
+  return select_scratch_bytes(1, per, 0) + (size_t)cap * 8 + 16 +
          (size_t)n_src * 4 + 128;
 }
 

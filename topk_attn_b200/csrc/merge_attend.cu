@@ -21,7 +21,7 @@ merge_attend_kernel(const __grid_constant__ MergeParams P) {
   const int row = blockIdx.x / C;  // (batch row, query head)
   const int bq = row / P.m.hq_total, hq = row % P.m.hq_total;
 
-  const size_t scratch_bytes = (sizeof(MergeScratch) + (size_t)P.m.per * 8 + 127) & ~size_t(127);
+  const size_t scratch_bytes = select_scratch_bytes(1, P.m.per, P.m.det_words);
   uint32_t* keys = reinterpret_cast<uint32_t*>(smem + scratch_bytes);
   int* idxs = reinterpret_cast<int*>(keys + P.cap);
   int* cnt = idxs + P.cap;
@@ -53,7 +53,7 @@ merge_attend_kernel(const __grid_constant__ MergeParams P) {
 }
 
 size_t merge_attend_smem_bytes(int per, int cap) {
-  return ((sizeof(MergeScratch) + (size_t)per * 8 + 127) & ~size_t(127)) + (size_t)cap * 8 + 16 + 128;
+  return select_scratch_bytes(1, per, det_words_for(cap)) + (size_t)cap * 8 + 16 + 128;
 }
 
 cudaError_t launch_merge_attend(const MergeParams& P, int rows, size_t smem, cudaStream_t stream) {

@@ -587,7 +587,7 @@ scan_select_kernel(const __grid_constant__ ScanParams P) {
 size_t scan_smem_bytes(int nl, int cap, int nstages) {
   return (size_t)nstages * kStageBytes + (size_t)nl * cap * 8 + sizeof(Ctrl) + 128;
 }
-size_t merge_scratch_bytes(int nl, int per) { return sizeof(MergeScratch) + (size_t)nl * per * 8; }
+size_t merge_scratch_bytes(int nl, int per, int det_words) { return select_scratch_bytes(nl, per, det_words); }
 
 // ---------------------------------------------------------------------------- launcher
 template <int HG, int NQ>

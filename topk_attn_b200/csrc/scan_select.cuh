@@ -29,7 +29,7 @@ struct ScanParams {
 };
 
 size_t scan_smem_bytes(int nl, int cap, int nstages);
-size_t merge_scratch_bytes(int nl, int per);
+size_t merge_scratch_bytes(int nl, int per, int det_words);
 cudaError_t launch_scan_select(const ScanParams& P, int hg, int nq, int grid, size_t smem,
                                cudaStream_t stream);
 

@@ -56,7 +56,9 @@ scan_store_kernel(const __grid_constant__ StoreParams P) {
   if (warp == 8 * G) {
     // ------------------------------------------------------------ producer warp
     if (lane == 0) {
-      // every consumer group has its own ring of S/G stages and waits on every phase of it
+      // every consumer group has its own ring of S/G stages and waits on every phase of it; K is
+      // read once, so its lines may leave L2 first and the stored scores stay for the selection
+      const uint64_t once = l2_policy_evict_first();
       for (int it = 0; it < ntiles; ++it) {
         const int jt = it / G;
         const int s = (jt % SG) * G + (it % G);
@@ -65,8 +67,8 @@ scan_store_kernel(const __grid_constant__ StoreParams P) {
         const int tok = part_lo + it * kTileRows;
         unsigned char* dst = stages + (size_t)s * kStageBytes;
         mbar_expect_tx(&ctrl->full[s], kStageBytes);
-        tma_load_4d(dst, &P.kmap, &ctrl->full[s], 0, h0, tok, kv_b);
-        tma_load_4d(dst + kSwzHalfBytes, &P.kmap, &ctrl->full[s], 64, h0, tok, kv_b);
+        tma_load_4d_hint(dst, &P.kmap, &ctrl->full[s], 0, h0, tok, kv_b, once);
+        tma_load_4d_hint(dst + kSwzHalfBytes, &P.kmap, &ctrl->full[s], 64, h0, tok, kv_b, once);
       }
     }
   } else {

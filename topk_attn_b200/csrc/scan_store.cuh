@@ -40,7 +40,7 @@ struct SelectStoredParams {
 
 size_t scan_store_smem_bytes(int nq_valid, int nstages);
 cudaError_t launch_scan_store(const StoreParams& P, int grid, size_t smem, cudaStream_t stream);
-size_t select_stored_fixed_smem_bytes(int per);
+size_t select_stored_fixed_smem_bytes(int per, int det_words);
 cudaError_t launch_select_stored(const SelectStoredParams& P, int rows, size_t smem,
                                  cudaStream_t stream);
 

@@ -87,13 +87,14 @@ select_stored_kernel(const __grid_constant__ SelectStoredParams P) {
   const int bq = row / P.m.hq_total, hq = row % P.m.hq_total;
   const int k = P.m.topk, cap = P.cap;
 
-  const size_t scratch_bytes = select_scratch_bytes(1, P.m.per);
+  const size_t scratch_bytes = select_scratch_bytes(1, P.m.per, P.m.det_words);
   uint32_t* keys = reinterpret_cast<uint32_t*>(smem + scratch_bytes);
   int* idxs = reinterpret_cast<int*>(keys + cap);
   int* cnt = idxs + cap;
   int* hist0 = cnt + 4;                                        // [kHistBins]
   SelCtrl* sc = reinterpret_cast<SelCtrl*>(hist0 + kHistBins);
 
+  RA_STAMP(P.m.status, 0);
   // ---- 1. the coarse bin of the k-th key
   {
     const uint32_t* hrow = P.hist_ws + (size_t)row * P.nparts * kHistBins;
@@ -117,6 +118,7 @@ select_stored_kernel(const __grid_constant__ SelectStoredParams P) {
   const int lo = min(P.n_tokens, crank * P.chunk), hi = min(P.n_tokens, lo + P.chunk);
   const uint32_t* krow = P.keys_ws + (size_t)row * P.n_pad;
 
+  RA_STAMP(P.m.status, 1);
   // ---- 2. refine the bin while it holds too much for the candidate list
   int buf = 0, last_local = 0;
   while (n_above + n_in > cap && shift > 0) {
@@ -180,6 +182,7 @@ select_stored_kernel(const __grid_constant__ SelectStoredParams P) {
     tie_take = max(0, min(last_local, rem - before));
   }
 
+  RA_STAMP(P.m.status, 2);
   // ---- 3. candidates: every key at or above the lower edge of the bin
   const unsigned lt_mask = (1u << lane) - 1u;
   if (!tie_mode) {
@@ -290,6 +293,7 @@ select_stored_kernel(const __grid_constant__ SelectStoredParams P) {
   }
   __syncthreads();
 
+  RA_STAMP(P.m.status, 3);
   // ---- 4. exact k-th key over the cluster's candidates, winners dealt, V rows mixed
   MergeArgs A = P.m;
   A.list_off = 0;
@@ -301,11 +305,12 @@ select_stored_kernel(const __grid_constant__ SelectStoredParams P) {
     d.hkv = hq / P.group;
     return d;
   };
-  cluster_select_attend<1>(cluster, smem, keys, idxs, cnt, cap, A, dest, lo, max(hi - lo, 1));
+  cluster_select_attend<1>(cluster, smem, keys, idxs, cnt, cap, A, dest, lo, max(hi - lo, 1), lo_key, shift,
+                           n_above);
 }
 
-size_t select_stored_fixed_smem_bytes(int per) {
-  return select_scratch_bytes(1, per) + 16 + (size_t)kHistBins * 4 + sizeof(SelCtrl) + 128;
+size_t select_stored_fixed_smem_bytes(int per, int det_words) {
+  return select_scratch_bytes(1, per, det_words) + 16 + (size_t)kHistBins * 4 + sizeof(SelCtrl) + 128;
 }
 
 cudaError_t launch_select_stored(const SelectStoredParams& P, int rows, size_t smem,
