@@ -496,6 +496,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling)")
+    ap.add_argument("--collectives", action="store_true",
+                    help="multi-GPU: exchange through NCCL all-gathers instead of peer stores")
     ap.add_argument("--no-cfg4", action="store_true",
                     help="skip the configuration-4 strong-scaling record that follows the headline run")
     ap.add_argument("--phases", action="store_true",

@@ -251,7 +251,10 @@ size_t ra_flash_workspace_bytes(int32_t batch, int32_t num_q_heads, int32_t num_
  * with index_base = first global token id of the shard, (2) all-gathers the [B,Hq,k] score and
  * id buffers of all ranks, (3) calls ra_merge_attend, which selects the global top-k out of the
  * num_parts*k candidates and mixes only the V rows this rank holds into an un-normalised
- * partial, (4) all-gathers the partials and (5) calls ra_lse_combine. */
+ * partial, (4) all-gathers the partials and (5) calls ra_lse_combine.  Every rank merges the same
+ * candidates and the merge is deterministic (candidates are ranked by score, then by their
+ * position in the candidate array), so every rank selects the same set.  The two all-gathers
+ * are either collectives of a library (NCCL) or ra_exchange_push / ra_exchange_wait below. */
 typedef struct ra_merge_params {
   const float* cand_scores;    /* fp32 [num_parts, batch, num_q_heads, topk] */
   const int32_t* cand_indices; /* int32, same shape, global token ids */
@@ -283,6 +286,25 @@ int ra_merge_attend(const ra_merge_params* p);
  * the layout ra_merge_attend writes ([num_parts, rows, 130]); out is fp16 [rows, 128].  The
  * log-sum-exp merge of baseline_1.cu:549-598 as a stand-alone step. */
 int ra_lse_combine(const float* partials, int32_t num_parts, int32_t rows, void* out, void* stream);
+
+/* ---- exchange step of the sharded decode over peer-mapped memory (no counterpart in the
+ * reference; the in-GPU mechanism it generalises is the cluster-wide exchange through
+ * distributed shared memory of baseline_1.cu:549-598) ----
+ * Every rank owns a receive buffer that all ranks of the node have mapped (CUDA IPC or virtual
+ * memory management; the library only sees the resulting pointers).  ra_exchange_push copies
+ * `bytes` (a multiple of 16) from `src` into this rank's slot on every peer (peer_dst[i], host
+ * array of num_peers device pointers; an entry equal to src is not copied) with plain stores, and
+ * when all of it is written stores the current epoch (the 32-bit word at `epoch`, device memory) to
+ * this rank's flag on every peer (peer_flags[i]).  `done_counter` is a zero-initialised device word
+ * the launch uses and leaves at zero.  ra_exchange_wait makes the stream wait until each of the
+ * num_flags local flag words has reached the epoch, at most timeout_ns per flag; a wait that runs
+ * out sets the timeout bit of the status block at status_workspace (ra_check_status then reports
+ * RA_ERR_DEVICE_TIMEOUT) and the stream carries on.  With advance != 0 the wait ends by adding one
+ * to the epoch word, so that a captured sequence of these calls can be replayed unchanged. */
+int ra_exchange_push(const void* src, size_t bytes, void* const* peer_dst, void* const* peer_flags,
+                     int32_t num_peers, const void* epoch, void* done_counter, void* stream);
+int ra_exchange_wait(const void* flags, int32_t num_flags, void* epoch, int32_t advance,
+                     uint64_t timeout_ns, void* status_workspace, void* stream);
 
 #ifdef __cplusplus
 }

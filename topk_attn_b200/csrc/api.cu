@@ -13,6 +13,7 @@
 
 #include "center_select.cuh"
 #include "dense_select.cuh"
+#include "exchange.cuh"
 #include "flash_decode.cuh"
 #include "gather_attend.cuh"
 #include "merge_attend.cuh"
@@ -1289,6 +1290,47 @@ int ra_lse_combine(const float* partials, int32_t num_parts, int32_t rows, void*
   cudaError_t e = launch_lse_combine(partials, num_parts, rows, static_cast<__half*>(out),
                                      static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail(e, "lse_combine launch");
+  return RA_OK;
+}
+
+int ra_exchange_push(const void* src, size_t bytes, void* const* peer_dst, void* const* peer_flags,
+                     int32_t num_peers, const void* epoch, void* done_counter, void* stream) {
+  if (!src || !peer_dst || !peer_flags || !epoch || !done_counter) return invalid("a required pointer is null");
+  if (num_peers < 1 || num_peers > kMaxPeers) return invalid("num_peers must be in [1, 32]");
+  if (bytes == 0 || (bytes & 15u) || (reinterpret_cast<uintptr_t>(src) & 15u))
+    return invalid("src must be 16-byte aligned and bytes a positive multiple of 16");
+  PushParams pp;
+  memset(&pp, 0, sizeof pp);
+  pp.src = static_cast<const uint4*>(src);
+  pp.n16 = bytes / 16;
+  pp.npeers = num_peers;
+  for (int i = 0; i < num_peers; ++i) {
+    if (!peer_dst[i] || !peer_flags[i] || (reinterpret_cast<uintptr_t>(peer_dst[i]) & 15u) ||
+        (reinterpret_cast<uintptr_t>(peer_flags[i]) & 3u))
+      return invalid("peer pointers must be non-null and aligned (16 bytes for slots, 4 for flags)");
+    pp.dst[i] = static_cast<uint4*>(peer_dst[i]);
+    pp.flag[i] = static_cast<unsigned*>(peer_flags[i]);
+  }
+  pp.epoch = static_cast<const unsigned*>(epoch);
+  pp.done = static_cast<unsigned*>(done_counter);
+  const int grid = (int)std::max<size_t>(1, std::min<size_t>((size_t)2 * sm_count(),
+                                                              (pp.n16 + kPushThreads - 1) / kPushThreads));
+  cudaError_t e = launch_exchange_push(pp, grid, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "exchange_push launch");
+  return RA_OK;
+}
+
+int ra_exchange_wait(const void* flags, int32_t num_flags, void* epoch, int32_t advance,
+                     uint64_t timeout_ns, void* status_workspace, void* stream) {
+  if (!flags || !epoch || !status_workspace) return invalid("a required pointer is null");
+  if (num_flags < 1 || num_flags > kMaxPeers) return invalid("num_flags must be in [1, 32]");
+  if (timeout_ns == 0) return invalid("timeout_ns must be positive");
+  cudaError_t e = launch_exchange_wait(static_cast<const unsigned*>(flags), num_flags,
+                                       static_cast<unsigned*>(epoch), advance,
+                                       (unsigned long long)timeout_ns,
+                                       static_cast<unsigned*>(status_workspace),
+                                       static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "exchange_wait launch");
   return RA_OK;
 }
 

@@ -13,7 +13,8 @@
 //
 // The epoch lives in device memory and is advanced by the last wait of a step, so a captured CUDA
 // graph of the step can be replayed without changing any kernel argument.  Only plain loads and
-// stores touch peer memory: no multicast, no bulk-tensor copies.  The reference is single-device;
+// stores touch peer memory (no switch-side replication, no bulk-tensor copies).  The reference is
+// single-device;
 // the in-GPU mechanism this generalises is the cluster-wide max/sum exchange through distributed
 // shared memory of baseline_1.cu:549-598.
 #include "exchange.cuh"

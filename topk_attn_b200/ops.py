@@ -272,7 +272,8 @@ def kv_append(k_cache: Tensor, v_cache: Tensor, new_k: Tensor, new_v: Tensor, po
 
 
 def merge_attend(cand_scores: Tensor, cand_indices: Tensor, v: Tensor, topk: int, sm_scale: float,
-                 own_base: int, partial: bool = True, return_indices: bool = False):
+                 own_base: int, partial: bool = True, return_indices: bool = False,
+                 out: Optional[Tensor] = None):
     """Select the global top-k out of ``cand_* [parts,B,Hq,topk]`` (global ids) and mix the V rows
     held in ``v`` (global ids own_base .. own_base+N).  Returns the fp32 partial [B,Hq,130]
     (128 un-normalised sums, weight, maximum) or, with ``partial=False``, the fp16 output."""
@@ -289,12 +290,15 @@ def merge_attend(cand_scores: Tensor, cand_indices: Tensor, v: Tensor, topk: int
     p.cand_scores, p.cand_indices, p.num_parts = cand_scores.data_ptr(), cand_indices.data_ptr(), parts
     p.cand_part_stride = st[0]
     p.v = v.data_ptr()
-    out = None
     if partial:
-        out = torch.empty(B, Hq, 130, dtype=torch.float32, device=dev)
+        if out is None:
+            out = torch.empty(B, Hq, 130, dtype=torch.float32, device=dev)
+        elif out.dtype != torch.float32 or not out.is_contiguous() or out.shape != (B, Hq, 130):
+            raise ValueError("out must be a contiguous fp32 [B,Hq,130] tensor")
         p.out_partial = out.data_ptr()
     else:
-        out = torch.empty(B, Hq, 128, dtype=torch.float16, device=dev)
+        if out is None:
+            out = torch.empty(B, Hq, 128, dtype=torch.float16, device=dev)
         p.out = out.data_ptr()
     p.batch, p.num_q_heads, p.num_kv_heads, p.head_dim, p.num_tokens = B, Hq, Hkv, 128, N
     p.kv_batch_stride = N * Hkv * 128 if v.dim() == 4 else 0
@@ -321,6 +325,30 @@ def lse_combine(partials: Tensor, out: Optional[Tensor] = None) -> Tensor:
     capi.check(capi.lib().ra_lse_combine(partials.data_ptr(), parts, B * Hq, out.data_ptr(),
                                          _stream_ptr()))
     return out
+
+
+def exchange_push(src: Tensor, peer_dst, peer_flags, epoch: Tensor, done: Tensor) -> None:
+    """Store the contiguous tensor ``src`` (a multiple of 16 bytes) into the slots ``peer_dst``
+    (device addresses as ints, one per rank; the own slot may be ``src`` itself) and then the epoch
+    word into ``peer_flags`` (this rank's flag word on every rank).  Plain stores over peer-mapped
+    memory, enqueued on the current stream."""
+    n = len(peer_dst)
+    if n != len(peer_flags) or not src.is_contiguous():
+        raise ValueError("one slot and one flag per rank; src contiguous")
+    arr = C.c_void_p * n
+    capi.check(capi.lib().ra_exchange_push(src.data_ptr(), src.numel() * src.element_size(),
+                                           arr(*peer_dst), arr(*peer_flags), n, epoch.data_ptr(),
+                                           done.data_ptr(), _stream_ptr()))
+
+
+def exchange_wait(flags: Tensor, epoch: Tensor, advance: bool, timeout_s: float = 2.0) -> None:
+    """Make the current stream wait until every word of ``flags`` (int32, one per rank) has reached
+    the epoch; a wait that outlasts ``timeout_s`` is reported by ``check_status``.  With ``advance``
+    the epoch word is incremented afterwards."""
+    ws = workspace(256, flags.device)
+    capi.check(capi.lib().ra_exchange_wait(flags.data_ptr(), flags.numel(), epoch.data_ptr(),
+                                           1 if advance else 0, int(timeout_s * 1e9), ws.data_ptr(),
+                                           _stream_ptr()))
 
 
 def check_status(device: Optional[torch.device] = None) -> None:

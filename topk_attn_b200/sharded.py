@@ -9,16 +9,24 @@ Per step every rank
   5. combines them through their log-sum-exp.  Every rank ends with the full output.
 
 The reference has no multi-device code; the result is defined as equal to the single-device
-operator on the concatenated cache.  Collectives go through ``torch.distributed`` (NCCL on GPUs,
-gloo in the CPU tests); the compute steps go through the C ABI (``CudaBackend``).  The class only
-orchestrates, so the same logic runs in CPU tests with a stand-in backend.
+operator on the concatenated cache.  The two exchanges (steps 2 and 4) run in one of two ways:
+
+* as collectives of ``torch.distributed`` (NCCL on GPUs, gloo in the CPU tests), or
+* with the library's own kernels over peer-mapped memory (``PeerExchange``): every rank stores its
+  piece straight into its slot of every peer's receive buffer with plain stores and raises a flag
+  there; the consumer's stream waits for the flags of all ranks, each wait bounded in time.  The
+  whole step is then kernels on one stream and can be replayed as one CUDA graph.
+
+The compute steps go through the C ABI (``CudaBackend``).  The class only orchestrates, so the same
+logic runs in CPU tests with a stand-in backend.
 """
 from __future__ import annotations
 
 import json
 import os
+import sys
 import time
-from typing import Optional
+from typing import List, Optional
 
 import torch
 import torch.distributed as dist
@@ -38,26 +46,130 @@ class CudaBackend:
         return ops.gemv_topk(q, k, topk, index_base=index_base, out=out)
 
     def merge_partial(self, cand_sc: Tensor, cand_idx: Tensor, v: Tensor, topk: int,
-                      sm_scale: float, own_base: int) -> Tensor:
+                      sm_scale: float, own_base: int, out: Optional[Tensor] = None) -> Tensor:
         from . import ops
-        return ops.merge_attend(cand_sc, cand_idx, v, topk, sm_scale, own_base, partial=True)
+        return ops.merge_attend(cand_sc, cand_idx, v, topk, sm_scale, own_base, partial=True, out=out)
 
     def combine(self, partials: Tensor) -> Tensor:
         from . import ops
         return ops.lse_combine(partials)
 
 
+class PeerExchange:
+    """Receive buffers of one rank for the two exchanges of a step, laid out identically on every
+    rank inside one int32 buffer that all ranks have mapped:
+
+        candidates  [world][2][B][Hq][k]   slot r = rank r's (scores as fp32 bits, ids)
+        partials    [world][B][Hq][130]    slot r = rank r's un-normalised partial (fp32 bits)
+        flags       [2][32]                word r of row 0 / 1 = epoch of rank r's last candidate /
+                                           partial push
+
+    ``base_ptrs[p]`` is the address of rank p's buffer as seen from this process (how the memory
+    got mapped is not this class's business: symmetric memory on real ranks, plain tensors of one
+    device for logical ranks in tests).  Slots are written by ``ops.exchange_push`` (plain stores
+    over peer memory, then a flag) and read after ``ops.exchange_wait``.  The buffers are reused every
+    step without double buffering: a rank pushes the candidates of step s+1 only after its own
+    combine of step s, which waited for every rank's partial of step s, and a rank pushes a partial
+    only after its merge has finished reading the candidates."""
+
+    ALIGN = 64  # words: regions start on 256-byte boundaries
+
+    @classmethod
+    def layout(cls, world: int, B: int, Hq: int, topk: int):
+        slot_c, slot_p = 2 * B * Hq * topk, B * Hq * 130
+        if slot_c % 4 or slot_p % 4:
+            raise ValueError("slots must be multiples of 16 bytes (B*Hq*k and B*Hq even)")
+        up = lambda x: (x + cls.ALIGN - 1) // cls.ALIGN * cls.ALIGN
+        off_c = 0
+        off_p = up(off_c + world * slot_c)
+        off_f = up(off_p + world * slot_p)
+        return slot_c, slot_p, off_c, off_p, off_f, off_f + 64
+
+    def __init__(self, buf: Tensor, base_ptrs: List[int], rank: int, world: int, B: int, Hq: int,
+                 topk: int, timeout_s: float = 2.0):
+        slot_c, slot_p, off_c, off_p, off_f, words = self.layout(world, B, Hq, topk)
+        if buf.dtype != torch.int32 or buf.numel() < words or world > 32:
+            raise ValueError("buffer too small or of the wrong type, or more than 32 ranks")
+        self.buf, self.rank, self.world, self.timeout_s = buf, rank, world, timeout_s
+        self.cand = buf[off_c:off_c + world * slot_c].view(world, 2, B, Hq, topk)
+        self.cand_sc = self.cand[:, 0].view(torch.float32)
+        self.cand_idx = self.cand[:, 1]
+        self.partials = buf[off_p:off_p + world * slot_p].view(torch.float32).view(world, B, Hq, 130)
+        self.flags_c = buf[off_f:off_f + world]
+        self.flags_p = buf[off_f + 32:off_f + 32 + world]
+        self.epoch = torch.ones(1, dtype=torch.int32, device=buf.device)
+        self.done = torch.zeros(1, dtype=torch.int32, device=buf.device)
+        self.dst_c = [b + 4 * (off_c + rank * slot_c) for b in base_ptrs]
+        self.dst_p = [b + 4 * (off_p + rank * slot_p) for b in base_ptrs]
+        self.flg_c = [b + 4 * (off_f + rank) for b in base_ptrs]
+        self.flg_p = [b + 4 * (off_f + 32 + rank) for b in base_ptrs]
+
+    def push_candidates(self) -> None:
+        from . import ops
+        ops.exchange_push(self.cand[self.rank], self.dst_c, self.flg_c, self.epoch, self.done)
+
+    def wait_candidates(self) -> None:
+        from . import ops
+        ops.exchange_wait(self.flags_c, self.epoch, advance=False, timeout_s=self.timeout_s)
+
+    def push_partial(self) -> None:
+        from . import ops
+        ops.exchange_push(self.partials[self.rank], self.dst_p, self.flg_p, self.epoch, self.done)
+
+    def wait_partials(self) -> None:
+        """Also ends the step: the epoch advances by one."""
+        from . import ops
+        ops.exchange_wait(self.flags_p, self.epoch, advance=True, timeout_s=self.timeout_s)
+
+
+def make_peer_exchange(B: int, Hq: int, topk: int, device, group=None) -> Optional[PeerExchange]:
+    """Receive buffers in symmetric memory (``torch.distributed._symmetric_memory``: one allocation
+    per rank, mapped into every rank of the node).  Returns None -- on every rank alike -- when the
+    buffers cannot be set up, and the caller stays on the collectives.  Multicast binding of the
+    allocation is switched off: only plain peer loads and stores are used."""
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    ex, ok = None, 1
+    try:
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm
+        words = PeerExchange.layout(world, B, Hq, topk)[-1]
+        buf = symm.empty(words, dtype=torch.int32, device=device)
+        buf.zero_()
+        hdl = symm.rendezvous(buf, group if group is not None else dist.group.WORLD)
+        ex = PeerExchange(buf, [int(p) for p in hdl.buffer_ptrs], rank, world, B, Hq, topk)
+        ex._handle = hdl     # keeps the mappings alive
+    except Exception as e:   # noqa: BLE001 - any failure means "use the collectives"
+        print(f"[topk_attn_b200] rank {rank}: peer exchange unavailable ({type(e).__name__}: {e})",
+              file=sys.stderr)
+        ok = 0
+    flag = torch.tensor([ok], device=device)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+    torch.cuda.synchronize()
+    dist.barrier(group)      # every buffer is zeroed before anyone pushes
+    return ex if flag.item() else None
+
+
 class ShardedTopkAttention:
-    def __init__(self, topk: int, sm_scale: float = 1.0, group=None, backend=None):
+    def __init__(self, topk: int, sm_scale: float = 1.0, group=None, backend=None,
+                 exchange: Optional[PeerExchange] = None):
         self.topk, self.sm_scale, self.group = topk, sm_scale, group
         self.backend = backend if backend is not None else CudaBackend()
-        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
-        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.exchange = exchange
+        if exchange is not None:
+            self.world, self.rank = exchange.world, exchange.rank
+        else:
+            self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+            self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self._recv = self._send = self._partials = None
+        self._graph = None
 
     def _buffers(self, B: int, Hq: int, device):
         """Scores and ids of one rank are the two halves of one int32 buffer, so that a single
         all-gather moves both: recv [world, 2, B, Hq, k], send [2, B, Hq, k]."""
+        if self.exchange is not None:
+            ex = self.exchange
+            self._recv, self._send, self._partials = ex.cand, ex.cand[self.rank], ex.partials
+            return ex.cand_sc, ex.cand_idx, ex.partials
         shape = (self.world, 2, B, Hq, self.topk)
         if self._recv is None or self._recv.shape != shape or self._recv.device != device:
             self._recv = torch.empty(shape, dtype=torch.int32, device=device)
@@ -93,20 +205,72 @@ class ShardedTopkAttention:
         cand_sc, cand_idx, partials = self._buffers(B, Hq, q.device)
         idx, sc = self.local_candidates(q, k, index_base)
         self.exchange_candidates(idx, sc)
+        self.merge_and_exchange(cand_sc, cand_idx, partials, v, index_base)
+        return self.backend.combine(partials)
+
+    def merge_and_exchange(self, cand_sc: Tensor, cand_idx: Tensor, partials: Tensor, v: Tensor,
+                           index_base: int) -> None:
+        """Steps 3 and 4: this rank's partial over the global winners it owns, then every rank's
+        partial into ``partials``."""
+        if self.exchange is not None:
+            self.backend.merge_partial(cand_sc, cand_idx, v, self.topk, self.sm_scale, index_base,
+                                       out=partials[self.rank])
+            self.exchange.push_partial()
+            self.exchange.wait_partials()
+            return
         part = self.backend.merge_partial(cand_sc, cand_idx, v, self.topk, self.sm_scale, index_base)
         if self.world > 1:
             _all_gather(partials, part, self.group)
         else:
             partials[0].copy_(part)
-        return self.backend.combine(partials)
+
+    def capture(self, q: Tensor, k: Tensor, v: Tensor, index_base: Optional[int] = None):
+        """Capture one step on (q, k, v) into a CUDA graph and return a function that replays it and
+        gives the step's output tensor (the same tensor on every replay; new queries are copied
+        into ``q`` before a replay).  Only with the peer exchange: then the step is nothing but the
+        library's kernels on one stream.  Every rank must call this at the same point, because the
+        warm-up step it runs is a real exchange."""
+        if self.exchange is None:
+            raise RuntimeError("capture() needs the peer exchange")
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            self.step(q, k, v, index_base)          # allocates this stream's scratch
+            side.synchronize()
+            with torch.cuda.graph(graph, stream=side):
+                out = self.step(q, k, v, index_base)
+        torch.cuda.current_stream().wait_stream(side)
+        self._graph, self._graph_stream = graph, side
+
+        def replay() -> Tensor:
+            graph.replay()
+            return out
+        return replay
+
+
+def _check_graph_status(self) -> None:
+    """Raise if a kernel of the captured step gave up a bounded wait (its status word lives in the
+    scratch of the capture stream)."""
+    from . import ops
+    torch.cuda.synchronize()
+    with torch.cuda.stream(self._graph_stream):
+        ops.check_status(self.exchange.buf.device)
+
+
+ShardedTopkAttention.check_graph_status = _check_graph_status
 
 
 def _exchange(self, idx: Tensor, sc: Tensor) -> None:
-    """All ranks' (score, id) proposals into the receive buffer with one collective."""
+    """All ranks' (score, id) proposals into the receive buffer: one collective, or peer stores
+    followed by a bounded wait for every rank's flag."""
     if idx.data_ptr() != self._send[1].data_ptr():
         self._send[1].copy_(idx)
         self._send[0].view(torch.float32).copy_(sc)
-    if self.world > 1:
+    if self.exchange is not None:
+        self.exchange.push_candidates()
+        self.exchange.wait_candidates()
+    elif self.world > 1:
         _all_gather(self._recv, self._send, self.group)
     else:
         self._recv[0].copy_(self._send)
@@ -213,48 +377,56 @@ def verify_sharded_step(op: "ShardedTopkAttention", q: Tensor, k: Tensor, v: Ten
 
 def time_sharded(op: "ShardedTopkAttention", q: Tensor, k: Tensor, v: Tensor, index_base: int,
                  steps: int, warmup: int):
-    """Device time of ``steps`` sharded steps, max over ranks, and the share of the local scan.
-    Returns (ms per step, scan ms per step, launches of this rank in the timed region)."""
+    """Device time of ``steps`` sharded steps, max over ranks, and of the local scan alone.  With the
+    peer exchange the step is replayed from a CUDA graph.  Returns (ms per step, scan ms per step,
+    launches of this rank per step, how the step was issued)."""
     from . import capi, ops
     dev = q.device
-    B, Hq, _ = q.shape
+    multi = op.world > 1 and dist.is_initialized()
+    run, how = (lambda: op.step(q, k, v, index_base)), "eager"
+    c0 = capi.lib().ra_launch_count()
+    op.step(q, k, v, index_base)
+    launches = capi.lib().ra_launch_count() - c0
+    if op.exchange is not None:
+        run, how = op.capture(q, k, v, index_base), "cuda graph"
     for _ in range(max(warmup, 3)):
-        op.step(q, k, v, index_base)
+        run()
+    torch.cuda.synchronize()
     ops.check_status(dev)
-    if op.world > 1:
+    # the local scan alone (the dominant kernel), outside the steps
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    op._buffers(q.size(0), q.size(1), dev)
+    if multi:
+        dist.barrier()
+    a.record()
+    for _ in range(steps):
+        op.local_candidates(q, k, index_base)
+    b.record()
+    torch.cuda.synchronize()
+    scan_ms = a.elapsed_time(b) / steps
+    run()                       # the exchanged candidates are this step's again
+    if multi:
         dist.barrier()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sel = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
-           for _ in range(steps)]
-    launches0 = capi.lib().ra_launch_count()
     e0.record()
-    for i in range(steps):
-        # the scan is the dominant kernel: time it separately inside the step
-        cand_sc, cand_idx, partials = op._buffers(B, Hq, dev)
-        sel[i][0].record()
-        idx, sc = op.local_candidates(q, k, index_base)
-        sel[i][1].record()
-        op.exchange_candidates(idx, sc)
-        part = op.backend.merge_partial(cand_sc, cand_idx, v, op.topk, op.sm_scale, index_base)
-        if op.world > 1:
-            _all_gather(partials, part, op.group)
-        else:
-            partials[0].copy_(part)
-        op.backend.combine(partials)
+    for _ in range(steps):
+        run()
     e1.record()
-    launches = capi.lib().ra_launch_count() - launches0
     torch.cuda.synchronize()
     t = torch.tensor([e0.elapsed_time(e1)], device=dev)
-    if op.world > 1:
+    if multi:
         dist.barrier()
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    scan_ms = sum(a.elapsed_time(b) for a, b in sel) / steps
     ops.check_status(dev)
-    return t.item() / steps, scan_ms, launches
+    if op._graph is not None:
+        # the captured kernels report into the scratch of the stream they were captured on
+        op.check_graph_status()
+    return t.item() / steps, scan_ms, launches, how
 
 
-def bench_long_context(rank: int, world: int, dev, steps: int, warmup: int, peak_gbs: float) -> dict:
+def bench_long_context(rank: int, world: int, dev, steps: int, warmup: int, peak_gbs: float,
+                       collectives: bool = False) -> dict:
     """Configuration 4 (1 048 576 tokens, 32 query / 8 kv heads, k = 4096) cut over ``world`` ranks:
     total work is fixed, so the time per step should fall as ranks are added (strong scaling).  On
     one GPU the step is the single fused call; on several it is the sharded step.  Every record
@@ -281,16 +453,20 @@ def bench_long_context(rank: int, world: int, dev, steps: int, warmup: int, peak
         ops.check_status(dev)
         per_ms = e0.elapsed_time(e1) / steps
         scan_ms = per_ms
+        how, ex = "eager", None
     else:
-        op = ShardedTopkAttention(w.topk, w.sm_scale)
+        ex = None if collectives else make_peer_exchange(q.size(0), q.size(1), w.topk, dev)
+        op = ShardedTopkAttention(w.topk, w.sm_scale, exchange=ex)
         parity = verify_sharded_step(op, q, k, v, base)
-        per_ms, scan_ms, _ = time_sharded(op, q, k, v, base, steps, warmup)
+        per_ms, scan_ms, _, how = time_sharded(op, q, k, v, base, steps, warmup)
     n_total = world * n_local
     alg_per_gpu = w.kv_bytes_scanned() + q.size(1) * w.topk * 128 * 2 // world
     return {"workload": "cfg4: B1 Hq32/Hkv8 N1048576 k4096, tokens cut over the ranks",
             "n_gpus": world, "context": n_total, "context_per_gpu": n_local, "scaling": "strong",
             "us_per_step": per_ms * 1e3, "tokens_per_s": n_total / (per_ms * 1e-3),
             "scan_us": scan_ms * 1e3, "exchange_us": (per_ms - scan_ms) * 1e3,
+            "exchange": "none" if world == 1 else ("peer stores + flags" if ex is not None else "nccl all_gather x2"),
+            "issued_as": how,
             "roofline_frac_step": alg_per_gpu / (per_ms * 1e-3) / 1e9 / peak_gbs,
             "algorithmic_bytes_per_gpu": alg_per_gpu, "parity": parity}
 
@@ -309,14 +485,16 @@ def bench(args, rank: int, local: int, world: int, ClockSampler, measured_peak_g
     else:
         w = W.fused_topk_128k_shard(rank, world, device=dev)
     q, k, v = w.q, w.k, w.v
-    op = ShardedTopkAttention(w.topk, w.sm_scale)
+    collectives = bool(getattr(args, "collectives", False))
+    ex = None if collectives else make_peer_exchange(q.size(0), q.size(1), w.topk, dev)
+    op = ShardedTopkAttention(w.topk, w.sm_scale, exchange=ex)
     n_local = w.n_tokens
     base = rank * n_local
 
     parity = verify_sharded_step(op, q, k, v, base)
     sampler = ClockSampler(local)
     sampler.start()
-    per_ms, scan_ms, launches = time_sharded(op, q, k, v, base, args.steps, args.warmup)
+    per_ms, scan_ms, launches, how = time_sharded(op, q, k, v, base, args.steps, args.warmup)
     clocks = sampler.stop()
 
     q_host = q.cpu().pin_memory()
@@ -342,12 +520,14 @@ def bench(args, rank: int, local: int, world: int, ClockSampler, measured_peak_g
     alg = w.algorithmic_bytes()
     heads_q, heads_kv, batch, bkv, topk = q.size(1), k.size(-2), w.batch, w.bkv, w.topk
     peak, kind = measured_peak_gbs()
+    exchange_label = "peer stores + flags" if ex is not None else "nccl all_gather x2"
 
     long_ctx = None
     if not strong and not args.no_cfg4:
-        del w, q, k, v, op, q_dev
+        del w, q, k, v, op, q_dev, ex
         torch.cuda.empty_cache()
-        long_ctx = bench_long_context(rank, world, dev, min(args.steps, 100), args.warmup, peak)
+        long_ctx = bench_long_context(rank, world, dev, min(args.steps, 100), args.warmup, peak,
+                                      collectives)
 
     if rank == 0:
         achieved = alg / (scan_ms * 1e-3) / 1e9
@@ -362,7 +542,8 @@ def bench(args, rank: int, local: int, world: int, ClockSampler, measured_peak_g
                        "batch": batch, "heads_q": heads_q,
                        "heads_kv": heads_kv, "head_dim": 128, "context": world * n_local,
                        "context_per_gpu": n_local, "topk": topk, "caches": bkv,
-                       "l2": "inputs_exceed_l2", "collectives": "nccl all_gather x2"},
+                       "l2": "inputs_exceed_l2",
+                       "exchange": exchange_label, "issued_as": how},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_kind": kind + " (burst copy)",
                          "algorithmic_bytes": alg, "traffic": None,
@@ -372,7 +553,7 @@ def bench(args, rank: int, local: int, world: int, ClockSampler, measured_peak_g
             "e2e": {"value": tokens / e2e_s, "unit": "tokens/s", "us_per_step": e2e_s * 1e6,
                     "h2d_bytes_per_step": q_host.numel() * 2,
                     "d2h_bytes_per_step": out_host.numel() * 2},
-            "gpu_launches": launches * world,
+            "gpu_launches": launches * world * args.steps,
             "clocks": clocks,
             "parity": parity,
         }
