@@ -255,6 +255,22 @@ size_t ra_flash_workspace_bytes(int32_t batch, int32_t num_q_heads, int32_t num_
  * candidates and the merge is deterministic (candidates are ranked by score, then by their
  * position in the candidate array), so every rank selects the same set.  The two all-gathers
  * are either collectives of a library (NCCL) or ra_exchange_push / ra_exchange_wait below. */
+/* Optional exchange steps fused into ra_merge_attend (see ra_exchange_push / ra_exchange_wait for
+ * the buffers, flags and epoch word): the merge first waits for the candidate flags of all ranks
+ * (bounded), and after writing out_partial stores the same rows into this rank's slot on every
+ * peer and raises this rank's flag there. */
+typedef struct ra_exchange_hooks {
+  const void* wait_flags;      /* local flag words to wait for before candidates are read, or NULL */
+  int32_t num_wait_flags;
+  const void* epoch;           /* device word holding the current epoch */
+  uint64_t wait_timeout_ns;
+  void* const* peer_partials;  /* host array: out_partial's address in every rank (own entry =
+                                  out_partial itself), or NULL */
+  void* const* peer_flags;     /* host array: this rank's partial flag word on every rank */
+  int32_t num_peers;
+  void* done_counter;          /* zero-initialised device word */
+} ra_exchange_hooks;
+
 typedef struct ra_merge_params {
   const float* cand_scores;    /* fp32 [num_parts, batch, num_q_heads, topk] */
   const int32_t* cand_indices; /* int32, same shape, global token ids */
@@ -278,6 +294,7 @@ typedef struct ra_merge_params {
   void* workspace;             /* >= 256 bytes, 256-byte aligned (status word only) */
   size_t workspace_bytes;
   void* stream;
+  const ra_exchange_hooks* exchange;  /* optional, with out_partial only */
 } ra_merge_params;
 
 int ra_merge_attend(const ra_merge_params* p);
@@ -286,6 +303,13 @@ int ra_merge_attend(const ra_merge_params* p);
  * the layout ra_merge_attend writes ([num_parts, rows, 130]); out is fp16 [rows, 128].  The
  * log-sum-exp merge of baseline_1.cu:549-598 as a stand-alone step. */
 int ra_lse_combine(const float* partials, int32_t num_parts, int32_t rows, void* out, void* stream);
+/* The same after a bounded wait for the num_flags partial flags of all ranks (ra_exchange_wait's
+ * rules); the kernel ends the step by adding one to the epoch word.  done_counter is a
+ * zero-initialised device word, status_workspace a workspace whose status block takes the
+ * timeout bit. */
+int ra_lse_combine_wait(const float* partials, int32_t num_parts, int32_t rows, void* out,
+                        const void* wait_flags, int32_t num_flags, void* epoch, uint64_t timeout_ns,
+                        void* done_counter, void* status_workspace, void* stream);
 
 /* ---- exchange step of the sharded decode over peer-mapped memory (no counterpart in the
  * reference; the in-GPU mechanism it generalises is the cluster-wide exchange through

@@ -46,6 +46,7 @@ def struct_fields(name):
 
 @pytest.mark.parametrize("cname,pyname", [
     ("ra_params", "RaParams"), ("ra_merge_params", "RaMergeParams"),
+    ("ra_exchange_hooks", "RaExchangeHooks"),
     ("ra_gather_params", "RaGatherParams"), ("ra_center_params", "RaCenterParams"),
     ("ra_dense_params", "RaDenseParams"), ("ra_two_level_params", "RaTwoLevelParams"),
 ])
@@ -79,7 +80,7 @@ def test_shape_validation_without_a_device():
     p.head_dim, p.topk = 128, 0
     assert lib.ra_topk_attention(C.byref(p)) == capi.RA_ERR_INVALID_ARGUMENT
     assert lib.ra_legacy_workspace_bytes(4, 8192, 128) > 0
-    assert lib.ra_flash_workspace_bytes(8, 32, 8, 32768, 64) == 256 + 64 * 8 * 32 * 130 * 4
+    assert lib.ra_flash_workspace_bytes(8, 32, 8, 32768, 64) == 256 + 64 * 8 * 32 * 130 * 4 + 8 * 8 * 4
     assert lib.ra_center_workspace_bytes(1, 32, 2048, 64) > 0
 
 

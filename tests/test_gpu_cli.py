@@ -14,7 +14,7 @@ BIN = os.path.join(ROOT, "topk_attn_b200", "bin", "ra_verify")
 
 
 @pytest.mark.parametrize("mode,heads", [("topk", "4"), ("center", "32"), ("fd", "8"), ("s1", "4"),
-                                        ("s3", "4")])
+                                        ("s2", "4"), ("s3", "4")])
 def test_cli_verify(mode, heads):
     assert os.path.exists(BIN), "build with python -m topk_attn_b200.build"
     r = subprocess.run([BIN, mode, "--verify", heads, "--iters", "20"], capture_output=True,
@@ -23,5 +23,7 @@ def test_cli_verify(mode, heads):
     assert "PASS" in r.stdout and "FAIL" not in r.stdout
     if mode != "fd":
         assert "recall=100.0000%" in r.stdout
-    if mode in ("fd", "s1", "s3"):
+    if mode in ("fd", "s1", "s2", "s3"):
         assert "attention max |diff|" in r.stdout
+    if mode == "s2":      # the fused and the two-call pipeline agree (`make s2`'s printout)
+        assert "[S2] max |fused - unfused|" in r.stdout

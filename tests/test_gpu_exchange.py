@@ -68,6 +68,43 @@ def test_logical_ranks_exchange_by_peer_stores(G, B, Hq, Hkv, N, topk):
         assert torch.equal(exs[r].cand, exs[0].cand)       # every rank received every proposal
 
 
+@pytest.mark.parametrize("G,B,Hq,Hkv,N,topk", [
+    (4, 1, 8, 2, 32768, 512),
+    (8, 1, 32, 8, 65536, 4096),      # few rows, 32768 candidates each: cluster merge, separate wait and push
+    (8, 2, 32, 8, 65536, 4096),      # more rows: one CTA per row, ids stay in global memory
+    (2, 4, 8, 8, 16384, 1024),
+])
+def test_logical_ranks_with_the_exchange_fused_into_merge_and_combine(G, B, Hq, Hkv, N, topk):
+    """The product's step: the merge kernel waits for the candidate flags itself and stores its
+    partial rows into every peer's slot, the combine kernel waits for the partial flags and ends the
+    step by advancing the epoch."""
+    from topk_attn_b200 import ops
+    from topk_attn_b200.sharded import ShardedTopkAttention
+    q, k, v = rand_case(B, Hq, Hkv, N, False, seed=G + N + 1)
+    n = N // G
+    qd = q.to(DEV)
+    ks = [k[r * n:(r + 1) * n].contiguous().to(DEV) for r in range(G)]
+    vs = [v[r * n:(r + 1) * n].contiguous().to(DEV) for r in range(G)]
+    exs = logical_ranks(G, B, Hq, topk)
+    shard = [ShardedTopkAttention(topk, 0.9, exchange=exs[r]) for r in range(G)]
+    for step in range(2):
+        bufs = [shard[r]._buffers(B, Hq, DEV) for r in range(G)]
+        for r in range(G):
+            idx, sc = shard[r].local_candidates(qd, ks[r], r * n)
+            shard[r].exchange_candidates(idx, sc)
+        for r in range(G):
+            shard[r].merge_and_exchange(bufs[r][0], bufs[r][1], bufs[r][2], vs[r], r * n)
+        outs = [shard[r].backend.combine(bufs[r][2], exchange=exs[r]) for r in range(G)]
+        ops.check_status(DEV)
+        assert all(int(e.epoch.item()) == step + 2 for e in exs)
+    s = O.full_scores(q, k)
+    ref, _, _ = O.topk_sparse_attention(q, k, v, topk, 0.9, scores=s)
+    for r in range(G):
+        O.check_output(ref, outs[r])
+        assert torch.equal(outs[r], outs[0])
+        assert torch.equal(exs[r].partials, exs[0].partials)   # every rank received every partial
+
+
 def test_one_rank_step_replays_from_a_cuda_graph():
     from topk_attn_b200 import ops
     from topk_attn_b200.sharded import ShardedTopkAttention
@@ -109,3 +146,31 @@ def test_wait_runs_out_and_reports_a_timeout():
     out = ops.topk_attention(q.to(DEV), k.to(DEV), v.to(DEV), 64)
     ops.check_status(DEV)
     assert torch.isfinite(out.float()).all()
+
+
+def test_pipeline_wait_runs_out_and_reports_a_timeout(monkeypatch):
+    """The bounded wait on a TMA pipeline barrier of the scan kernel: in the tuning build the
+    producer can be told to leave its last tile out (no access out of place, the consumers simply
+    never see that tile arrive).  With a limit of a few milliseconds the kernel returns, the status
+    word reports the timeout, and after it is cleared the next call is fine."""
+    import time
+    from topk_attn_b200 import capi, ops
+    q, k, v = rand_case(1, 8, 8, 8192, False, seed=2)
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    monkeypatch.setenv("RA_DEBUG_FLAGS", "32")
+    monkeypatch.setenv("RA_WAIT_LIMIT_MS", "5")
+    with capi.tuning_library():
+        ops.check_status(DEV)
+        t0 = time.perf_counter()
+        ops.topk_attention(qd, kd, vd, 64)
+        with pytest.raises(capi.RaError) as e:
+            ops.check_status(DEV)
+        assert e.value.status == capi.RA_ERR_DEVICE_TIMEOUT
+        assert time.perf_counter() - t0 < 2.0
+        ops.workspace(256, DEV)[:4].zero_()
+        monkeypatch.delenv("RA_DEBUG_FLAGS")
+        out = ops.topk_attention(qd, kd, vd, 64)
+        ops.check_status(DEV)
+    ref = ops.topk_attention(qd, kd, vd, 64)
+    ops.check_status(DEV)
+    assert torch.equal(out, ref)

@@ -37,6 +37,16 @@ class RaParams(C.Structure):
     ]
 
 
+class RaExchangeHooks(C.Structure):
+    """Mirror of ``struct ra_exchange_hooks``."""
+    _fields_ = [
+        ("wait_flags", C.c_void_p), ("num_wait_flags", C.c_int32), ("epoch", C.c_void_p),
+        ("wait_timeout_ns", C.c_uint64),
+        ("peer_partials", C.POINTER(C.c_void_p)), ("peer_flags", C.POINTER(C.c_void_p)),
+        ("num_peers", C.c_int32), ("done_counter", C.c_void_p),
+    ]
+
+
 class RaMergeParams(C.Structure):
     """Mirror of ``struct ra_merge_params``."""
     _fields_ = [
@@ -49,6 +59,7 @@ class RaMergeParams(C.Structure):
         ("topk", C.c_int32), ("sm_scale", C.c_float), ("own_base", C.c_int32),
         ("out_indices", C.c_void_p), ("out_scores", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("stream", C.c_void_p),
+        ("exchange", C.POINTER(RaExchangeHooks)),
     ]
 
 
@@ -179,6 +190,7 @@ def _declare(l: C.CDLL) -> None:
         "ra_center_only_topk": (C.c_int, [C.POINTER(RaCenterParams)]),
         "ra_center_workspace_bytes": (sz, [i32, i32, i32, i32]),
         "ra_lse_combine": (C.c_int, [vp, i32, i32, vp, vp]),
+        "ra_lse_combine_wait": (C.c_int, [vp, i32, i32, vp, vp, i32, vp, C.c_uint64, vp, vp, vp]),
         "ra_exchange_push": (C.c_int, [vp, sz, C.POINTER(vp), C.POINTER(vp), i32, vp, vp, vp]),
         "ra_exchange_wait": (C.c_int, [vp, i32, vp, i32, C.c_uint64, vp, vp]),
     }

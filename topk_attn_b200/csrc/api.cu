@@ -217,9 +217,28 @@ bool plan_merge(int m_total, int topk, Plan& pl) {
 
 // The single-CTA merge when the row's candidates fit in one CTA's shared memory, else the cluster
 // form.
+// Whether the single-CTA merge takes these candidates: keys and ids in shared memory when both fit,
+// else the keys alone (ids fetched for the winners).  With few rows and long lists a cluster of CTAs
+// per row is quicker (the radix passes of one CTA over tens of thousands of keys are bound by its
+// shared-memory atomics), so the single CTA is kept for many rows or short lists.  Sets
+// mp.ids_global.
+bool merge_fits_one_cta(MergeParams& mp, int rows, size_t& smem) {
+  if (tuning_env("RA_FORCE_MERGE_CLUSTER")) return false;
+  const bool cluster_possible = merge_attend_smem_bytes(ceil_div(mp.m.topk, 8), ceil_div(mp.m_total, 8)) <= kSmemBudget;
+  if (cluster_possible && mp.m_total > 8192 && rows * 4 <= sm_count()) return false;
+  for (int ids_global = 0; ids_global < 2; ++ids_global) {
+    smem = merge_attend_cta_smem_bytes(mp.m_total, mp.m.topk, ids_global != 0);
+    if (smem <= kSmemBudget) {
+      mp.ids_global = ids_global;
+      return true;
+    }
+  }
+  return false;
+}
+
 cudaError_t dispatch_merge(MergeParams& mp, int rows, const Plan& pl, cudaStream_t stream) {
-  const size_t one = merge_attend_cta_smem_bytes(mp.m_total, mp.m.topk);
-  if (one <= kSmemBudget && !tuning_env("RA_FORCE_MERGE_CLUSTER")) {
+  size_t one = 0;
+  if (merge_fits_one_cta(mp, rows, one)) {
     mp.m.cluster = 1;
     return launch_merge_attend_cta(mp, rows, one, stream);
   }
@@ -499,9 +518,10 @@ int run(const ra_params* p, bool attend, const PartIds* ext = nullptr) {
   int dense_bshare = 1;
   if (!s.per_batch)
     for (int b = 1; b <= s.batch; ++b)
-      if (s.batch % b == 0 && b * c.group <= 4) dense_bshare = b;
+      if (s.batch % b == 0 && b * c.group <= 8) dense_bshare = b;
   // (one query per K row and one segment: the fused single launch of the scan kernel is quicker)
-  if (!ext && seg_len <= kDenseMaxSeg && c.group <= 4 && (s.segments > 1 || dense_bshare * c.group > 1) &&
+  if (!ext && seg_len <= kDenseMaxSeg &&
+      (s.segments > 1 || dense_bshare * c.group > 1 || tuning_env("RA_DENSE_SINGLE")) &&
       !tuning_env("RA_NO_DENSE_SELECT")) {
     const int bshare = dense_bshare;
     const int nq_valid = bshare * c.group, nq = next_pow2(nq_valid);
@@ -520,10 +540,14 @@ int run(const ra_params* p, bool attend, const PartIds* ext = nullptr) {
     dp.batch = s.batch; dp.hq = s.hq; dp.hkv = s.hkv; dp.group = c.group;
     dp.bshare = bshare; dp.nq_valid = nq_valid;
     dp.seg_len = seg_len; dp.segments = s.segments; dp.topk = s.topk;
+    // CTAs per (segment, kv head, batch group): about 512 rows each, but not more CTAs than run
+    // at once (two per multiprocessor): a second wave would double the time of a step this short
+    const int items = s.segments * s.hkv * (s.batch / bshare);
     int cl = 1;
-    while (cl < kDenseMaxCluster && seg_len > 512 * cl) cl <<= 1;
+    while (cl < kDenseMaxCluster && seg_len > 512 * cl && (long long)items * cl * 2 <= 2LL * sm_count()) cl <<= 1;
     dp.cluster = cl; dp.per = (ceil_div(seg_len, cl) + 3) & ~3;
     dp.index_base = p->index_base;
+    dp.status = status;
     dp.out_idx = p->out_indices ? p->out_indices : l_idx;
     dp.out_score = p->out_scores ? p->out_scores : l_score;
     if (verbose)
@@ -585,7 +609,9 @@ int run(const ra_params* p, bool attend, const PartIds* ext = nullptr) {
   sp.kv_per_batch = s.per_batch;
   sp.cap = pl.cap; sp.nstages = pl.nstages; sp.groups = pl.groups; sp.rendezvous = pl.rendezvous; sp.nparts = parts; sp.part_len = pl.part_len;
   sp.head_major = s.head_major;
+  sp.wait_limit_ns = kWaitLimitNs;
   if (const char* d = tuning_env("RA_DEBUG_FLAGS")) sp.debug = atoi(d);
+  if (const char* d = tuning_env("RA_WAIT_LIMIT_MS")) sp.wait_limit_ns = 1000000ull * (unsigned long long)std::max(1, atoi(d));
   MergeArgs& m = sp.m;
   m.topk = s.topk; m.per = pl.per; m.cluster = pl.cluster; m.det_words = pl.det_words;
   m.hq_total = s.hq; m.list_pitch = parts * s.topk; m.list_off = 0;
@@ -995,6 +1021,30 @@ int ra_center_only_topk(const ra_center_params* p) {
   sp.topk = p->top_clusters; sp.num_segments = 1; sp.sm_scale = 1.f;
   sp.workspace = p->workspace; sp.workspace_bytes = tail; sp.stream = p->stream;
   if (p->num_centers <= kCenterMaxCsz && !tuning_env("RA_NO_CENTER_SELECT")) {
+    if (attend && n_members <= (1 << 20) && !tuning_env("RA_NO_CENTER_ATTEND")) {
+      // selection, expansion and attention in one launch; ids only leave the kernel when asked for
+      CenterSelectParams cp;
+      memset(&cp, 0, sizeof cp);
+      cp.q = static_cast<const __half*>(p->q);
+      cp.centers = static_cast<const __half*>(p->centers);
+      cp.heads = p->num_heads; cp.csz = p->num_centers; cp.topc = p->top_clusters; cp.clen = p->cluster_len;
+      // as many CTAs per row as fit on the machine at once (one CTA of this kernel per
+      // multiprocessor): a second wave would double the time of a step this short
+      int cluster = 1;
+      while (cluster < kCenterMaxCluster && (long long)rows * cluster * 2 <= sm_count()) cluster <<= 1;
+      cp.cluster = cluster;
+      cp.per = (ceil_div(p->num_centers, cluster) + 3) & ~3;
+      cp.out_cluster_ids = p->out_cluster_ids; cp.out_scores = nullptr; cp.out_members = p->out_indices;
+      cp.k = static_cast<const __half*>(p->k); cp.v = static_cast<const __half*>(p->v);
+      cp.out = static_cast<__half*>(p->out);
+      cp.batch_stride = p->kv_batch_stride; cp.token_stride = p->kv_token_stride;
+      cp.head_stride = p->kv_head_stride; cp.n_tokens = p->num_tokens;
+      cp.scale_log2e = (p->sm_scale > 0.f ? p->sm_scale : 1.f) * kLog2e;
+      cp.status = static_cast<unsigned*>(p->workspace);
+      cudaError_t e = launch_center_attend(cp, (int)rows, static_cast<cudaStream_t>(p->stream));
+      if (e != cudaSuccess) return cuda_fail(e, "center_attend launch");
+      return RA_OK;
+    }
     int* ids = p->out_cluster_ids ? p->out_cluster_ids : c_ids;
     int st = center_select(p->q, p->centers, p->batch, p->num_heads, p->num_centers, p->top_clusters,
                            p->cluster_len, ids, c_score, attend ? nullptr : p->out_indices,
@@ -1280,8 +1330,71 @@ int ra_merge_attend(const ra_merge_params* p) {
                                        : (long long)p->batch * p->num_q_heads * p->topk;
   mp.row_stride = p->topk;
   mp.m_total = (int)m_total; mp.cap = pl.cap2; mp.group = p->num_q_heads / p->num_kv_heads;
-  cudaError_t e = dispatch_merge(mp, p->batch * p->num_q_heads, pl, static_cast<cudaStream_t>(p->stream));
+  cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
+  const int rows = p->batch * p->num_q_heads;
+  const ra_exchange_hooks* xh = p->exchange;
+  if (xh) {
+    if (!p->out_partial) return invalid("exchange hooks need out_partial");
+    if (!xh->epoch) return invalid("exchange hooks need the epoch word");
+    if (xh->wait_flags && (xh->num_wait_flags < 1 || xh->num_wait_flags > kMaxPeers || xh->wait_timeout_ns == 0))
+      return invalid("bad wait flags in the exchange hooks");
+    if (xh->peer_partials && (!xh->peer_flags || !xh->done_counter || xh->num_peers < 1 || xh->num_peers > kMaxPeers))
+      return invalid("bad peer slots in the exchange hooks");
+  }
+  size_t one = 0;
+  const bool cta = merge_fits_one_cta(mp, rows, one);
+  cudaError_t e;
+  if (xh && cta) {
+    // wait and push inside the merge kernel
+    ExchangeHooks& x = mp.x;
+    x.wait_flags = static_cast<const unsigned*>(xh->wait_flags);
+    x.wait_n = xh->wait_flags ? xh->num_wait_flags : 0;
+    x.epoch = static_cast<const unsigned*>(xh->epoch);
+    x.limit_ns = xh->wait_timeout_ns;
+    if (xh->peer_partials) {
+      x.npeers = xh->num_peers;
+      for (int i = 0; i < xh->num_peers; ++i) {
+        x.peer_rows[i] = static_cast<float*>(xh->peer_partials[i]);
+        x.peer_flag[i] = static_cast<unsigned*>(xh->peer_flags[i]);
+      }
+      x.done = static_cast<unsigned*>(xh->done_counter);
+    }
+  } else if (xh && xh->wait_flags) {
+    e = launch_exchange_wait(static_cast<const unsigned*>(xh->wait_flags), xh->num_wait_flags,
+                             const_cast<unsigned*>(static_cast<const unsigned*>(xh->epoch)), 0,
+                             xh->wait_timeout_ns, m.status, stream);
+    if (e != cudaSuccess) return cuda_fail(e, "exchange_wait launch");
+  }
+  e = dispatch_merge(mp, rows, pl, stream);
   if (e != cudaSuccess) return cuda_fail(e, "merge_attend launch");
+  if (xh && !cta && xh->peer_partials) {
+    const size_t bytes = (size_t)rows * (kHeadDim + 2) * sizeof(float);
+    return ra_exchange_push(p->out_partial, bytes, xh->peer_partials, xh->peer_flags, xh->num_peers,
+                            xh->epoch, xh->done_counter, p->stream);
+  }
+  return RA_OK;
+}
+
+int ra_lse_combine_wait(const float* partials, int32_t num_parts, int32_t rows, void* out,
+                        const void* wait_flags, int32_t num_flags, void* epoch, uint64_t timeout_ns,
+                        void* done_counter, void* status_workspace, void* stream) {
+  if (!partials || !out || num_parts < 1 || rows < 1) return invalid("bad lse_combine arguments");
+  if (!wait_flags || !epoch || !done_counter || !status_workspace || num_flags < 1 ||
+      num_flags > kMaxPeers || timeout_ns == 0)
+    return invalid("bad exchange arguments");
+  ExchangeHooks x;
+  memset(&x, 0, sizeof x);
+  x.wait_flags = static_cast<const unsigned*>(wait_flags);
+  x.wait_n = num_flags;
+  x.epoch = static_cast<const unsigned*>(epoch);
+  x.limit_ns = timeout_ns;
+  x.done = static_cast<unsigned*>(done_counter);
+  x.advance = 1;
+  x.epoch_rw = static_cast<unsigned*>(epoch);
+  cudaError_t e = launch_lse_combine(partials, num_parts, rows, static_cast<__half*>(out),
+                                     static_cast<cudaStream_t>(stream), &x,
+                                     static_cast<unsigned*>(status_workspace));
+  if (e != cudaSuccess) return cuda_fail(e, "lse_combine launch");
   return RA_OK;
 }
 

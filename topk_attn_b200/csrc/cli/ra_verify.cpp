@@ -12,6 +12,9 @@
 //                                                      (flash_decoding.cu:32-37,413-421)
 //   ra_verify s1     [--verify [heads]] [--iters N]    two-level selection, then gathered attention:
 //                                                      two calls per step (baseline_1.cu:663-701)
+//   ra_verify s2     [--verify [heads]] [--iters N]    the pipeline as one call, then once more as two
+//                                                      calls, printing max |fused - unfused| over the
+//                                                      outputs (`make s2`, baseline_2.cu:1166-1181)
 //   ra_verify s3     [--verify [heads]] [--iters N]    the same pipeline as one call
 //                                                      (baseline_3.cu:595, the fused version)
 //
@@ -183,13 +186,13 @@ bool check_attention(const Problem& p, int heads, const std::vector<int>& ids, i
 
 int main(int argc, char** argv) {
   if (argc < 2) {
-    fprintf(stderr, "usage: %s topk|center|fd|s1|s3 [--verify [heads]] [--iters N]\n", argv[0]);
+    fprintf(stderr, "usage: %s topk|center|fd|s1|s2|s3 [--verify [heads]] [--iters N]\n", argv[0]);
     return 1;
   }
   Problem p;
   const std::string mode = argv[1];
   const bool random_ids = mode == "fd";
-  if (mode == "topk" || mode == "s1" || mode == "s3" || mode == "fd") {
+  if (mode == "topk" || mode == "s1" || mode == "s2" || mode == "s3" || mode == "fd") {
     p.CSZ = 32; p.CLEN = 1280; p.TOPC = 5; p.TOPK = 512;       // gemv_topk.cu:21-28
     p.attend = mode != "topk";
   } else if (mode == "center") {
@@ -258,7 +261,7 @@ int main(int argc, char** argv) {
   tl.kv_token_stride = (int64_t)p.H * p.D; tl.kv_head_stride = p.D; tl.sm_scale = scale;
   tl.out_cluster_ids = d_clusters; tl.out_indices = d_ids;
   tl.workspace = ws; tl.workspace_bytes = ws_bytes; tl.stream = stream;
-  if (mode == "s3") { tl.v = d_v; tl.out = d_out; }            // selection + attention in one call
+  if (mode == "s3" || mode == "s2") { tl.v = d_v; tl.out = d_out; }   // selection + attention in one call
   ra_center_params ce;
   memset(&ce, 0, sizeof ce);
   ce.q = d_q; ce.centers = d_centers; ce.batch = 1; ce.num_heads = p.H; ce.head_dim = p.D;
@@ -295,6 +298,30 @@ int main(int argc, char** argv) {
          mode.c_str(), p.H, p.CSZ, p.CLEN, p.TOPC, p.TOPK, ms * 1000.f / iters, iters);
 
   int rc = 0;
+  if (mode == "s2") {
+    // the unfused pipeline on the same inputs: selection only, then attention over its ids
+    std::vector<__half> fused(p.q.size()), unfused(p.q.size());
+    CK(cudaMemcpy(fused.data(), d_out, fused.size() * 2, cudaMemcpyDeviceToHost));
+    __half* d_out2;
+    CK(cudaMalloc(&d_out2, p.q.size() * 2));
+    ra_two_level_params sel = tl;
+    sel.v = nullptr; sel.out = nullptr;
+    ra_gather_params ga2 = ga;
+    ga2.out = d_out2;
+    RA(ra_two_level_topk(&sel));
+    RA(ra_gathered_attention(&ga2));
+    RA(ra_check_status(ws, stream));
+    CK(cudaMemcpy(unfused.data(), d_out2, unfused.size() * 2, cudaMemcpyDeviceToHost));
+    cudaFree(d_out2);
+    double worst = 0, excess = 0;
+    for (size_t i = 0; i < fused.size(); ++i) {
+      const double a = __half2float(fused[i]), b = __half2float(unfused[i]);
+      worst = std::max(worst, std::fabs(a - b));
+      excess = std::max(excess, std::fabs(a - b) - (1e-3 + 1e-2 * std::fabs(b)));
+    }
+    printf("[S2] max |fused - unfused| = %.3e -> %s\n", worst, excess <= 0 ? "PASS" : "FAIL");
+    if (excess > 0) rc = 3;
+  }
   if (verify) {
     std::vector<int> gpu(out_elems), cpu;
     CK(cudaMemcpy(gpu.data(), d_ids, out_elems * 4, cudaMemcpyDeviceToHost));
@@ -314,7 +341,7 @@ int main(int argc, char** argv) {
              aok ? "PASS" : "FAIL");
       ok = ok && aok;
     }
-    rc = ok ? 0 : 3;
+    if (!ok) rc = 3;
   }
   cudaFree(d_q); cudaFree(d_centers); cudaFree(d_kv); cudaFree(d_ids); cudaFree(d_clusters); cudaFree(ws);
   if (d_v) cudaFree(d_v);

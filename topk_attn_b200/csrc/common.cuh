@@ -79,18 +79,19 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-// Wait on an mbarrier phase for at most kWaitLimitNs of wall time.  Returns false when the limit
+// Wait on an mbarrier phase for at most limit_ns (default kWaitLimitNs) of wall time.  Returns false when the limit
 // ran out or when another thread of the CTA already gave up (*abort != 0); in both cases *abort is
 // set, the caller records that in the status word and carries on so that every barrier stays
 // matched and the kernel ends promptly.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, volatile int* abort) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, volatile int* abort,
+                                          unsigned long long limit_ns = kWaitLimitNs) {
   const uint32_t addr = smem_u32(bar);
   if (mbar_try_wait(addr, parity)) return true;
   const unsigned long long t0 = global_timer_ns();
   for (;;) {
     if (mbar_try_wait(addr, parity)) return true;
     if (*abort) return false;
-    if (global_timer_ns() - t0 > kWaitLimitNs) {
+    if (global_timer_ns() - t0 > limit_ns) {
       *abort = 1;
       return false;
     }

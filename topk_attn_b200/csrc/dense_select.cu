@@ -7,7 +7,7 @@
 // retrieval_attn/retrieval_attention.cu:254-472: 4 chunks of 2048 keys, top-K of each) and of
 // gemv_topk_kernel (gemv_topk.cu:173-380) on short inputs.  One cluster of CTAs per (segment, kv
 // head, group of batch rows that share the cache): each CTA scores a slice of the segment's K rows
-// for all NQ queries at once (half-warp per row, one 128-bit load per lane, NQ dot products) and
+// for all queries of the row at once (tensor cores, 16 rows per warp and step, up to 8 queries) and
 // stores the scores into the shared memory of every CTA of the cluster.  After one cluster barrier
 // the CTAs divide the NQ score vectors among themselves; each runs the radix descent of
 // radix_winners.cuh on its vectors and writes the winners' ids and scores.
@@ -20,112 +20,105 @@ namespace cg = cooperative_groups;
 
 namespace ra {
 
-template <int NQ>
-__global__ void __launch_bounds__(kDenseThreads, 4)   // 64 registers: four CTAs per SM
+// Scoring on the tensor cores without staging K in shared memory: a warp takes 16 K rows per step
+// as the M dimension of mma.sync.m16n8k16 and the (up to 8) queries as N.  Lane (g, t) reads rows g
+// and g+8 straight from global memory in 16-byte pieces -- piece j of a row is bytes
+// 64j + 16t .. +15, so the four lanes of a row read 64 contiguous bytes per load -- and feeds the
+// words of a piece to the A fragments of two k-steps.  The k index of the product is only a
+// summation index, so any assignment of the 128 dims to k slots is valid as long as the query
+// fragments use the same one: lane (g, t) holds the matching 16-byte pieces of query g.
+__global__ void __launch_bounds__(kDenseThreads, 2)
 dense_select_kernel(const __grid_constant__ DenseSelectParams P) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   cg::cluster_group cluster = cg::this_cluster();
   const int C = P.cluster;
   const int crank = C > 1 ? (int)cluster.block_rank() : 0;
-  const int tid = threadIdx.x;
-  const int hw = tid >> 4, l16 = tid & 15;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
   const int item = blockIdx.x / C;
   const int seg = item % P.segments;
   const int hk = (item / P.segments) % P.hkv;
   const int b0 = (item / (P.segments * P.hkv)) * P.bshare;
   const int n = P.seg_len;
   const int n_pad = (n + 3) & ~3;
+  const int NQ = P.nq_valid;
 
   uint32_t* keys = reinterpret_cast<uint32_t*>(smem_raw);          // [NQ][n_pad]
   int* winners = reinterpret_cast<int*>(keys + (size_t)NQ * n_pad);  // [topk]
   __shared__ WinnerCtrl ctrl;
 
-  // ---- the queries of this K row: list qi is batch row b0 + qi / group, head hk*group + qi % group
-  float qf[NQ][8];
+  // ---- query g of this K row: batch row b0 + g / group, head hk*group + g % group
+  uint4 qreg[4];
+  if (g < NQ) {
+    const int b = b0 + g / P.group, h = hk * P.group + g % P.group;
+    const __half* qp = P.q + ((size_t)b * P.hq + h) * kHeadDim + 8 * t;
 #pragma unroll
-  for (int qi = 0; qi < NQ; ++qi) {
-    const int qv = min(qi, P.nq_valid - 1);   // padding lists repeat the last query, never written
-    const int b = b0 + qv / P.group, h = hk * P.group + qv % P.group;
-    const uint4 raw = *reinterpret_cast<const uint4*>(P.q + ((size_t)b * P.hq + h) * kHeadDim + l16 * 8);
-    const float2 a = h2f2(raw.x), bb = h2f2(raw.y), c = h2f2(raw.z), d = h2f2(raw.w);
-    qf[qi][0] = a.x; qf[qi][1] = a.y; qf[qi][2] = bb.x; qf[qi][3] = bb.y;
-    qf[qi][4] = c.x; qf[qi][5] = c.y; qf[qi][6] = d.x; qf[qi][7] = d.y;
+    for (int j = 0; j < 4; ++j) qreg[j] = *reinterpret_cast<const uint4*>(qp + 32 * j);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) qreg[j] = make_uint4(0u, 0u, 0u, 0u);
   }
+  RA_STAMP(P.status, 0);
   if (C > 1) cluster.sync();   // every CTA of the cluster is running before its memory is written
+  RA_STAMP(P.status, 1);
 
   // ---- scores of this CTA's slice, stored into every CTA of the cluster ----
   const int lo = crank * P.per, hi = min(n, lo + P.per);
   const __half* rows = P.k + (size_t)b0 * P.batch_stride + (size_t)hk * P.head_stride +
-                       (size_t)seg * n * P.token_stride + l16 * 8;
-  constexpr int U = NQ >= 4 ? 4 : 8;   // rows in flight per half-warp
-  constexpr int kRowsPerIter = (kDenseThreads / 16) * U;
-  for (int r0 = lo; r0 < hi; r0 += kRowsPerIter) {   // same trip count for all threads
-    uint4 kv[U];
+                       (size_t)seg * n * P.token_stride + 8 * t;
+  constexpr int kWarps = kDenseThreads / 32;
+  constexpr int GRP = 2;   // groups of 16 rows in flight per warp
+  for (int r0 = lo + warp * 16; r0 < hi; r0 += kWarps * 16 * GRP) {
+    uint4 a_lo[GRP][4], a_hi[GRP][4];
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int r = r0 + u * (kDenseThreads / 16) + hw;
-      kv[u] = r < hi ? ldg128_nc(rows + (size_t)r * P.token_stride) : make_uint4(0, 0, 0, 0);
+    for (int gi = 0; gi < GRP; ++gi) {
+      const int ra = r0 + gi * kWarps * 16 + g, rb = ra + 8;
+      const __half* pa = rows + (size_t)ra * P.token_stride;
+      const __half* pb = rows + (size_t)rb * P.token_stride;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        a_lo[gi][j] = ra < hi ? ldg128_nc(pa + 32 * j) : make_uint4(0u, 0u, 0u, 0u);
+        a_hi[gi][j] = rb < hi ? ldg128_nc(pb + 32 * j) : make_uint4(0u, 0u, 0u, 0u);
+      }
     }
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int r = r0 + u * (kDenseThreads / 16) + hw;
-      const float2 a = h2f2(kv[u].x), b = h2f2(kv[u].y), c = h2f2(kv[u].z), d = h2f2(kv[u].w);
-      float s[NQ];
+    for (int gi = 0; gi < GRP; ++gi) {
+      float c[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int qi = 0; qi < NQ; ++qi) {
-        float t = a.x * qf[qi][0];
-        t = fmaf(a.y, qf[qi][1], t); t = fmaf(b.x, qf[qi][2], t); t = fmaf(b.y, qf[qi][3], t);
-        t = fmaf(c.x, qf[qi][4], t); t = fmaf(c.y, qf[qi][5], t); t = fmaf(d.x, qf[qi][6], t);
-        t = fmaf(d.y, qf[qi][7], t);
-        s[qi] = t;
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t a0[4] = {a_lo[gi][j].x, a_hi[gi][j].x, a_lo[gi][j].y, a_hi[gi][j].y};
+        const uint32_t a1[4] = {a_lo[gi][j].z, a_hi[gi][j].z, a_lo[gi][j].w, a_hi[gi][j].w};
+        mma_16816(c, a0, qreg[j].x, qreg[j].y);
+        mma_16816(c, a1, qreg[j].z, qreg[j].w);
       }
-      // Transposing reduction over the 16 lanes of the row: each exchange halves the number of
-      // queries a lane carries, so lane l ends with the full sum of query l / (16 / NQ).
-      float tot;
-      if constexpr (NQ == 4) {
-        const bool up8 = l16 & 8, up4 = l16 & 4;
-        float a0 = up8 ? s[2] : s[0], a1 = up8 ? s[3] : s[1];
-        const float b0 = up8 ? s[0] : s[2], b1 = up8 ? s[1] : s[3];
-        a0 += __shfl_xor_sync(0xffffffffu, b0, 8);
-        a1 += __shfl_xor_sync(0xffffffffu, b1, 8);
-        tot = up4 ? a1 : a0;
-        const float give = up4 ? a0 : a1;
-        tot += __shfl_xor_sync(0xffffffffu, give, 4);
-      } else if constexpr (NQ == 2) {
-        const bool up8 = l16 & 8;
-        tot = up8 ? s[1] : s[0];
-        const float give = up8 ? s[0] : s[1];
-        tot += __shfl_xor_sync(0xffffffffu, give, 8);
-        tot += __shfl_xor_sync(0xffffffffu, tot, 4);
-      } else {
-        tot = s[0];
-        tot += __shfl_xor_sync(0xffffffffu, tot, 8);
-        tot += __shfl_xor_sync(0xffffffffu, tot, 4);
-      }
-      tot += __shfl_xor_sync(0xffffffffu, tot, 2);
-      tot += __shfl_xor_sync(0xffffffffu, tot, 1);
-      // the 16 / NQ lanes that hold a query's sum deal its C stores among themselves
-      if (r < hi) {
-        constexpr int kLanesPerQuery = 16 / NQ;
-        const int qi = l16 / kLanesPerQuery;
-        uint32_t* dst = &keys[(size_t)qi * n_pad + r];
-        const uint32_t key = score_key(tot);
-        if (C > 1) {
-          for (int c2 = l16 % kLanesPerQuery; c2 < C; c2 += kLanesPerQuery)
-            *cluster.map_shared_rank(dst, c2) = key;
-        } else if (l16 % kLanesPerQuery == 0) {
-          *dst = key;
+      // lane (g, t) holds the scores of rows g, g+8 for the queries 2t, 2t+1
+      const int ra = r0 + gi * kWarps * 16 + g;
+#pragma unroll
+      for (int jv = 0; jv < 4; ++jv) {
+        const int qi = 2 * t + (jv & 1);
+        const int r = ra + 8 * (jv >> 1);
+        if (qi < NQ && r < hi) {
+          uint32_t* dst = &keys[(size_t)qi * n_pad + r];
+          const uint32_t key = score_key(c[jv]);
+          if (C > 1) {
+            for (int c2 = 0; c2 < C; ++c2) *cluster.map_shared_rank(dst, c2) = key;
+          } else {
+            *dst = key;
+          }
         }
       }
     }
   }
+  RA_STAMP(P.status, 2);
   if (C > 1) cluster.sync(); else __syncthreads();
+  RA_STAMP(P.status, 3);
   // from here on a CTA touches its own shared memory only
 
-  // ---- CTA c selects on score vectors c, c + C, ...; the winners of a vector are written in the
-  // order the descent found them (lists are unordered inside a segment) ----
+  // ---- CTA c selects on score vectors c, c + C, ...; the winners of a vector are written in
+  // ascending token order (lists are unordered inside a segment for the caller, but a fixed order
+  // makes the attention that follows reproducible) ----
   const int id0 = P.index_base + seg * n;
-  for (int l = crank; l < P.nq_valid; l += C) {   // CTA-uniform
+  for (int l = crank; l < NQ; l += C) {   // CTA-uniform
     const uint32_t* kl = keys + (size_t)l * n_pad;
     select_winners<kDenseThreads>(kl, n, P.topk, ctrl, winners);
     const int nwin = min(ctrl.nwin, P.topk);
@@ -138,6 +131,7 @@ dense_select_kernel(const __grid_constant__ DenseSelectParams P) {
     }
     __syncthreads();   // winners and ctrl are reused by the next vector
   }
+  RA_STAMP(P.status, 4);
 }
 
 size_t dense_select_smem_bytes(int nq, int seg_len, int topk) {
@@ -145,12 +139,10 @@ size_t dense_select_smem_bytes(int nq, int seg_len, int topk) {
 }
 
 cudaError_t launch_dense_select(const DenseSelectParams& P, int nq, cudaStream_t stream) {
-  void (*kern)(const DenseSelectParams) = nullptr;
-  if (nq == 1) kern = dense_select_kernel<1>;
-  if (nq == 2) kern = dense_select_kernel<2>;
-  if (nq == 4) kern = dense_select_kernel<4>;
-  if (!kern) return cudaErrorInvalidValue;
-  const size_t smem = dense_select_smem_bytes(nq, P.seg_len, P.topk);
+  (void)nq;
+  if (P.nq_valid < 1 || P.nq_valid > 8) return cudaErrorInvalidValue;
+  auto kern = dense_select_kernel;
+  const size_t smem = dense_select_smem_bytes(P.nq_valid, P.seg_len, P.topk);
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   cudaLaunchConfig_t cfg = {};

@@ -20,6 +20,7 @@ struct DenseSelectParams {
   int index_base;         // added to the token ids written
   int* out_idx;           // [batch, hq, segments * topk], unordered inside a segment
   float* out_score;       // same shape: q.K of the listed ids
+  unsigned* status;       // status block of the caller's workspace
 };
 
 size_t dense_select_smem_bytes(int nq, int seg_len, int topk);

@@ -21,15 +21,6 @@
 
 namespace ra {
 
-__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
-  unsigned v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-
 __global__ void __launch_bounds__(kPushThreads)
 exchange_push_kernel(const __grid_constant__ PushParams P) {
   const size_t stride = (size_t)gridDim.x * kPushThreads;

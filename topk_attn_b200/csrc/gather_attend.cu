@@ -9,6 +9,7 @@
 // the expansion loop of center_only_topk/gemv_topk.cu:271-279.  The output is written once, no
 // atomics, no pre-zeroing.
 #include "gather_attend.cuh"
+#include "gather_flash.cuh"
 
 namespace ra {
 
@@ -131,15 +132,6 @@ gather_attend_kernel(const __grid_constant__ GatherParams P) {
   cluster_select_attend<1>(cluster, smem, keys, idxs, cnt, P.cap, A, dest);
 }
 
-// Attention over the id list in one pass: every half-warp streams K and V rows of its ids
-// together, keeps a running maximum / weight / weighted sum (online softmax in the log2 domain),
-// and the partials are merged through their log-sum-exp inside the warp, across the warps in
-// shared memory and across the CTAs of the cluster in distributed shared memory.
-struct GatherPartial {
-  float m, l;
-  float o[kHeadDim];
-};
-
 // UN: K and V rows in flight per half-warp.  GIVEN: the list carries the raw scores q.K of its ids
 // (src_score, expand_clen == 0), so only the V rows are read.
 template <int UN, bool GIVEN>
@@ -149,14 +141,12 @@ gather_flash_kernel(const __grid_constant__ GatherParams P) {
   cg::cluster_group cluster = cg::this_cluster();
   const int C = P.m.cluster;
   const int crank = (int)cluster.block_rank();
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  constexpr int kW = kMergeThreads / 32;
+  const int tid = threadIdx.x;
   const int row = blockIdx.x / C;
   const int bq = row / P.m.hq_total, hq = row % P.m.hq_total;
   const int hkv = hq / P.group;
-  GatherPartial* wpart = reinterpret_cast<GatherPartial*>(smem_g);  // [kW] per-warp partials
-  GatherPartial* cpart = wpart + kW;                                // this CTA's partial (peers read)
-  int* src = reinterpret_cast<int*>(cpart + 1);
+  GatherPartial* part = reinterpret_cast<GatherPartial*>(smem_g);
+  int* src = reinterpret_cast<int*>(smem_g + flash_partials_bytes<kMergeThreads>());
 
   const int* gsrc = P.src_idx + (size_t)bq * P.src_batch_stride + (size_t)hq * P.src_head_stride;
   const float* gsc = nullptr;
@@ -184,160 +174,21 @@ gather_flash_kernel(const __grid_constant__ GatherParams P) {
   auto token_of = [&](int e) {
     return P.expand_clen > 0 ? src[e / P.expand_clen] * P.expand_clen + e % P.expand_clen : src[e];
   };
+  auto score_of = [&](int e) { return gsc[e]; };
   if (P.out_token_ids) {
     int* dst = P.out_token_ids + (size_t)row * P.n_entries + lo;
     for (int i = tid; i < n; i += kMergeThreads) dst[i] = token_of(lo + i);
   }
-
-  const int half = lane >> 4, l16 = lane & 15;
-  float qf[8];
-  {
-    const uint4 a = *reinterpret_cast<const uint4*>(P.q + (size_t)row * kHeadDim + 8 * l16);
-    const uint32_t w[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float2 f = h2f2(w[i]);
-      qf[2 * i] = f.x * P.m.scale_log2e;
-      qf[2 * i + 1] = f.y * P.m.scale_log2e;
-    }
-  }
-  const size_t head_off = (size_t)bq * P.m.v_batch_stride + (size_t)hkv * P.m.v_head_stride + l16 * 8;
-  const __half* kb = P.k + head_off;
-  const __half* vb = P.m.v + head_off;
-  constexpr int kRowsPerIter = 2 * kW;
-  float m_run = -INFINITY, l_run = 0.f, acc[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-  // the trip count is the same for every lane: the shuffles below need the whole warp
-  for (int base = 0; base < n; base += kRowsPerIter * UN) {
-    uint4 kk[GIVEN ? 1 : UN], vv[UN];
-    float given[GIVEN ? UN : 1];
-    bool ok[UN];
-#pragma unroll
-    for (int u = 0; u < UN; ++u) {
-      const int e = base + warp * 2 + half + kRowsPerIter * u;
-      const int raw = (e < n) ? token_of(lo + e) : -1;
-      const int tok = raw - P.m.id_shift;
-      ok[u] = raw >= 0 && (unsigned)tok < (unsigned)P.m.n_tokens;
-      // an empty slot (-1) is skipped silently; any other id outside the cache is reported
-      if (e < n && raw >= 0 && !ok[u] && l16 == 0) atomicOr(P.m.status, kStatusBadId);
-      const size_t off = ok[u] ? (size_t)tok * P.m.v_token_stride : 0;
-      if constexpr (GIVEN) {
-        given[u] = ok[u] ? gsc[lo + e] * P.m.scale_log2e : 0.f;
-      } else {
-        kk[u] = ok[u] ? ldg128_nc(kb + off) : make_uint4(0u, 0u, 0u, 0u);
-      }
-      vv[u] = ok[u] ? ldg128_nc(vb + off) : make_uint4(0u, 0u, 0u, 0u);
-    }
-    float x[UN];
-    float bm = -INFINITY;
-#pragma unroll
-    for (int u = 0; u < UN; ++u) {
-      float a = 0.f;
-      if constexpr (GIVEN) {
-        a = given[u];
-      } else {
-        const uint32_t w[4] = {kk[u].x, kk[u].y, kk[u].z, kk[u].w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float2 f = h2f2(w[i]);
-          a = fmaf(f.x, qf[2 * i], a);
-          a = fmaf(f.y, qf[2 * i + 1], a);
-        }
-        a += __shfl_xor_sync(0xffffffffu, a, 8);
-        a += __shfl_xor_sync(0xffffffffu, a, 4);
-        a += __shfl_xor_sync(0xffffffffu, a, 2);
-        a += __shfl_xor_sync(0xffffffffu, a, 1);
-      }
-      x[u] = ok[u] ? a : -INFINITY;
-      bm = fmaxf(bm, x[u]);
-    }
-    const float m_new = fmaxf(m_run, bm);
-    if (m_new > -INFINITY) {
-      const float alpha = fast_exp2(m_run - m_new);
-      l_run *= alpha;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] *= alpha;
-#pragma unroll
-      for (int u = 0; u < UN; ++u) {
-        const float pw = fast_exp2(x[u] - m_new);
-        l_run += pw;
-        const uint32_t w[4] = {vv[u].x, vv[u].y, vv[u].z, vv[u].w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float2 f = h2f2(w[i]);
-          acc[2 * i] = fmaf(pw, f.x, acc[2 * i]);
-          acc[2 * i + 1] = fmaf(pw, f.y, acc[2 * i + 1]);
-        }
-      }
-      m_run = m_new;
-    }
-  }
-  // the two half-warps
-  {
-    const float m_o = __shfl_xor_sync(0xffffffffu, m_run, 16);
-    const float l_o = __shfl_xor_sync(0xffffffffu, l_run, 16);
-    const float m_n = fmaxf(m_run, m_o);
-    const float a_me = (m_run > -INFINITY) ? fast_exp2(m_run - m_n) : 0.f;
-    const float a_ot = (m_o > -INFINITY) ? fast_exp2(m_o - m_n) : 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const float o_o = __shfl_xor_sync(0xffffffffu, acc[i], 16);
-      acc[i] = acc[i] * a_me + o_o * a_ot;
-    }
-    l_run = l_run * a_me + l_o * a_ot;
-    m_run = m_n;
-  }
-  if (lane < 16) {
-#pragma unroll
-    for (int i = 0; i < 8; ++i) wpart[warp].o[lane * 8 + i] = acc[i];
-    if (lane == 0) {
-      wpart[warp].m = m_run;
-      wpart[warp].l = l_run;
-    }
-  }
-  __syncthreads();
-  if (tid < kHeadDim) {
-    float m = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < kW; ++w) m = fmaxf(m, wpart[w].m);
-    float o = 0.f, l = 0.f;
-#pragma unroll
-    for (int w = 0; w < kW; ++w) {
-      const float f = (wpart[w].m > -INFINITY) ? fast_exp2(wpart[w].m - m) : 0.f;
-      o = fmaf(f, wpart[w].o[tid], o);
-      l = fmaf(f, wpart[w].l, l);
-    }
-    cpart->o[tid] = o;
-    if (tid == 0) {
-      cpart->m = m;
-      cpart->l = l;
-    }
-  }
-  cluster.sync();
-  const int dper = kHeadDim / C;
-  if (tid < dper) {
-    const int d = crank * dper + tid;
-    float m = -INFINITY;
-    for (int c = 0; c < C; ++c) m = fmaxf(m, cluster.map_shared_rank(cpart, c)->m);
-    float o = 0.f, l = 0.f;
-    for (int c = 0; c < C; ++c) {
-      const GatherPartial* rp = cluster.map_shared_rank(cpart, c);
-      const float f = (rp->m > -INFINITY) ? fast_exp2(rp->m - m) : 0.f;
-      o = fmaf(f, rp->o[d], o);
-      l = fmaf(f, rp->l, l);
-    }
-    P.m.out[(size_t)row * kHeadDim + d] = __float2half_rn(o / l);
-    if (P.m.out_lse && d == 0) {
-      P.m.out_lse[(size_t)row * 2 + 0] = m * 0.6931471805599453f;  // natural-log domain
-      P.m.out_lse[(size_t)row * 2 + 1] = l;
-    }
-  }
-  cluster.sync();  // nobody leaves while a peer may still read its partial
+  const size_t head_off = (size_t)bq * P.m.v_batch_stride + (size_t)hkv * P.m.v_head_stride;
+  flash_over_entries<UN, GIVEN, kMergeThreads>(
+      cluster, C, crank, part, P.q + (size_t)row * kHeadDim, GIVEN ? P.m.v + head_off : P.k + head_off,
+      P.m.v + head_off, P.m.v_token_stride, P.m.n_tokens, P.m.id_shift, lo, n, P.m.scale_log2e,
+      P.m.status, P.m.out + (size_t)row * kHeadDim,
+      P.m.out_lse ? P.m.out_lse + (size_t)row * 2 : nullptr, token_of, score_of);
 }
 
 size_t gather_flash_smem_bytes(int n_src) {
-  return (kMergeThreads / 32 + 1) * sizeof(GatherPartial) + (size_t)n_src * 4 + 16;
+  return flash_partials_bytes<kMergeThreads>() + (size_t)n_src * 4 + 16;
 }
 
 cudaError_t launch_gather_flash(const GatherParams& P, int rows, size_t smem, cudaStream_t stream) {

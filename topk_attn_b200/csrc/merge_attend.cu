@@ -7,6 +7,8 @@
 // (retrieval_attn/retrieval_attention.cu:1243-1339) generalised with a selection step.
 #include "merge_attend.cuh"
 
+#include <cstring>
+
 namespace ra {
 
 __global__ void __launch_bounds__(kMergeThreads, 1)
@@ -80,27 +82,75 @@ cudaError_t launch_merge_attend(const MergeParams& P, int rows, size_t smem, cud
   return cudaLaunchKernelEx(&cfg, kern, P);
 }
 
+// One CTA of 128 threads per output row.  The (maximum, weight) pairs of all parts are fetched by
+// as many threads at once, one warp turns them into the common maximum and the parts' weights,
+// then thread d sums dimension d over the parts with eight loads in flight (one load at a time
+// would cost a full L2 round trip per part).
+constexpr int kCombineMaxParts = 1024;
+
 __global__ void __launch_bounds__(kHeadDim)
-lse_combine_kernel(const float* __restrict__ partials, int parts, int rows, __half* __restrict__ out) {
-  const int row = blockIdx.x, d = threadIdx.x;
-  float m = -INFINITY;
-  for (int p = 0; p < parts; ++p)
-    m = fmaxf(m, partials[((size_t)p * rows + row) * (kHeadDim + 2) + kHeadDim + 1]);
-  float o = 0.f, l = 0.f;
-  for (int p = 0; p < parts; ++p) {
-    const float* src = partials + ((size_t)p * rows + row) * (kHeadDim + 2);
-    const float lp = src[kHeadDim];
-    const float w = (lp > 0.f) ? __expf(src[kHeadDim + 1] - m) : 0.f;
-    o = fmaf(w, src[d], o);
-    l = fmaf(w, lp, l);
+lse_combine_kernel(const float* __restrict__ partials, int parts, int rows, __half* __restrict__ out,
+                   const ExchangeHooks X, unsigned* status) {
+  __shared__ float wt[kCombineMaxParts];
+  __shared__ float wsum4[4];
+  exchange_wait_in_kernel(X, status);   // every rank's partial has landed (bounded wait)
+  const int row = blockIdx.x, d = threadIdx.x, lane = d & 31;
+  const size_t pitch = (size_t)rows * (kHeadDim + 2);
+  const float* base = partials + (size_t)row * (kHeadDim + 2);
+  float o = 0.f;
+  if (parts <= kCombineMaxParts) {
+    float m = -INFINITY;
+    for (int p = d; p < parts; p += kHeadDim) m = fmaxf(m, __ldcg(base + (size_t)p * pitch + kHeadDim + 1));
+#pragma unroll
+    for (int off = 16; off; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+    if (lane == 0) wt[d >> 5] = m;
+    __syncthreads();
+    m = fmaxf(fmaxf(wt[0], wt[1]), fmaxf(wt[2], wt[3]));
+    __syncthreads();
+    float l = 0.f;
+    for (int p = d; p < parts; p += kHeadDim) {
+      const float lp = __ldcg(base + (size_t)p * pitch + kHeadDim);
+      const float w = (lp > 0.f) ? __expf(__ldcg(base + (size_t)p * pitch + kHeadDim + 1) - m) : 0.f;
+      wt[p] = w;
+      l = fmaf(w, lp, l);
+    }
+#pragma unroll
+    for (int off = 16; off; off >>= 1) l += __shfl_xor_sync(0xffffffffu, l, off);
+    if (lane == 0) wsum4[d >> 5] = l;
+    __syncthreads();
+    const float total = (wsum4[0] + wsum4[1]) + (wsum4[2] + wsum4[3]);   // fixed order: same bits every run
+    for (int p0 = 0; p0 < parts; p0 += 8) {
+      float x[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) x[u] = (p0 + u < parts) ? __ldcg(base + (size_t)(p0 + u) * pitch + d) : 0.f;
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (p0 + u < parts) o = fmaf(wt[p0 + u], x[u], o);
+    }
+    out[(size_t)row * kHeadDim + d] = __float2half_rn(o / total);
+  } else {
+    float m = -INFINITY;
+    for (int p = 0; p < parts; ++p) m = fmaxf(m, base[(size_t)p * pitch + kHeadDim + 1]);
+    float l = 0.f;
+    for (int p = 0; p < parts; ++p) {
+      const float* src = base + (size_t)p * pitch;
+      const float lp = src[kHeadDim];
+      const float w = (lp > 0.f) ? __expf(src[kHeadDim + 1] - m) : 0.f;
+      o = fmaf(w, src[d], o);
+      l = fmaf(w, lp, l);
+    }
+    out[(size_t)row * kHeadDim + d] = __float2half_rn(o / l);
   }
-  out[(size_t)row * kHeadDim + d] = __float2half_rn(o / l);
+  exchange_publish_in_kernel(X);        // ends the step: the last CTA advances the epoch
 }
 
 cudaError_t launch_lse_combine(const float* partials, int parts, int rows, __half* out,
-                               cudaStream_t stream) {
+                               cudaStream_t stream, const ExchangeHooks* x, unsigned* status) {
+  ExchangeHooks hooks;
+  memset(&hooks, 0, sizeof hooks);
+  if (x) hooks = *x;
   note_launch();
-  lse_combine_kernel<<<rows, kHeadDim, 0, stream>>>(partials, parts, rows, out);
+  lse_combine_kernel<<<rows, kHeadDim, 0, stream>>>(partials, parts, rows, out, hooks, status);
   return cudaGetLastError();
 }
 
@@ -131,14 +181,21 @@ merge_attend_cta_kernel(const __grid_constant__ MergeParams P) {
   const int bq = row / P.m.hq_total, hq = row % P.m.hq_total;
   const int hkv = hq / P.group;
   const int n = P.m_total, k = P.m.topk;
+  // candidate ids stay in global memory when keys and ids together would not fit (they are only
+  // needed for the k winners)
+  const bool ids_global = P.ids_global != 0;
   uint32_t* keys = reinterpret_cast<uint32_t*>(smem_m);
   int* idxs = reinterpret_cast<int*>(keys + n);
-  uint32_t* wkey = reinterpret_cast<uint32_t*>(idxs + n);  // winners
+  uint32_t* wkey = reinterpret_cast<uint32_t*>(idxs + (ids_global ? 0 : n));  // winners
   int* widx = reinterpret_cast<int*>(wkey + k);
   float* red = reinterpret_cast<float*>(widx + k);         // [32][128]
   MergeCtaCtrl* ctrl = reinterpret_cast<MergeCtaCtrl*>(red + 32 * kHeadDim);
   uint32_t* bits = reinterpret_cast<uint32_t*>(ctrl + 1);   // one bit per candidate
   int* wpre = reinterpret_cast<int*>(bits + ((n + 31) >> 5));
+  auto src_of = [&](int c) {
+    const int part = c / P.part_len, off = c - part * P.part_len;
+    return (size_t)part * P.part_stride + (size_t)row * P.row_stride + off;
+  };
 
   if (tid == 0) {
     ctrl->kmin = 0xffffffffu;
@@ -146,16 +203,30 @@ merge_attend_cta_kernel(const __grid_constant__ MergeParams P) {
     ctrl->wpos = 0;
     ctrl->eqc = 0;
   }
+  exchange_wait_in_kernel(P.x, P.m.status);   // the peers' candidates have landed (bounded wait)
   __syncthreads();
   uint32_t mn = 0xffffffffu, mx = 0u;
-  for (int c = tid; c < n; c += kMergeCtaThreads) {
-    const int part = c / P.part_len, off = c - part * P.part_len;
-    const size_t src = (size_t)part * P.part_stride + (size_t)row * P.row_stride + off;
-    const uint32_t key = score_key(P.cand_score[src]);
-    keys[c] = key;
-    idxs[c] = P.cand_idx[src];
-    mn = min(mn, key);
-    mx = max(mx, key);
+  constexpr int LU = 8;   // loads in flight per thread: the lists come from L2 or a peer's stores
+  for (int c0 = 0; c0 < n; c0 += kMergeCtaThreads * LU) {
+    float sc[LU];
+    int id[LU];
+#pragma unroll
+    for (int u = 0; u < LU; ++u) {
+      const int c = c0 + u * kMergeCtaThreads + tid;
+      sc[u] = c < n ? P.cand_score[src_of(c)] : 0.f;
+      id[u] = (c < n && !ids_global) ? P.cand_idx[src_of(c)] : 0;
+    }
+#pragma unroll
+    for (int u = 0; u < LU; ++u) {
+      const int c = c0 + u * kMergeCtaThreads + tid;
+      if (c < n) {
+        const uint32_t key = score_key(sc[u]);
+        keys[c] = key;
+        if (!ids_global) idxs[c] = id[u];
+        mn = min(mn, key);
+        mx = max(mx, key);
+      }
+    }
   }
 #pragma unroll
   for (int off = 16; off; off >>= 1) {
@@ -240,7 +311,7 @@ merge_attend_cta_kernel(const __grid_constant__ MergeParams P) {
       const int p = wpre[i >> 5] + __popc(bits[i >> 5] & ((1u << (i & 31)) - 1u));
       if (p < k) {
         wkey[p] = key;
-        widx[p] = idxs[i];
+        widx[p] = ids_global ? P.cand_idx[src_of(i)] : idxs[i];
       }
     }
   }
@@ -319,19 +390,31 @@ merge_attend_cta_kernel(const __grid_constant__ MergeParams P) {
         P.m.out_lse[(size_t)row * 2 + 1] = lt;
       }
     } else {
-      float* dstp = P.m.out_partial + (size_t)row * (kHeadDim + 2);
+      // this rank's partial row, and the same row into this rank's slot on every peer
+      const size_t roff = (size_t)row * (kHeadDim + 2);
+      float* dstp = P.m.out_partial + roff;
       dstp[tid] = o;
       if (tid == 0) {
         dstp[kHeadDim] = lt;
         dstp[kHeadDim + 1] = mscaled;
       }
+      for (int p = 0; p < P.x.npeers; ++p) {
+        float* pr = P.x.peer_rows[p];
+        if (pr == nullptr || pr == P.m.out_partial) continue;
+        pr[roff + tid] = o;
+        if (tid == 0) {
+          pr[roff + kHeadDim] = lt;
+          pr[roff + kHeadDim + 1] = mscaled;
+        }
+      }
     }
   }
+  exchange_publish_in_kernel(P.x);
 }
 
-size_t merge_attend_cta_smem_bytes(int m_total, int topk) {
-  return (size_t)m_total * 8 + (size_t)topk * 8 + 32 * kHeadDim * 4 + sizeof(MergeCtaCtrl) +
-         (size_t)((m_total + 31) / 32) * 8 + 64;
+size_t merge_attend_cta_smem_bytes(int m_total, int topk, bool ids_global) {
+  return (size_t)m_total * (ids_global ? 4 : 8) + (size_t)topk * 8 + 32 * kHeadDim * 4 +
+         sizeof(MergeCtaCtrl) + (size_t)((m_total + 31) / 32) * 8 + 64;
 }
 
 cudaError_t launch_merge_attend_cta(const MergeParams& P, int rows, size_t smem, cudaStream_t stream) {

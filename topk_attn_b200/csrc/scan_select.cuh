@@ -25,6 +25,7 @@ struct ScanParams {
   int part_len;              // tokens per part
   int head_major;            // 1: table is [H, N, 128] (centroids); one head per CTA
   int swizzled;              // 1: tiles are two 64-dim halves with the 128-byte swizzle (tensor-core scoring)
+  unsigned long long wait_limit_ns;   // bound of every wait on a pipeline barrier
   int debug;                 // RA_TUNING builds only: bits switch parts of the kernel off (phase timing)
 };
 

@@ -273,7 +273,7 @@ def kv_append(k_cache: Tensor, v_cache: Tensor, new_k: Tensor, new_v: Tensor, po
 
 def merge_attend(cand_scores: Tensor, cand_indices: Tensor, v: Tensor, topk: int, sm_scale: float,
                  own_base: int, partial: bool = True, return_indices: bool = False,
-                 out: Optional[Tensor] = None):
+                 out: Optional[Tensor] = None, exchange=None):
     """Select the global top-k out of ``cand_* [parts,B,Hq,topk]`` (global ids) and mix the V rows
     held in ``v`` (global ids own_base .. own_base+N).  Returns the fp32 partial [B,Hq,130]
     (128 un-normalised sums, weight, maximum) or, with ``partial=False``, the fp16 output."""
@@ -311,17 +311,41 @@ def merge_attend(cand_scores: Tensor, cand_indices: Tensor, v: Tensor, topk: int
         p.out_indices, p.out_scores = idx.data_ptr(), sc.data_ptr()
     ws = workspace(256, dev)
     p.workspace, p.workspace_bytes, p.stream = ws.data_ptr(), ws.numel(), _stream_ptr()
+    if exchange is not None:
+        # exchange: an object with the fields of sharded.PeerExchange -- the merge waits for the
+        # candidate flags itself and pushes its partial rows to the peers
+        if not partial:
+            raise ValueError("the fused exchange works on partial outputs")
+        n = len(exchange.dst_p)
+        arr = C.c_void_p * n
+        h = capi.RaExchangeHooks()
+        h.wait_flags, h.num_wait_flags = exchange.flags_c.data_ptr(), exchange.flags_c.numel()
+        h.epoch, h.wait_timeout_ns = exchange.epoch.data_ptr(), int(exchange.timeout_s * 1e9)
+        keep = (arr(*exchange.dst_p), arr(*exchange.flg_p))
+        h.peer_partials = C.cast(keep[0], C.POINTER(C.c_void_p))
+        h.peer_flags = C.cast(keep[1], C.POINTER(C.c_void_p))
+        h.num_peers, h.done_counter = n, exchange.done[1:2].data_ptr()
+        p.exchange = C.pointer(h)
     capi.check(capi.lib().ra_merge_attend(C.byref(p)))
     return (out, idx, sc) if return_indices else out
 
 
-def lse_combine(partials: Tensor, out: Optional[Tensor] = None) -> Tensor:
-    """partials fp32 [parts, B, Hq, 130] -> fp16 [B, Hq, 128]."""
+def lse_combine(partials: Tensor, out: Optional[Tensor] = None, exchange=None) -> Tensor:
+    """partials fp32 [parts, B, Hq, 130] -> fp16 [B, Hq, 128].  With ``exchange`` (the fields of
+    sharded.PeerExchange) the kernel first waits for every rank's partial flag and ends the step
+    by advancing the epoch."""
     parts, B, Hq, w = partials.shape
     if w != 130 or partials.dtype != torch.float32 or not partials.is_contiguous():
         raise ValueError("partials must be contiguous fp32 [parts, B, Hq, 130]")
     if out is None:
         out = torch.empty(B, Hq, 128, dtype=torch.float16, device=partials.device)
+    if exchange is not None:
+        ws = workspace(256, partials.device)
+        capi.check(capi.lib().ra_lse_combine_wait(
+            partials.data_ptr(), parts, B * Hq, out.data_ptr(), exchange.flags_p.data_ptr(),
+            exchange.flags_p.numel(), exchange.epoch.data_ptr(), int(exchange.timeout_s * 1e9),
+            exchange.done[2:3].data_ptr(), ws.data_ptr(), _stream_ptr()))
+        return out
     capi.check(capi.lib().ra_lse_combine(partials.data_ptr(), parts, B * Hq, out.data_ptr(),
                                          _stream_ptr()))
     return out

@@ -46,13 +46,15 @@ class CudaBackend:
         return ops.gemv_topk(q, k, topk, index_base=index_base, out=out)
 
     def merge_partial(self, cand_sc: Tensor, cand_idx: Tensor, v: Tensor, topk: int,
-                      sm_scale: float, own_base: int, out: Optional[Tensor] = None) -> Tensor:
+                      sm_scale: float, own_base: int, out: Optional[Tensor] = None,
+                      exchange=None) -> Tensor:
         from . import ops
-        return ops.merge_attend(cand_sc, cand_idx, v, topk, sm_scale, own_base, partial=True, out=out)
+        return ops.merge_attend(cand_sc, cand_idx, v, topk, sm_scale, own_base, partial=True, out=out,
+                                exchange=exchange)
 
-    def combine(self, partials: Tensor) -> Tensor:
+    def combine(self, partials: Tensor, exchange=None) -> Tensor:
         from . import ops
-        return ops.lse_combine(partials)
+        return ops.lse_combine(partials, exchange=exchange)
 
 
 class PeerExchange:
@@ -98,7 +100,7 @@ class PeerExchange:
         self.flags_c = buf[off_f:off_f + world]
         self.flags_p = buf[off_f + 32:off_f + 32 + world]
         self.epoch = torch.ones(1, dtype=torch.int32, device=buf.device)
-        self.done = torch.zeros(1, dtype=torch.int32, device=buf.device)
+        self.done = torch.zeros(4, dtype=torch.int32, device=buf.device)   # one word per kernel kind
         self.dst_c = [b + 4 * (off_c + rank * slot_c) for b in base_ptrs]
         self.dst_p = [b + 4 * (off_p + rank * slot_p) for b in base_ptrs]
         self.flg_c = [b + 4 * (off_f + rank) for b in base_ptrs]
@@ -106,7 +108,7 @@ class PeerExchange:
 
     def push_candidates(self) -> None:
         from . import ops
-        ops.exchange_push(self.cand[self.rank], self.dst_c, self.flg_c, self.epoch, self.done)
+        ops.exchange_push(self.cand[self.rank], self.dst_c, self.flg_c, self.epoch, self.done[0:1])
 
     def wait_candidates(self) -> None:
         from . import ops
@@ -114,7 +116,7 @@ class PeerExchange:
 
     def push_partial(self) -> None:
         from . import ops
-        ops.exchange_push(self.partials[self.rank], self.dst_p, self.flg_p, self.epoch, self.done)
+        ops.exchange_push(self.partials[self.rank], self.dst_p, self.flg_p, self.epoch, self.done[1:2])
 
     def wait_partials(self) -> None:
         """Also ends the step: the epoch advances by one."""
@@ -206,6 +208,9 @@ class ShardedTopkAttention:
         idx, sc = self.local_candidates(q, k, index_base)
         self.exchange_candidates(idx, sc)
         self.merge_and_exchange(cand_sc, cand_idx, partials, v, index_base)
+        if self.exchange is not None:
+            # the combine waits for every rank's partial itself and ends the step
+            return self.backend.combine(partials, exchange=self.exchange)
         return self.backend.combine(partials)
 
     def merge_and_exchange(self, cand_sc: Tensor, cand_idx: Tensor, partials: Tensor, v: Tensor,
@@ -213,10 +218,9 @@ class ShardedTopkAttention:
         """Steps 3 and 4: this rank's partial over the global winners it owns, then every rank's
         partial into ``partials``."""
         if self.exchange is not None:
+            # the merge waits for the candidate flags, writes this rank's partial and pushes it
             self.backend.merge_partial(cand_sc, cand_idx, v, self.topk, self.sm_scale, index_base,
-                                       out=partials[self.rank])
-            self.exchange.push_partial()
-            self.exchange.wait_partials()
+                                       out=partials[self.rank], exchange=self.exchange)
             return
         part = self.backend.merge_partial(cand_sc, cand_idx, v, self.topk, self.sm_scale, index_base)
         if self.world > 1:
@@ -268,8 +272,7 @@ def _exchange(self, idx: Tensor, sc: Tensor) -> None:
         self._send[1].copy_(idx)
         self._send[0].view(torch.float32).copy_(sc)
     if self.exchange is not None:
-        self.exchange.push_candidates()
-        self.exchange.wait_candidates()
+        self.exchange.push_candidates()      # the merge kernel waits for the flags
     elif self.world > 1:
         _all_gather(self._recv, self._send, self.group)
     else:
