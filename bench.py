@@ -122,6 +122,8 @@ def make_workload(name: str, device):
         return W.fused_topk_128k(device=device, n=32768)
     if name == "cfg2_shared":
         return W.fused_topk_128k(device=device, shared_cache=True)
+    if name == "cfg2_shared_n32k":   # the shared-cache geometry at a quarter of the context (profiling)
+        return W.fused_topk_128k(device=device, shared_cache=True, n=32768)
     if name == "cfg0":
         return W.reference_cpu_case(device=device)
     if name == "cfg1":
@@ -146,7 +148,7 @@ def make_workload(name: str, device):
 def cpu_sample(workload: str):
     """A bounded sample of the workload for the CPU oracle: one batch row."""
     from topk_attn_b200 import workloads as W
-    if workload in ("cfg2", "cfg2_shared", "cfg2_n32k"):
+    if workload in ("cfg2", "cfg2_shared", "cfg2_n32k", "cfg2_shared_n32k"):
         return W.fused_topk_128k(device="cpu", batch=1), "one batch row of cfg2 (N=131072, 32 heads, k=2048)"
     if workload == "cfg0":
         return W.reference_cpu_case(), "cfg0 in full"
@@ -321,10 +323,12 @@ def run_ours(args):
     q, k, v = w.q, w.k, w.v
     out = torch.empty_like(q)
     kind = "dense" if w.num_splits else ("centroid" if w.centers is not None else "topk")
-    kernel_name = {"dense": "flash_decode_kernel", "centroid": "center_select_kernel + gather_flash_kernel",
+    kernel_name = {"dense": "flash_decode_kernel", "centroid": "center_attend_kernel",
                    "topk": "scan_select_kernel"}[kind]
     if args.workload == "legacy":
         kernel_name = "dense_select_kernel + gather_flash_kernel"
+    if args.workload in ("cfg2_shared", "cfg2_shared_n32k", "cfg4"):
+        kernel_name = "scan_store_kernel + select_stored_kernel"
 
     def op(q_in):
         if kind == "dense":

@@ -228,6 +228,7 @@ __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char*
   const int nthr = blockDim.x, nwarps = nthr >> 5;
   const int crank = (int)cluster.block_rank();
 
+  RA_STAMP(A.status, 3);
   for (int i = tid; i < 2 * kMaxLists * 256; i += nthr) (&ms->hist[0][0][0])[i] = 0;
   // winner slots start out empty; a slot nobody fills is skipped by the mixing loop
   for (int i = tid; i < NL * per; i += nthr) sel_idx[i] = -1;
