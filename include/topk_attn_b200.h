@@ -6,7 +6,8 @@
  * torch types, no exceptions, no exit().  Each returns an int status (RA_OK == 0,
  * ra_strerror() gives the text).  Work is enqueued on the caller's stream and the call
  * returns without synchronising; no entry point allocates device memory — scratch comes
- * from a caller-provided workspace sized by ra_workspace_bytes().
+ * from a caller-provided workspace sized by ra_workspace_bytes(), zeroed once before its first
+ * use (its first 256 bytes are a status block whose bits are sticky).
  *
  * Tensor layouts are the reference project's:
  *   q      fp16 [B, Hq, D]                       retrieval_attn/retrieval_attention.cu:257
@@ -121,8 +122,11 @@ int ra_check_status(void* workspace, void* stream);
  * launch_retrieval_attention{,_global,_pipelined,_pipelined_global,_two_kernels,
  * _gather_baseline}_{32,128,256,512,1024}(q, k, v, out, batch)): N = num_tokens keys in a shared
  * [N,32,128] cache cut in 4 chunks, top-K per chunk, raw-exp softmax, no scale.
- * variant: 0 fused, 1 global-scratch, 2 pipelined, 3 pipelined-global, 4 two kernels,
- * 5 gather + dense baseline; all variants return the same result. */
+ * variant (0 fused, 1 global-scratch, 2 pipelined, 3 pipelined-global, 4 two kernels, 5 gather +
+ * dense baseline) is accepted so that each of the reference's 30 names has a target, and is
+ * validated, but selects nothing: the reference's variants schedule the same arithmetic in
+ * different ways, and this library runs its one fastest route for all of them.  There is no A/B
+ * between variants here; ra_gemv_topk + ra_gathered_attention is the two-call form. */
 int ra_legacy_retrieval_attention(const void* q, const void* k, const void* v, void* out,
                                   int32_t batch, int32_t num_tokens, int32_t topk_per_chunk,
                                   int32_t variant, void* workspace, size_t workspace_bytes,
