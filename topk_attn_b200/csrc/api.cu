@@ -124,6 +124,7 @@ struct Plan {
   int cluster = 1, nsplit = 1, cap = 0, nstages = 0, per = 0, part_len = 0, grid = 0;
   int groups = 2, rendezvous = 4;
   int det_words = 32;  // bitmap words of the ordered deal in the scan kernel's scratch
+  bool parts_in_cluster = false;  // every segment of a (row, head) is one CTA of one cluster
   size_t smem = 0;
   // second stage (only when parts > 1)
   int cluster2 = 1, cap2 = 0, per2 = 0;
@@ -281,9 +282,15 @@ Plan make_plan(const Shape& s) {
     // several queries per K row are scored on the tensor cores, one kv head per CTA
     if (nq > 1 && hg != 1 && !tuning_env("RA_NO_MMA")) continue;
     const int nl = hg * nq, T = kTileRows / hg;
-    const int groups = (s.batch / bshare) * (s.hkv / hg) * s.segments * qsplit;
-    for (int cluster : {1, 2, 4, 8, 16}) {
-      if (f_cluster && cluster != f_cluster) continue;
+    // bit 8 of fused_ok: the caller attends over all segments of a (row, head) and they are few
+    // enough to be the CTAs of one cluster -- each CTA scans and selects its own segment, the
+    // attention is merged across the cluster, nothing goes through global memory
+    const bool pic = (s.fused_ok & 8) != 0;
+    const int groups = (s.batch / bshare) * (s.hkv / hg) * (pic ? 1 : s.segments) * qsplit;
+    for (int cluster : {1, 2, 4, 8, 16, 0}) {
+      if (pic != (cluster == 0)) continue;
+      if (cluster == 0) cluster = s.segments;
+      if (f_cluster && cluster != f_cluster && !pic) continue;
       for (int nsplit = 1; nsplit <= kMaxSplit; ++nsplit) {
         if (nsplit > 1 && (s.segments > 1 || (s.fused_ok & 4))) break;
         if (f_nsplit && nsplit != f_nsplit) continue;
@@ -292,12 +299,13 @@ Plan make_plan(const Shape& s) {
         if (nsplit > 1 && part_len * (nsplit - 1) >= seg_len) continue;  // empty last part
         if (nsplit == 1) part_len = seg_len;
         const int tiles = ceil_div(part_len, T);
-        if (cluster > 1 && tiles < cluster) continue;
-        const int per = ceil_div(s.topk, cluster);
+        if (!pic && cluster > 1 && tiles < cluster) continue;
+        const int per = pic ? s.topk : ceil_div(s.topk, cluster);
         // scratch of the cluster select in the freed pipeline stages; the bitmap of the ordered
         // deal covers a CTA's token slab in one window when the stages have room for it
         const size_t scratch = merge_scratch_bytes(nl, per, 32);
-        const int slab_tokens = ceil_div(tiles, cluster) * T;
+        const int cta_tiles = pic ? tiles : ceil_div(tiles, cluster);
+        const int slab_tokens = cta_tiles * T;
         // stages, consumer groups, check interval and list capacity within the shared-memory
         // budget: the deepest pipeline whose lists still hold k keys plus the keys that may arrive
         // between two overflow checks
@@ -342,22 +350,22 @@ Plan make_plan(const Shape& s) {
         if (active <= 0) continue;
         const int waves = ceil_div(nclusters, active);
         const int live = std::min(nclusters, active) * cluster;
-        const double bytes_cta = (double)ceil_div(tiles, cluster) * kStageBytes;
+        const double bytes_cta = (double)cta_tiles * kStageBytes;
         // clusters that share a K row stream it once from HBM and qsplit - 1 times from L2
         const double rate = std::min(per_sm, hbm * qsplit / live);
         // every cut of a candidate list stalls the CTA's consumers for a few microseconds; the
         // seen-token count grows by (1 + room/k) between two cuts of one list
         const int margin = rdv * cgroups * T;
         const double room = std::max(64, cap - s.topk - margin);
-        const double slab = (double)ceil_div(tiles, cluster) * T;
+        const double slab = (double)cta_tiles * T;
         const double cuts = slab > cap ? std::log(slab / cap) / std::log1p(room / s.topk) + 1.0 : 0.0;
-        const bool two_stage = nsplit > 1 || s.segments > 1;
+        const bool two_stage = !pic && (nsplit > 1 || s.segments > 1);
         // clusters of up to 4 CTAs cost little; 8 and more are hard to co-schedule with 227 KiB of
         // shared memory per CTA and measured about twice as slow
         const double cluster_cost = cluster <= 4 ? 0.4e-6 * cluster : 4e-6 * cluster;
         // until a list has filled once every key passes the threshold and is appended: about a
         // microsecond per iteration instead of a fraction of one
-        const double warmup = 1e-6 * std::min(ceil_div(tiles, cluster), cap / T) / cgroups;
+        const double warmup = 1e-6 * std::min(cta_tiles, cap / T) / cgroups;
         double cost = waves * (geos[gx].slow * bytes_cta / rate + cuts * nl * 2e-6 + warmup + 6e-6 +
                                cluster_cost) +
                       (two_stage ? 8e-6 : 0.0);
@@ -366,6 +374,7 @@ Plan make_plan(const Shape& s) {
         pl.qsplit = qsplit; pl.nq_cta = nq_cta;
         pl.cluster = cluster; pl.nsplit = nsplit; pl.cap = cap; pl.nstages = nstages;
         pl.groups = cgroups; pl.rendezvous = rdv; pl.det_words = geos[gx].det;
+        pl.parts_in_cluster = pic;
         pl.per = per; pl.part_len = part_len; pl.grid = nclusters * cluster; pl.smem = smem;
         pl.cost = cost;
         if (two_stage && !plan_merge(s.segments * nsplit * s.topk,
@@ -495,6 +504,10 @@ struct PartIds {
   int* expand_ids = nullptr;
   // status block of the caller's workspace when p->workspace is only an inner slice of it
   unsigned* status = nullptr;
+  // two-level retrieval with a small centroid table: the scan kernel ranks the centroids itself
+  const void* coarse_centers = nullptr;
+  int coarse_csz = 0;
+  int* coarse_ids_out = nullptr;
 };
 
 int run_store(const ra_params* p, const Shape& s, int group, bool attend, unsigned* status);
@@ -507,8 +520,12 @@ int run(const ra_params* p, bool attend, const PartIds* ext = nullptr) {
   Shape s = c.shape;
   // bit 1: every (row, head) scans its own parts — nothing is shared; bit 2: one part only (the
   // scan kernel itself must produce the final winners)
-  s.fused_ok = 1 | ((ext && ext->ids) ? 2 : 0) | ((ext && ext->expand_out) ? 4 : 0);
-  const int real_tokens = (ext && ext->ids) ? ext->real_tokens : s.n;
+  s.fused_ok = 1 | ((ext && (ext->ids || ext->coarse_centers)) ? 2 : 0) | ((ext && ext->expand_out) ? 4 : 0);
+  // attention over a few per-segment selections of own parts (two-level retrieval): the segments of
+  // a (row, head) become the CTAs of one cluster and the whole pipeline is one launch
+  if (attend && (s.fused_ok & 2) && s.segments >= 2 && s.segments <= 8 && !tuning_env("RA_NO_SEGMENT_CLUSTER"))
+    s.fused_ok |= 8;
+  const int real_tokens = (ext && (ext->ids || ext->coarse_centers)) ? ext->real_tokens : s.n;
   const bool verbose = verbose_plan();
   cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
   unsigned* status = (ext && ext->status) ? ext->status : static_cast<unsigned*>(p->workspace);
@@ -580,7 +597,7 @@ int run(const ra_params* p, bool attend, const PartIds* ext = nullptr) {
             pl.rendezvous, pl.per,
             pl.part_len, pl.grid, pl.smem, pl.cluster2, pl.cap2, pl.smem2, pl.cost * 1e6);
   const int parts = s.segments * pl.nsplit;
-  const bool two_stage = parts > 1;
+  const bool two_stage = parts > 1 && !pl.parts_in_cluster;
   // the candidate lists of this plan must fit in what the caller gave
   if (p->workspace_bytes < kStatusBytes + (two_stage ? cand_bytes(s, parts) : 0)) {
     g_last_error = "workspace smaller than ra_workspace_bytes()";
@@ -600,6 +617,11 @@ int run(const ra_params* p, bool attend, const PartIds* ext = nullptr) {
   sp.status = status;
   sp.batch = s.batch; sp.hq = s.hq; sp.hkv = s.hkv; sp.n_tokens = real_tokens;
   sp.part_ids = ext ? ext->ids : nullptr;
+  if (ext && ext->coarse_centers) {
+    sp.coarse_centers = static_cast<const __half*>(ext->coarse_centers);
+    sp.coarse_csz = ext->coarse_csz;
+    sp.coarse_ids_out = ext->coarse_ids_out;
+  }
   if (ext && ext->expand_out) {
     sp.m.expand_clen = ext->expand_clen; sp.m.expand_out = ext->expand_out;
     sp.m.expand_ids = ext->expand_ids;
@@ -614,6 +636,8 @@ int run(const ra_params* p, bool attend, const PartIds* ext = nullptr) {
   if (const char* d = tuning_env("RA_WAIT_LIMIT_MS")) sp.wait_limit_ns = 1000000ull * (unsigned long long)std::max(1, atoi(d));
   MergeArgs& m = sp.m;
   m.topk = s.topk; m.per = pl.per; m.cluster = pl.cluster; m.det_words = pl.det_words;
+  m.per_cta_select = pl.parts_in_cluster ? 1 : 0;
+  sp.parts_in_cluster = pl.parts_in_cluster ? 1 : 0;
   m.hq_total = s.hq; m.list_pitch = parts * s.topk; m.list_off = 0;
   m.index_base = two_stage ? 0 : p->index_base;
   m.own_lo = 0; m.own_hi = 0x7fffffff; m.id_shift = 0;
@@ -1139,7 +1163,10 @@ int ra_two_level_topk(const ra_two_level_params* p) {
   sp.out_indices = c_ids; sp.out_scores = c_score;
   sp.workspace = ws; sp.workspace_bytes = coarse; sp.stream = p->stream;
   int* sorted = p->out_cluster_ids ? p->out_cluster_ids : c_sorted;
-  if (p->num_centers <= kCenterMaxCsz && !tuning_env("RA_NO_CENTER_SELECT")) {
+  // a small table is ranked by the scan kernel's own prologue: no launch for the coarse stage
+  const bool coarse_in_scan = p->num_centers <= kMaxCoarse && !tuning_env("RA_NO_COARSE_PROLOGUE");
+  if (coarse_in_scan) {
+  } else if (p->num_centers <= kCenterMaxCsz && !tuning_env("RA_NO_CENTER_SELECT")) {
     // steps 1 and 2 in one launch
     int st = center_select(p->q, p->centers, p->batch, p->num_heads, p->num_centers, p->top_clusters,
                            p->cluster_len, sorted, nullptr, nullptr, stream);
@@ -1165,8 +1192,14 @@ int ra_two_level_topk(const ra_two_level_params* p) {
   fp.out_indices = p->out_indices; fp.out_scores = p->out_scores;
   fp.workspace = ws + coarse; fp.workspace_bytes = fine; fp.stream = p->stream;
   PartIds ext;
-  ext.ids = sorted; ext.real_tokens = p->num_tokens;
+  ext.ids = coarse_in_scan ? nullptr : sorted;
+  ext.real_tokens = p->num_tokens;
   ext.status = static_cast<unsigned*>(p->workspace);   // one status block for every stage
+  if (coarse_in_scan) {
+    ext.coarse_centers = p->centers;
+    ext.coarse_csz = p->num_centers;
+    ext.coarse_ids_out = p->out_cluster_ids;
+  }
   return run(&fp, attend, &ext);
 }
 

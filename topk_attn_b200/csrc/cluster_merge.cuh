@@ -67,6 +67,8 @@ struct MergeArgs {
   int own_lo, own_hi;  // only winners with own_lo <= id < own_hi are mixed (id before index_base)
   int id_shift;        // subtracted from an id to address V (ids of another shard's frame)
   int det_words;       // bitmap words of the ordered deal's window (0 with select_all + local_deal)
+  int per_cta_select;  // 1: every CTA keeps the topk best of its own list (per == topk); the cluster
+                       // only shares the maximum and merges the attention over all CTAs' winners
   int select_all;      // 1: every candidate is a winner (topk == number of candidates)
   int local_deal;      // with select_all: CTA c already holds winners c*per .. c*per+cnt-1, keep them
   int expand_clen;     // > 0 with expand_out: winners are cluster ids, written out expanded
@@ -266,13 +268,17 @@ __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char*
         if (key >= sel_base && (rel & mask) == pre) atomicAdd(&ms->hist[buf][l][(rel >> ns) & dmask], 1);
       });
     }
-    cluster_barrier(cluster, C);
+    if (A.per_cta_select) __syncthreads(); else cluster_barrier(cluster, C);
     for (int item = tid; item < NL * 256; item += nthr) {
       const int l = item >> 8, bin = item & 255;
       int sum = 0;
-      for (int c = 0; c < C; ++c) {
-        const int* rh = cluster.map_shared_rank(&ms->hist[buf][l][0], c);
-        sum += rh[bin];
+      if (A.per_cta_select) {
+        sum = ms->hist[buf][l][bin];
+      } else {
+        for (int c = 0; c < C; ++c) {
+          const int* rh = cluster.map_shared_rank(&ms->hist[buf][l][0], c);
+          sum += rh[bin];
+        }
       }
       ms->ghist[l][bin] = sum;
       ms->hist[buf ^ 1][l][bin] = 0;  // peers finished reading it before the barrier above
@@ -332,6 +338,14 @@ __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char*
       const uint32_t* rc = cluster.map_shared_rank(&ms->counts[l][0], c);
       const int g = (int)rc[0], e = (int)rc[1];
       mx = max(mx, rc[2]);
+      if (A.per_cta_select) {
+        // own selection: only the maximum is common
+        if (c == crank) {
+          my_take = max(0, min(e, need_eq));
+          total = g + my_take;
+        }
+        continue;
+      }
       const int take = max(0, min(e, need_eq - eq_before));
       if (c < crank) off_win += g + take;
       if (c == crank) my_take = take;
@@ -418,7 +432,8 @@ __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char*
         if ((key > kth || (key == kth && tg <= cut)) && t < (unsigned)det_window) {
           const int p = off_win + base + det_pre[t >> 5] + __popc(det_bits[t >> 5] & ((1u << (t & 31)) - 1u));
           if (p < k) {
-            const int dst = p / per, slot = p - dst * per;
+            const int dst = A.per_cta_select ? crank : p / per;
+            const int slot = A.per_cta_select ? p : p - dst * per;
             uint32_t* rk = cluster.map_shared_rank(sel_key, dst);
             int* ri = cluster.map_shared_rank(sel_idx, dst);
             rk[(size_t)l * per + slot] = key;
@@ -471,18 +486,18 @@ __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char*
   for (int l = 0; l < NL; ++l) {
     const ListDest ld = dest(l);
     if (!ld.valid) continue;  // uniform over the CTA
-    const int n_l = max(0, min(per, ms->total_sel[l] - crank * per));
+    const int n_l = A.per_cta_select ? ms->total_sel[l] : max(0, min(per, ms->total_sel[l] - crank * per));
     const uint32_t* sk = sel_key + (size_t)l * per;
     const int* si = sel_idx + (size_t)l * per;
     if (A.sel_idx) {
       const size_t dst = ((size_t)ld.bq * A.hq_total + ld.hq) * A.list_pitch + A.list_off +
-                         (size_t)crank * per;
+                         (A.per_cta_select ? (size_t)0 : (size_t)crank * per);
       for (int e = tid; e < n_l; e += nthr) {
         A.sel_idx[dst + e] = si[e] + A.index_base;
         if (A.sel_score) A.sel_score[dst + e] = key_score(sk[e]);
       }
       // a part with fewer than k keys pads its slots with entries that can never win
-      const int slots = max(0, min(per, k - crank * per));
+      const int slots = A.per_cta_select ? k : max(0, min(per, k - crank * per));
       for (int e = n_l + tid; e < slots; e += nthr) {
         A.sel_idx[dst + e] = -1;
         if (A.sel_score) A.sel_score[dst + e] = -INFINITY;
@@ -553,9 +568,10 @@ __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char*
   RA_STAMP(A.status, 7);
   if (A.out_mode != kOutNone) {
     cluster_barrier(cluster, C);
-    const int dper = kHeadDim / C;  // the cluster size divides 128
-    for (int item = tid; item < NL * dper; item += nthr) {
-      const int l = item / dper, d = crank * dper + item % dper;
+    // CTA c finishes the dimensions d with d % C == c (any cluster size)
+    for (int item = tid; item < NL * kHeadDim; item += nthr) {
+      const int l = item / kHeadDim, d = item % kHeadDim;
+      if (d % C != crank) continue;
       const ListDest ld = dest(l);
       if (!ld.valid) continue;
       float o = 0.f, lt = 0.f;

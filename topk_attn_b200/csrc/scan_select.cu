@@ -38,6 +38,8 @@ struct Ctrl {
   uint32_t tie_pre;   // radix descent over the inverted ids of the copies of a cut's k-th key
   int tie_rem;
   int timeout;
+  int coarse_id;              // two-level retrieval: the cluster this part scans
+  float coarse[kMaxCoarse];   // its head's centroid scores
 };
 enum CutState : int { kCutIdle = 0, kCutRun = 1, kCutInclusive = 2, kCutExact = 3 };
 
@@ -263,9 +265,11 @@ scan_select_kernel(const __grid_constant__ ScanParams P) {
   Ctrl* ctrl = reinterpret_cast<Ctrl*>(idxs + (size_t)NL * cap);
 
   // which part of which (batch group, kv-head group) this cluster owns
+  // (or, with parts_in_cluster, which part this CTA owns: the cluster holds all parts of a row)
+  const bool pic = P.parts_in_cluster != 0;
   int cid = blockIdx.x / C;
-  const int part = cid % P.nparts;
-  cid /= P.nparts;
+  const int part = pic ? crank : cid % P.nparts;
+  if (!pic) cid /= P.nparts;
   // the queries that share a K row may be dealt over several clusters (each re-reads the rows,
   // mostly from L2, and keeps fewer candidate lists): this cluster scores queries q0 .. q0+nq_cta-1
   const int q0 = (cid % P.qsplit) * P.nq_cta;
@@ -277,13 +281,58 @@ scan_select_kernel(const __grid_constant__ ScanParams P) {
 
   // a part is normally the part-th slice of the token axis; with part_ids it is the cluster whose
   // id the (batch row, head) chose at that rank (two-level retrieval, one head and query per CTA)
-  const int part_lo =
-      (P.part_ids ? P.part_ids[((size_t)b0 * P.hq + (size_t)h0 * P.group) * P.nparts + part] : part) *
-      P.part_len;
+  int part_slice = part;
+  if (P.part_ids) part_slice = P.part_ids[((size_t)b0 * P.hq + (size_t)h0 * P.group) * P.nparts + part];
+  if (P.coarse_centers) {
+    // Coarse stage in the prologue (gemv_topk.cu:218-262: score the head's centroids, keep the best
+    // few): half-warp per centroid row, the arithmetic of center_select_kernel, then every
+    // centroid counts the ones ahead of it in (score descending, id ascending) order; the one with
+    // `part` ahead of it is this part's cluster.
+    const int row = b0 * P.hq + h0 * P.group;
+    const int hw = tid >> 4, l16 = tid & 15;
+    float qf[8];
+    {
+      const uint4 qraw = *reinterpret_cast<const uint4*>(P.q + (size_t)row * kHeadDim + l16 * 8);
+      const float2 a = h2f2(qraw.x), b = h2f2(qraw.y), c = h2f2(qraw.z), d = h2f2(qraw.w);
+      qf[0] = a.x; qf[1] = a.y; qf[2] = b.x; qf[3] = b.y;
+      qf[4] = c.x; qf[5] = c.y; qf[6] = d.x; qf[7] = d.y;
+    }
+    const __half* table = P.coarse_centers + (size_t)(h0 * P.group) * P.coarse_csz * kHeadDim + l16 * 8;
+    const int nhw = (int)blockDim.x >> 4;
+    for (int r0 = 0; r0 < P.coarse_csz; r0 += nhw) {   // same trip count for all threads
+      const int r = r0 + hw;
+      const uint4 kv = r < P.coarse_csz ? ldg128_nc(table + (size_t)r * kHeadDim) : make_uint4(0, 0, 0, 0);
+      const float2 a = h2f2(kv.x), b = h2f2(kv.y), c = h2f2(kv.z), d = h2f2(kv.w);
+      float sc = a.x * qf[0];
+      sc = fmaf(a.y, qf[1], sc); sc = fmaf(b.x, qf[2], sc); sc = fmaf(b.y, qf[3], sc);
+      sc = fmaf(c.x, qf[4], sc); sc = fmaf(c.y, qf[5], sc); sc = fmaf(d.x, qf[6], sc);
+      sc = fmaf(d.y, qf[7], sc);
+      sc += __shfl_xor_sync(0xffffffffu, sc, 8);
+      sc += __shfl_xor_sync(0xffffffffu, sc, 4);
+      sc += __shfl_xor_sync(0xffffffffu, sc, 2);
+      sc += __shfl_xor_sync(0xffffffffu, sc, 1);
+      if (l16 == 0 && r < P.coarse_csz) ctrl->coarse[r] = sc;
+    }
+    __syncthreads();
+    for (int r = tid; r < P.coarse_csz; r += blockDim.x) {
+      const uint32_t me = score_key(ctrl->coarse[r]);
+      int ahead = 0;
+      for (int j = 0; j < P.coarse_csz; ++j) {
+        const uint32_t o = score_key(ctrl->coarse[j]);
+        ahead += (o > me) || (o == me && j < r);
+      }
+      if (ahead == part) ctrl->coarse_id = r;
+    }
+    __syncthreads();
+    part_slice = ctrl->coarse_id;
+    if ((pic || crank == 0) && tid == 0 && P.coarse_ids_out)   // one writer per part
+      P.coarse_ids_out[(size_t)row * P.nparts + part] = part_slice;
+  }
+  const int part_lo = part_slice * P.part_len;
   const int part_hi = min(P.n_tokens, part_lo + P.part_len);
   const int ntiles_part = ceil_div(max(part_hi - part_lo, 0), T);
-  const int tpc = ceil_div(ntiles_part, C);
-  const int tile_b = crank * tpc;
+  const int tpc = pic ? ntiles_part : ceil_div(ntiles_part, C);
+  const int tile_b = pic ? 0 : crank * tpc;
   const int my_ntiles = max(0, min(ntiles_part, tile_b + tpc) - tile_b);
   const int tok_begin = part_lo + tile_b * T;
   const int S = P.nstages;
