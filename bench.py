@@ -384,6 +384,9 @@ def run_ours(args):
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
+            if args.consecutive:
+                # consecutive decode steps of one sequence: the cache is asked to persist in L2
+                ops.l2_persist(w.centers if kind == "centroid" else k)
             step()
             c0 = count()
             with torch.cuda.graph(graph, stream=side):
@@ -393,16 +396,23 @@ def run_ours(args):
         torch.cuda.synchronize()
         pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
                  for _ in range(args.steps)]
-        for a, bq in pairs:
-            flush.fill_(1)
-            a.record()
-            graph.replay()
-            bq.record()
-        torch.cuda.synchronize()
+        with nvtx_range("timed steps"):
+            for a, bq in pairs:
+                if not args.consecutive:
+                    flush.fill_(1)
+                a.record()
+                graph.replay()
+                bq.record()
+            torch.cuda.synchronize()
         clocks = sampler.stop()
         launch_ms = sorted(a.elapsed_time(bq) for a, bq in pairs)
         per_ms = sum(launch_ms) / len(launch_ms)
-        l2_note = "l2_flushed_between_steps (512 MB overwrite), step replayed from a CUDA graph"
+        l2_note = ("consecutive steps, no flush, cache persisting in L2 (ra_l2_persist), "
+                   "step replayed from a CUDA graph") if args.consecutive else \
+            "l2_flushed_between_steps (512 MB overwrite), step replayed from a CUDA graph"
+        if args.consecutive:
+            with torch.cuda.stream(side):
+                ops.l2_persist(None)
     ops.check_status(dev)
 
     # end to end: query from pinned host memory, output read back, every step
@@ -500,6 +510,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling)")
+    ap.add_argument("--consecutive", action="store_true",
+                    help="small workloads: time consecutive decode steps of one sequence (no L2 flush, "
+                         "the cache marked persisting in L2) instead of cold steps")
     ap.add_argument("--collectives", action="store_true",
                     help="multi-GPU: exchange through NCCL all-gathers instead of peer stores")
     ap.add_argument("--no-cfg4", action="store_true",

@@ -315,6 +315,17 @@ int ra_lse_combine_wait(const float* partials, int32_t num_parts, int32_t rows, 
                         const void* wait_flags, int32_t num_flags, void* epoch, uint64_t timeout_ns,
                         void* done_counter, void* status_workspace, void* stream);
 
+/* Keep a cache resident in L2 across consecutive decode steps (no counterpart in the reference,
+ * whose pipelined kernels keep K hot only inside one launch, retrieval_attn/
+ * retrieval_attention.cu:654-896).  Marks [base, base + bytes) as persisting for every kernel later
+ * launched into `stream` (an access-policy window, a stream attribute) and reserves as much of L2
+ * for persisting lines as the device allows for that size; hit_ratio in (0, 1] is the fraction of
+ * the window that should persist when it is larger than the reservation.  bytes == 0 removes the
+ * window and releases the persisting lines.  Both settings belong to the calling process's CUDA
+ * context and end with it.  Worth it for caches of up to roughly the L2 size shared by all batch
+ * rows (kv_batch_stride == 0): each step then re-reads K from L2 instead of HBM. */
+int ra_l2_persist(const void* base, size_t bytes, float hit_ratio, void* stream);
+
 /* ---- exchange step of the sharded decode over peer-mapped memory (no counterpart in the
  * reference; the in-GPU mechanism it generalises is the cluster-wide exchange through
  * distributed shared memory of baseline_1.cu:549-598) ----

@@ -50,3 +50,20 @@ def test_append_per_sequence_caches_and_bounds():
     assert not k[:, :5].any() and not k[:, 6:].any()
     with pytest.raises(capi.RaError):
         ops.kv_append(k, v, nk, nv, cap)
+
+
+def test_l2_persistence_window_can_be_set_and_removed():
+    """ra_l2_persist marks a shared cache as persisting in L2 for the current stream (consecutive
+    decode steps of one sequence); results do not change, and the window can be removed again."""
+    from topk_attn_b200 import ops
+    from gpu_util import rand_case
+    q, k, v = rand_case(1, 8, 8, 4096, False, seed=4)
+    dev = torch.device("cuda:0")
+    qd, kd, vd = q.to(dev), k.to(dev), v.to(dev)
+    ref = ops.topk_attention(qd, kd, vd, 128)
+    ops.l2_persist(kd)
+    for _ in range(3):
+        out = ops.topk_attention(qd, kd, vd, 128)
+    ops.l2_persist(None)
+    ops.check_status(dev)
+    assert torch.equal(out, ref)

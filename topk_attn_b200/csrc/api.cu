@@ -1439,6 +1439,43 @@ int ra_lse_combine(const float* partials, int32_t num_parts, int32_t rows, void*
   return RA_OK;
 }
 
+int ra_l2_persist(const void* base, size_t bytes, float hit_ratio, void* stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaStreamAttrValue attr;
+  memset(&attr, 0, sizeof attr);
+  if (bytes == 0) {
+    attr.accessPolicyWindow.num_bytes = 0;
+    cudaError_t e = cudaStreamSetAttribute(st, cudaStreamAttributeAccessPolicyWindow, &attr);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaStreamSetAttribute(access policy window)");
+    e = cudaCtxResetPersistingL2Cache();
+    if (e != cudaSuccess) return cuda_fail(e, "cudaCtxResetPersistingL2Cache");
+    return RA_OK;
+  }
+  if (!base || !(hit_ratio > 0.f) || hit_ratio > 1.f) return invalid("base must be given and hit_ratio in (0, 1]");
+  int dev = 0, max_persist = 0, max_window = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&max_persist, cudaDevAttrMaxPersistingL2CacheSize, dev);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&max_window, cudaDevAttrMaxAccessPolicyWindowSize, dev);
+  if (e != cudaSuccess) return cuda_fail(e, "querying the L2 persistence limits");
+  if (max_persist <= 0 || max_window <= 0) return unsupported("this device has no persisting L2 lines");
+  size_t have = 0;
+  e = cudaDeviceGetLimit(&have, cudaLimitPersistingL2CacheSize);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetLimit(persisting L2)");
+  const size_t want = std::min<size_t>(bytes, (size_t)max_persist);
+  if (have < want) {
+    e = cudaDeviceSetLimit(cudaLimitPersistingL2CacheSize, want);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceSetLimit(persisting L2)");
+  }
+  attr.accessPolicyWindow.base_ptr = const_cast<void*>(base);
+  attr.accessPolicyWindow.num_bytes = std::min<size_t>(bytes, (size_t)max_window);
+  attr.accessPolicyWindow.hitRatio = hit_ratio;
+  attr.accessPolicyWindow.hitProp = cudaAccessPropertyPersisting;
+  attr.accessPolicyWindow.missProp = cudaAccessPropertyStreaming;
+  e = cudaStreamSetAttribute(st, cudaStreamAttributeAccessPolicyWindow, &attr);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaStreamSetAttribute(access policy window)");
+  return RA_OK;
+}
+
 int ra_exchange_push(const void* src, size_t bytes, void* const* peer_dst, void* const* peer_flags,
                      int32_t num_peers, const void* epoch, void* done_counter, void* stream) {
   if (!src || !peer_dst || !peer_flags || !epoch || !done_counter) return invalid("a required pointer is null");

@@ -351,6 +351,17 @@ def lse_combine(partials: Tensor, out: Optional[Tensor] = None, exchange=None) -
     return out
 
 
+def l2_persist(cache: Optional[Tensor], hit_ratio: float = 1.0) -> None:
+    """Mark ``cache`` (a key cache shared by the batch, up to roughly the L2 size) as persisting in
+    L2 for the kernels launched into the current stream from now on, so that consecutive decode
+    steps re-read it from L2; ``None`` removes the window."""
+    if cache is None:
+        capi.check(capi.lib().ra_l2_persist(None, 0, 1.0, _stream_ptr()))
+        return
+    capi.check(capi.lib().ra_l2_persist(cache.data_ptr(), cache.numel() * cache.element_size(),
+                                        hit_ratio, _stream_ptr()))
+
+
 def exchange_push(src: Tensor, peer_dst, peer_flags, epoch: Tensor, done: Tensor) -> None:
     """Store the contiguous tensor ``src`` (a multiple of 16 bytes) into the slots ``peer_dst``
     (device addresses as ints, one per rank; the own slot may be ``src`` itself) and then the epoch
