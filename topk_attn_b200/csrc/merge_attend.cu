@@ -169,6 +169,7 @@ struct MergeCtaCtrl {
   int hist[256];
   uint32_t kmin, kmax;
   int digit, remaining, wpos, eqc, cut;
+  int own_first, own_last;   // range of winner slots whose ids this rank owns
   int wsum[kMaxWarps + 2];
   float lred[32];
 };
@@ -202,29 +203,64 @@ merge_attend_cta_kernel(const __grid_constant__ MergeParams P) {
     ctrl->kmax = 0u;
     ctrl->wpos = 0;
     ctrl->eqc = 0;
+    ctrl->own_first = 0x7fffffff;
+    ctrl->own_last = -1;
   }
+  RA_STAMP(P.m.status, 0);
   exchange_wait_in_kernel(P.x, P.m.status);   // the peers' candidates have landed (bounded wait)
   __syncthreads();
+  RA_STAMP(P.m.status, 1);
   uint32_t mn = 0xffffffffu, mx = 0u;
-  constexpr int LU = 8;   // loads in flight per thread: the lists come from L2 or a peer's stores
-  for (int c0 = 0; c0 < n; c0 += kMergeCtaThreads * LU) {
-    float sc[LU];
-    int id[LU];
+  // several loads in flight per thread: the lists come from L2 or from a peer's stores.  Lists
+  // whose length and strides are multiples of four elements are read 16 bytes at a time.
+  const bool vec = (P.part_len % 4 == 0) && (P.part_stride % 4 == 0) && (P.row_stride % 4 == 0) &&
+                   ((reinterpret_cast<uintptr_t>(P.cand_score) | reinterpret_cast<uintptr_t>(P.cand_idx)) & 15u) == 0;
+  if (vec) {
+    constexpr int LU = 4;
+    for (int c0 = 0; c0 < n; c0 += kMergeCtaThreads * LU * 4) {
+      float4 sc[LU];
+      int4 id[LU];
 #pragma unroll
-    for (int u = 0; u < LU; ++u) {
-      const int c = c0 + u * kMergeCtaThreads + tid;
-      sc[u] = c < n ? P.cand_score[src_of(c)] : 0.f;
-      id[u] = (c < n && !ids_global) ? P.cand_idx[src_of(c)] : 0;
+      for (int u = 0; u < LU; ++u) {
+        const int c = c0 + (u * kMergeCtaThreads + tid) * 4;
+        sc[u] = c < n ? *reinterpret_cast<const float4*>(P.cand_score + src_of(c)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        id[u] = (c < n && !ids_global) ? *reinterpret_cast<const int4*>(P.cand_idx + src_of(c))
+                                       : make_int4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int u = 0; u < LU; ++u) {
+        const int c = c0 + (u * kMergeCtaThreads + tid) * 4;
+        if (c < n) {
+          const uint4 kq = make_uint4(score_key(sc[u].x), score_key(sc[u].y), score_key(sc[u].z),
+                                      score_key(sc[u].w));
+          *reinterpret_cast<uint4*>(keys + c) = kq;
+          if (!ids_global) *reinterpret_cast<int4*>(idxs + c) = id[u];
+          mn = min(min(mn, kq.x), min(min(kq.y, kq.z), kq.w));
+          mx = max(max(mx, kq.x), max(max(kq.y, kq.z), kq.w));
+        }
+      }
     }
+  } else {
+    constexpr int LU = 8;
+    for (int c0 = 0; c0 < n; c0 += kMergeCtaThreads * LU) {
+      float sc[LU];
+      int id[LU];
 #pragma unroll
-    for (int u = 0; u < LU; ++u) {
-      const int c = c0 + u * kMergeCtaThreads + tid;
-      if (c < n) {
-        const uint32_t key = score_key(sc[u]);
-        keys[c] = key;
-        if (!ids_global) idxs[c] = id[u];
-        mn = min(mn, key);
-        mx = max(mx, key);
+      for (int u = 0; u < LU; ++u) {
+        const int c = c0 + u * kMergeCtaThreads + tid;
+        sc[u] = c < n ? P.cand_score[src_of(c)] : 0.f;
+        id[u] = (c < n && !ids_global) ? P.cand_idx[src_of(c)] : 0;
+      }
+#pragma unroll
+      for (int u = 0; u < LU; ++u) {
+        const int c = c0 + u * kMergeCtaThreads + tid;
+        if (c < n) {
+          const uint32_t key = score_key(sc[u]);
+          keys[c] = key;
+          if (!ids_global) idxs[c] = id[u];
+          mn = min(mn, key);
+          mx = max(mx, key);
+        }
       }
     }
   }
@@ -238,6 +274,7 @@ merge_attend_cta_kernel(const __grid_constant__ MergeParams P) {
     atomicMax(&ctrl->kmax, mx);
   }
   __syncthreads();
+  RA_STAMP(P.m.status, 2);
   const uint32_t base = ctrl->kmin, maxkey = ctrl->kmax;
   int shift = max(0, 32 - __clz((int)((maxkey - base) | 1u)) - 8);
   uint32_t prefix = 0u, mask = 0u;
@@ -266,6 +303,7 @@ merge_attend_cta_kernel(const __grid_constant__ MergeParams P) {
     if (shift == 0) break;
     shift = max(0, shift - 8);
   }
+  RA_STAMP(P.m.status, 3);
   const uint32_t kth = base + prefix;
   const int need_eq = remaining;
   // Winners in a fixed order, so that every rank that merges the same candidates picks the same keys
@@ -273,13 +311,8 @@ merge_attend_cta_kernel(const __grid_constant__ MergeParams P) {
   // in the candidate array (ranks in order, each rank's list in the order it was written); of the
   // copies of the k-th key the first need_eq are taken.
   const int nwords = (n + 31) >> 5;
-  int n_eq = 0;
-  for (int i = tid; i < n; i += kMergeCtaThreads) n_eq += keys[i] == kth;
-#pragma unroll
-  for (int off = 16; off; off >>= 1) n_eq += __shfl_xor_sync(0xffffffffu, n_eq, off);
-  if (lane == 0 && n_eq) atomicAdd(&ctrl->eqc, n_eq);
-  __syncthreads();
-  n_eq = ctrl->eqc;
+  // the last pass ran at shift 0: the chosen bin of its histogram holds the copies of the k-th key
+  const int n_eq = ctrl->hist[ctrl->digit];
   int cut = need_eq >= n_eq ? 0x7fffffff : -1;
   if (need_eq > 0 && need_eq < n_eq) {
     for (int w = tid; w < nwords; w += kMergeCtaThreads) bits[w] = 0u;
@@ -310,13 +343,20 @@ merge_attend_cta_kernel(const __grid_constant__ MergeParams P) {
     if (key > kth || (key == kth && i <= cut)) {
       const int p = wpre[i >> 5] + __popc(bits[i >> 5] & ((1u << (i & 31)) - 1u));
       if (p < k) {
+        const int id = ids_global ? P.cand_idx[src_of(i)] : idxs[i];
         wkey[p] = key;
-        widx[p] = ids_global ? P.cand_idx[src_of(i)] : idxs[i];
+        widx[p] = id;
+        // first and last winner slot this rank owns: the mixing loop only walks that range
+        if (id >= P.m.own_lo && id < P.m.own_hi) {
+          atomicMin(&ctrl->own_first, p);
+          atomicMax(&ctrl->own_last, p);
+        }
       }
     }
   }
   if (tid == 0) ctrl->wpos = total_win;
   __syncthreads();
+  RA_STAMP(P.m.status, 4);
   const int nw = min(ctrl->wpos, k);
   if (P.m.sel_idx) {
     const size_t dst = (size_t)row * P.m.list_pitch + P.m.list_off;
@@ -336,13 +376,16 @@ merge_attend_cta_kernel(const __grid_constant__ MergeParams P) {
   float lsum = 0.f;
   constexpr int UN = 8;
   constexpr int kRows = 2 * (kMergeCtaThreads / 32);
-  for (int e0 = warp * 2 + (lane >> 4); e0 < nw; e0 += kRows * UN) {
+  // only the slots between the first and the last winner this rank owns can contribute (in the
+  // sharded step that is one contiguous run: the winners proposed by this rank itself)
+  const int e_begin = min(ctrl->own_first, nw), e_end = min(nw, ctrl->own_last + 1);
+  for (int e0 = e_begin + warp * 2 + (lane >> 4); e0 < e_end; e0 += kRows * UN) {
     uint4 vv[UN];
     float w[UN];
 #pragma unroll
     for (int u = 0; u < UN; ++u) {
       const int e = e0 + kRows * u;
-      const int id = (e < nw) ? widx[e] : -1;
+      const int id = (e < e_end) ? widx[e] : -1;
       const int local = id - P.m.id_shift;
       const bool mine = id >= P.m.own_lo && id < P.m.own_hi;
       if (mine && (unsigned)local >= (unsigned)P.m.n_tokens) atomicOr(P.m.status, kStatusBadId);
@@ -409,7 +452,9 @@ merge_attend_cta_kernel(const __grid_constant__ MergeParams P) {
       }
     }
   }
+  RA_STAMP(P.m.status, 5);
   exchange_publish_in_kernel(P.x);
+  RA_STAMP(P.m.status, 6);
 }
 
 size_t merge_attend_cta_smem_bytes(int m_total, int topk, bool ids_global) {

@@ -264,6 +264,7 @@ scan_select_kernel(const __grid_constant__ ScanParams P) {
   int* idxs = reinterpret_cast<int*>(keys + (size_t)NL * cap);
   Ctrl* ctrl = reinterpret_cast<Ctrl*>(idxs + (size_t)NL * cap);
 
+  RA_STAMP(P.status, 0);
   // which part of which (batch group, kv-head group) this cluster owns
   // (or, with parts_in_cluster, which part this CTA owns: the cluster holds all parts of a row)
   const bool pic = P.parts_in_cluster != 0;
@@ -619,6 +620,7 @@ scan_select_kernel(const __grid_constant__ ScanParams P) {
   }
   __syncthreads();
 
+  RA_STAMP(P.status, 1);
   if (RA_DEBUG(P, 16)) return;  // tuning aid: time the scan without the merge
   // ------------------------------------------------------------------ cluster merge
   // The pipeline stages are free now and become the merge scratch.
