@@ -299,6 +299,12 @@ typedef struct ra_merge_params {
   size_t workspace_bytes;
   void* stream;
   const ra_exchange_hooks* exchange;  /* optional, with out_partial only */
+  int32_t own_part_only;       /* 1: only the candidates of part `own_part` can be owned by this
+                                  rank; cand_indices of every other part is not read, so the ranks
+                                  need to exchange the scores only (ties between parts are broken
+                                  by position, not by id).  out_indices then lists -1 for winners of
+                                  other parts.  0: ownership by id range, all ids are read. */
+  int32_t own_part;
 } ra_merge_params;
 
 int ra_merge_attend(const ra_merge_params* p);

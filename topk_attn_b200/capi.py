@@ -60,6 +60,7 @@ class RaMergeParams(C.Structure):
         ("out_indices", C.c_void_p), ("out_scores", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("stream", C.c_void_p),
         ("exchange", C.POINTER(RaExchangeHooks)),
+        ("own_part_only", C.c_int32), ("own_part", C.c_int32),
     ]
 
 

@@ -695,7 +695,7 @@ int run(const ra_params* p, bool attend, const PartIds* ext = nullptr) {
   }
   mp.cand_score = sp.m.sel_score; mp.cand_idx = sp.m.sel_idx;
   mp.part_len = s.topk; mp.part_stride = s.topk; mp.row_stride = (long long)parts * s.topk;
-  mp.m_total = parts * s.topk; mp.cap = pl.cap2; mp.group = c.group;
+  mp.m_total = parts * s.topk; mp.cap = pl.cap2; mp.group = c.group; mp.own_part = -1;
   e = dispatch_merge(mp, s.batch * s.hq, pl, stream);
   if (e != cudaSuccess) return cuda_fail(e, "merge_attend launch");
   return RA_OK;
@@ -1363,6 +1363,11 @@ int ra_merge_attend(const ra_merge_params* p) {
                                        : (long long)p->batch * p->num_q_heads * p->topk;
   mp.row_stride = p->topk;
   mp.m_total = (int)m_total; mp.cap = pl.cap2; mp.group = p->num_q_heads / p->num_kv_heads;
+  mp.own_part = -1;
+  if (p->own_part_only) {
+    if (p->own_part < 0 || p->own_part >= p->num_parts) return invalid("own_part must name one of the parts");
+    mp.own_part = p->own_part;
+  }
   cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
   const int rows = p->batch * p->num_q_heads;
   const ra_exchange_hooks* xh = p->exchange;

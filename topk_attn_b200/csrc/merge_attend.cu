@@ -36,7 +36,7 @@ merge_attend_kernel(const __grid_constant__ MergeParams P) {
     const int part = c / P.part_len, off = c - part * P.part_len;
     const size_t src = (size_t)part * P.part_stride + (size_t)row * P.row_stride + off;
     keys[i] = score_key(P.cand_score[src]);
-    idxs[i] = P.cand_idx[src];
+    idxs[i] = (P.own_part < 0 || part == P.own_part) ? P.cand_idx[src] : -1;
   }
   if (tid == 0) cnt[0] = n;
   __syncthreads();
@@ -197,6 +197,8 @@ merge_attend_cta_kernel(const __grid_constant__ MergeParams P) {
     const int part = c / P.part_len, off = c - part * P.part_len;
     return (size_t)part * P.part_stride + (size_t)row * P.row_stride + off;
   };
+  // whether the id of candidate c may be read (with own_part only this rank's own proposals carry ids)
+  auto readable = [&](int c) { return P.own_part < 0 || c / P.part_len == P.own_part; };
 
   if (tid == 0) {
     ctrl->kmin = 0xffffffffu;
@@ -224,8 +226,8 @@ merge_attend_cta_kernel(const __grid_constant__ MergeParams P) {
       for (int u = 0; u < LU; ++u) {
         const int c = c0 + (u * kMergeCtaThreads + tid) * 4;
         sc[u] = c < n ? *reinterpret_cast<const float4*>(P.cand_score + src_of(c)) : make_float4(0.f, 0.f, 0.f, 0.f);
-        id[u] = (c < n && !ids_global) ? *reinterpret_cast<const int4*>(P.cand_idx + src_of(c))
-                                       : make_int4(0, 0, 0, 0);
+        id[u] = (c < n && !ids_global && readable(c)) ? *reinterpret_cast<const int4*>(P.cand_idx + src_of(c))
+                                                      : make_int4(-1, -1, -1, -1);
       }
 #pragma unroll
       for (int u = 0; u < LU; ++u) {
@@ -249,7 +251,7 @@ merge_attend_cta_kernel(const __grid_constant__ MergeParams P) {
       for (int u = 0; u < LU; ++u) {
         const int c = c0 + u * kMergeCtaThreads + tid;
         sc[u] = c < n ? P.cand_score[src_of(c)] : 0.f;
-        id[u] = (c < n && !ids_global) ? P.cand_idx[src_of(c)] : 0;
+        id[u] = (c < n && !ids_global && readable(c)) ? P.cand_idx[src_of(c)] : -1;
       }
 #pragma unroll
       for (int u = 0; u < LU; ++u) {
@@ -343,7 +345,7 @@ merge_attend_cta_kernel(const __grid_constant__ MergeParams P) {
     if (key > kth || (key == kth && i <= cut)) {
       const int p = wpre[i >> 5] + __popc(bits[i >> 5] & ((1u << (i & 31)) - 1u));
       if (p < k) {
-        const int id = ids_global ? P.cand_idx[src_of(i)] : idxs[i];
+        const int id = ids_global ? (readable(i) ? P.cand_idx[src_of(i)] : -1) : idxs[i];
         wkey[p] = key;
         widx[p] = id;
         // first and last winner slot this rank owns: the mixing loop only walks that range

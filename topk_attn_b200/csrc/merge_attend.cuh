@@ -14,6 +14,8 @@ struct MergeParams {
   int m_total;
   int cap;                  // ceil(m_total / cluster)
   int group;                // query heads per kv head
+  int own_part;             // >= 0: ids are read for the candidates of this part only (the others
+                            // count as -1: never owned); -1: every id is read
   int ids_global;           // single-CTA form: ids are read from cand_idx for the winners only
   ExchangeHooks x;          // single-CTA form: wait for the candidates / push the partial rows
 };

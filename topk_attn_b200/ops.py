@@ -273,7 +273,7 @@ def kv_append(k_cache: Tensor, v_cache: Tensor, new_k: Tensor, new_v: Tensor, po
 
 def merge_attend(cand_scores: Tensor, cand_indices: Tensor, v: Tensor, topk: int, sm_scale: float,
                  own_base: int, partial: bool = True, return_indices: bool = False,
-                 out: Optional[Tensor] = None, exchange=None):
+                 out: Optional[Tensor] = None, exchange=None, own_part: Optional[int] = None):
     """Select the global top-k out of ``cand_* [parts,B,Hq,topk]`` (global ids) and mix the V rows
     held in ``v`` (global ids own_base .. own_base+N).  Returns the fp32 partial [B,Hq,130]
     (128 un-normalised sums, weight, maximum) or, with ``partial=False``, the fp16 output."""
@@ -311,6 +311,9 @@ def merge_attend(cand_scores: Tensor, cand_indices: Tensor, v: Tensor, topk: int
         p.out_indices, p.out_scores = idx.data_ptr(), sc.data_ptr()
     ws = workspace(256, dev)
     p.workspace, p.workspace_bytes, p.stream = ws.data_ptr(), ws.numel(), _stream_ptr()
+    if own_part is not None:
+        # only part `own_part` carries ids (the ranks exchanged scores only)
+        p.own_part_only, p.own_part = 1, own_part
     if exchange is not None:
         # exchange: an object with the fields of sharded.PeerExchange -- the merge waits for the
         # candidate flags itself and pushes its partial rows to the peers

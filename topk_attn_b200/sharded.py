@@ -47,10 +47,10 @@ class CudaBackend:
 
     def merge_partial(self, cand_sc: Tensor, cand_idx: Tensor, v: Tensor, topk: int,
                       sm_scale: float, own_base: int, out: Optional[Tensor] = None,
-                      exchange=None) -> Tensor:
+                      exchange=None, own_part: Optional[int] = None) -> Tensor:
         from . import ops
         return ops.merge_attend(cand_sc, cand_idx, v, topk, sm_scale, own_base, partial=True, out=out,
-                                exchange=exchange)
+                                exchange=exchange, own_part=own_part)
 
     def combine(self, partials: Tensor, exchange=None) -> Tensor:
         from . import ops
@@ -61,7 +61,10 @@ class PeerExchange:
     """Receive buffers of one rank for the two exchanges of a step, laid out identically on every
     rank inside one int32 buffer that all ranks have mapped:
 
-        candidates  [world][2][B][Hq][k]   slot r = rank r's (scores as fp32 bits, ids)
+        candidates  [world][2][B][Hq][k]   slot r = rank r's (scores as fp32 bits, ids); only the
+                                           score half travels: a rank mixes none but its own
+                                           proposals, whose ids it has, and ties between ranks are
+                                           broken by position
         partials    [world][B][Hq][130]    slot r = rank r's un-normalised partial (fp32 bits)
         flags       [2][32]                word r of row 0 / 1 = epoch of rank r's last candidate /
                                            partial push
@@ -101,14 +104,14 @@ class PeerExchange:
         self.flags_p = buf[off_f + 32:off_f + 32 + world]
         self.epoch = torch.ones(1, dtype=torch.int32, device=buf.device)
         self.done = torch.zeros(4, dtype=torch.int32, device=buf.device)   # one word per kernel kind
-        self.dst_c = [b + 4 * (off_c + rank * slot_c) for b in base_ptrs]
+        self.dst_c = [b + 4 * (off_c + rank * slot_c) for b in base_ptrs]   # the score half comes first
         self.dst_p = [b + 4 * (off_p + rank * slot_p) for b in base_ptrs]
         self.flg_c = [b + 4 * (off_f + rank) for b in base_ptrs]
         self.flg_p = [b + 4 * (off_f + 32 + rank) for b in base_ptrs]
 
     def push_candidates(self) -> None:
         from . import ops
-        ops.exchange_push(self.cand[self.rank], self.dst_c, self.flg_c, self.epoch, self.done[0:1])
+        ops.exchange_push(self.cand[self.rank, 0], self.dst_c, self.flg_c, self.epoch, self.done[0:1])
 
     def wait_candidates(self) -> None:
         from . import ops
@@ -220,7 +223,8 @@ class ShardedTopkAttention:
         if self.exchange is not None:
             # the merge waits for the candidate flags, writes this rank's partial and pushes it
             self.backend.merge_partial(cand_sc, cand_idx, v, self.topk, self.sm_scale, index_base,
-                                       out=partials[self.rank], exchange=self.exchange)
+                                       out=partials[self.rank], exchange=self.exchange,
+                                       own_part=self.rank)
             return
         part = self.backend.merge_partial(cand_sc, cand_idx, v, self.topk, self.sm_scale, index_base)
         if self.world > 1:
@@ -372,6 +376,12 @@ def verify_sharded_step(op: "ShardedTopkAttention", q: Tensor, k: Tensor, v: Ten
     out = op.step(q, k, v, index_base)
     B, Hq, _ = q.shape
     cand_sc, cand_idx, _ = op._buffers(B, Hq, q.device)
+    if op.exchange is not None and op.world > 1 and dist.is_initialized():
+        # the peer exchange moves scores only; the check wants every rank's ids as well
+        torch.cuda.synchronize()
+        ids = torch.empty(op.world, B, Hq, op.topk, dtype=torch.int32, device=q.device)
+        dist.all_gather_into_tensor(ids.view(-1, Hq, op.topk), cand_idx[op.rank].contiguous(), group=op.group)
+        cand_idx.copy_(ids)
     _, gidx, gsc = ops.merge_attend(cand_sc, cand_idx, v, op.topk, op.sm_scale, index_base,
                                     partial=True, return_indices=True)
     ops.check_status(q.device)
@@ -407,6 +417,11 @@ def time_sharded(op: "ShardedTopkAttention", q: Tensor, k: Tensor, v: Tensor, in
     b.record()
     torch.cuda.synchronize()
     scan_ms = a.elapsed_time(b) / steps
+    if multi:
+        # a step waits for the slowest rank's proposals: report the slowest scan
+        sm = torch.tensor([scan_ms], device=dev)
+        dist.all_reduce(sm, op=dist.ReduceOp.MAX)
+        scan_ms = sm.item()
     run()                       # the exchanged candidates are this step's again
     if multi:
         dist.barrier()
