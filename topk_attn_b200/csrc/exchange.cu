@@ -24,24 +24,23 @@ namespace ra {
 __global__ void __launch_bounds__(kPushThreads)
 exchange_push_kernel(const __grid_constant__ PushParams P) {
   const size_t stride = (size_t)gridDim.x * kPushThreads;
-  for (size_t i = (size_t)blockIdx.x * kPushThreads + threadIdx.x; i < P.n16; i += stride) {
-    const uint4 v = P.src[i];
+  bool any_remote = false;
+  for (int p = 0; p < P.npeers; ++p) any_remote |= (P.dst[p] != P.src);
+  if (any_remote) {
+    for (size_t i0 = (size_t)blockIdx.x * kPushThreads + threadIdx.x; i0 < P.n16; i0 += 4 * stride) {
+      uint4 v[4];   // four loads in flight per thread, then the stores to every peer
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = (i0 + u * stride < P.n16) ? P.src[i0 + u * stride] : make_uint4(0, 0, 0, 0);
 #pragma unroll 1
-    for (int p = 0; p < P.npeers; ++p)
-      if (P.dst[p] != P.src) P.dst[p][i] = v;
-  }
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    const unsigned arrived = atomicAdd(P.done, 1u);
-    if (arrived == gridDim.x - 1) {
-      // every CTA's stores are fenced and counted: publish
-      *P.done = 0u;   // ready for the next launch (kernel boundaries order it)
-      __threadfence_system();
-      const unsigned e = *P.epoch;
-      for (int p = 0; p < P.npeers; ++p) st_release_sys(P.flag[p], e);
+      for (int p = 0; p < P.npeers; ++p) {
+        if (P.dst[p] == P.src) continue;
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (i0 + u * stride < P.n16) P.dst[p][i0 + u * stride] = v[u];
+      }
     }
   }
+  exchange_publish(P.done, P.epoch, P.flag, P.npeers, nullptr);
 }
 
 __global__ void __launch_bounds__(kMaxPeers)

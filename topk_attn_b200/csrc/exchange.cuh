@@ -59,22 +59,40 @@ __device__ __forceinline__ void exchange_wait_in_kernel(const ExchangeHooks& X, 
   __syncthreads();
 }
 
-// Called by all threads of every CTA after its stores to peer memory: the last CTA of the grid
-// publishes the flags (and advances the epoch when asked to).
+__device__ __forceinline__ void st_relaxed_sys(unsigned* p, unsigned v) {
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Publish step shared by the push kernel and the kernels with the exchange fused in; called by all
+// threads of every CTA after its stores to peer memory.  Every CTA orders its stores at device
+// scope and counts itself; the last CTA to arrive issues ONE system-scope fence (cumulative: it
+// covers the stores of all CTAs it synchronised with through the counter) and then writes this
+// rank's flag on every peer with relaxed system-scope stores, one lane per peer.  System-scope
+// fences and release stores cost microseconds each here, so there is exactly one per launch.
+__device__ __forceinline__ void exchange_publish(unsigned* done, const unsigned* epoch,
+                                                 unsigned* const* peer_flag, int npeers,
+                                                 unsigned* epoch_rw) {
+  __shared__ unsigned s_last, s_epoch;
+  __syncthreads();   // orders every thread's stores before thread 0's (cumulative) fence
+  if (threadIdx.x == 0) {
+    __threadfence();
+    s_last = (atomicAdd(done, 1u) == gridDim.x - 1) ? 1u : 0u;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  if (threadIdx.x == 0) {
+    *done = 0u;   // ready for the next launch (kernel boundaries order it)
+    __threadfence_system();
+    s_epoch = *epoch;
+  }
+  __syncthreads();
+  if ((int)threadIdx.x < npeers) st_relaxed_sys(peer_flag[threadIdx.x], s_epoch);
+  if (epoch_rw && threadIdx.x == 0) *epoch_rw = s_epoch + 1u;
+}
+
 __device__ __forceinline__ void exchange_publish_in_kernel(const ExchangeHooks& X) {
   if (X.done == nullptr) return;
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    const unsigned arrived = atomicAdd(X.done, 1u);
-    if (arrived == gridDim.x - 1) {
-      *X.done = 0u;
-      __threadfence_system();
-      const unsigned e = *X.epoch;
-      for (int p = 0; p < X.npeers; ++p) st_release_sys(X.peer_flag[p], e);
-      if (X.advance) *X.epoch_rw = e + 1u;
-    }
-  }
+  exchange_publish(X.done, X.epoch, X.peer_flag, X.npeers, X.advance ? X.epoch_rw : nullptr);
 }
 
 cudaError_t launch_exchange_push(const PushParams& P, int grid, cudaStream_t stream);

@@ -340,6 +340,7 @@ merge_attend_cta_kernel(const __grid_constant__ MergeParams P) {
   }
   __syncthreads();
   const int total_win = bitmap_prefix(bits, wpre, ctrl->wsum, nwords, tid, kMergeCtaThreads);
+  int my_first = 0x7fffffff, my_last = -1;
   for (int i = tid; i < n; i += kMergeCtaThreads) {
     const uint32_t key = keys[i];
     if (key > kth || (key == kth && i <= cut)) {
@@ -350,11 +351,17 @@ merge_attend_cta_kernel(const __grid_constant__ MergeParams P) {
         widx[p] = id;
         // first and last winner slot this rank owns: the mixing loop only walks that range
         if (id >= P.m.own_lo && id < P.m.own_hi) {
-          atomicMin(&ctrl->own_first, p);
-          atomicMax(&ctrl->own_last, p);
+          my_first = min(my_first, p);
+          my_last = max(my_last, p);
         }
       }
     }
+  }
+  my_first = __reduce_min_sync(0xffffffffu, my_first);
+  my_last = __reduce_max_sync(0xffffffffu, my_last);
+  if (lane == 0 && my_last >= 0) {
+    atomicMin(&ctrl->own_first, my_first);
+    atomicMax(&ctrl->own_last, my_last);
   }
   if (tid == 0) ctrl->wpos = total_win;
   __syncthreads();
