@@ -71,8 +71,8 @@ def test_logical_ranks_exchange_by_peer_stores(G, B, Hq, Hkv, N, topk):
 
 @pytest.mark.parametrize("G,B,Hq,Hkv,N,topk", [
     (4, 1, 8, 2, 32768, 512),
-    (8, 1, 32, 8, 65536, 4096),      # few rows, 32768 candidates each: cluster merge, separate wait and push
-    (8, 2, 32, 8, 65536, 4096),      # more rows: one CTA per row, ids stay in global memory
+    (8, 1, 32, 8, 65536, 4096),      # 32768 candidates per row: ids stay in global memory
+    (8, 2, 32, 8, 65536, 4096),
     (2, 4, 8, 8, 16384, 1024),
 ])
 def test_logical_ranks_with_the_exchange_fused_into_merge_and_combine(G, B, Hq, Hkv, N, topk):
@@ -175,3 +175,33 @@ def test_pipeline_wait_runs_out_and_reports_a_timeout(monkeypatch):
     ref = ops.topk_attention(qd, kd, vd, 64)
     ops.check_status(DEV)
     assert torch.equal(out, ref)
+
+
+def test_cluster_merge_with_separate_wait_and_push(monkeypatch):
+    """When the candidates of a row do not fit one CTA the merge runs as a cluster of CTAs and the
+    exchange steps run as kernels of their own around it; forced here through the tuning build."""
+    from topk_attn_b200 import capi, ops
+    from topk_attn_b200.sharded import ShardedTopkAttention
+    G, B, Hq, Hkv, N, topk = 4, 1, 8, 2, 32768, 512
+    q, k, v = rand_case(B, Hq, Hkv, N, False, seed=77)
+    n = N // G
+    qd = q.to(DEV)
+    ks = [k[r * n:(r + 1) * n].contiguous().to(DEV) for r in range(G)]
+    vs = [v[r * n:(r + 1) * n].contiguous().to(DEV) for r in range(G)]
+    monkeypatch.setenv("RA_FORCE_MERGE_CLUSTER", "8")
+    with capi.tuning_library():
+        exs = logical_ranks(G, B, Hq, topk)
+        shard = [ShardedTopkAttention(topk, 0.9, exchange=exs[r]) for r in range(G)]
+        bufs = [shard[r]._buffers(B, Hq, DEV) for r in range(G)]
+        for r in range(G):
+            idx, sc = shard[r].local_candidates(qd, ks[r], r * n)
+            shard[r].exchange_candidates(idx, sc)
+        for r in range(G):
+            shard[r].merge_and_exchange(bufs[r][0], bufs[r][1], bufs[r][2], vs[r], r * n)
+        outs = [shard[r].backend.combine(bufs[r][2], exchange=exs[r]) for r in range(G)]
+        ops.check_status(DEV)
+    s = O.full_scores(q, k)
+    ref, _, _ = O.topk_sparse_attention(q, k, v, topk, 0.9, scores=s)
+    for r in range(G):
+        O.check_output(ref, outs[r])
+        assert torch.equal(outs[r], outs[0])
