@@ -415,6 +415,20 @@ def run_ours(args):
                 ops.l2_persist(None)
     ops.check_status(dev)
 
+    # what this GPU delivers to a kernel that only reads (the copy figure of the roofline reads and
+    # writes): one read-only stream over the key cache, when it is much larger than L2
+    read_gbs = None
+    if not small:
+        for _ in range(2):
+            ops.stream_read_probe(k)
+        r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        r0.record()
+        for _ in range(5):
+            ops.stream_read_probe(k)
+        r1.record()
+        torch.cuda.synchronize()
+        read_gbs = 5 * k.numel() * 2 / (r0.elapsed_time(r1) * 1e-3) / 1e9
+
     # end to end: query from pinned host memory, output read back, every step
     q_host = q.cpu().pin_memory()
     out_host = torch.empty_like(q_host).pin_memory()
@@ -460,7 +474,10 @@ def run_ours(args):
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "peak_kind": peak_kind + " (burst copy)",
                      "algorithmic_bytes": alg_bytes, "traffic": None,
-                     "kernel": kernel_name},
+                     "kernel": kernel_name,
+                     "read_only_stream_gbs": read_gbs,
+                     "frac_of_read_only_stream": (achieved / read_gbs) if read_gbs else None,
+                     "ms_x_sm_mhz": per_ms * clocks["sm_mhz"] if clocks.get("sm_mhz") else None},
         "cpu_baseline": {"value": (cw.batch * cw.n_tokens / cpu_t) if cw is not None else None,
                          "unit": "tokens/s",
                          "cores": torch.get_num_threads(), "kind": "port", "sample": what},

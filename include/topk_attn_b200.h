@@ -321,6 +321,12 @@ int ra_lse_combine_wait(const float* partials, int32_t num_parts, int32_t rows, 
                         const void* wait_flags, int32_t num_flags, void* epoch, uint64_t timeout_ns,
                         void* done_counter, void* status_workspace, void* stream);
 
+/* Measuring aid (no counterpart in the reference): one kernel that reads `bytes` (a multiple of 16)
+ * from `src` and does nothing else, on `stream`.  Timing it over a buffer much larger than L2 gives
+ * the read-only streaming rate of the device, the natural ceiling of a K scan, beside the copy
+ * (read + write) figure rooflines are usually quoted against.  `sink` is one writable device word. */
+int ra_stream_read_probe(const void* src, size_t bytes, void* sink, void* stream);
+
 /* Keep a cache resident in L2 across consecutive decode steps (no counterpart in the reference,
  * whose pipelined kernels keep K hot only inside one launch, retrieval_attn/
  * retrieval_attention.cu:654-896).  Marks [base, base + bytes) as persisting for every kernel later

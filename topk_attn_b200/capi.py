@@ -191,6 +191,7 @@ def _declare(l: C.CDLL) -> None:
         "ra_center_only_topk": (C.c_int, [C.POINTER(RaCenterParams)]),
         "ra_center_workspace_bytes": (sz, [i32, i32, i32, i32]),
         "ra_lse_combine": (C.c_int, [vp, i32, i32, vp, vp]),
+        "ra_stream_read_probe": (C.c_int, [vp, sz, vp, vp]),
         "ra_l2_persist": (C.c_int, [vp, sz, f32, vp]),
         "ra_lse_combine_wait": (C.c_int, [vp, i32, i32, vp, vp, i32, vp, C.c_uint64, vp, vp, vp]),
         "ra_exchange_push": (C.c_int, [vp, sz, C.POINTER(vp), C.POINTER(vp), i32, vp, vp, vp]),

@@ -1442,6 +1442,15 @@ int ra_lse_combine(const float* partials, int32_t num_parts, int32_t rows, void*
   return RA_OK;
 }
 
+int ra_stream_read_probe(const void* src, size_t bytes, void* sink, void* stream) {
+  if (!src || !sink || bytes < 16 || (bytes & 15u) || (reinterpret_cast<uintptr_t>(src) & 15u))
+    return invalid("src and sink must be given, src 16-byte aligned, bytes a positive multiple of 16");
+  cudaError_t e = launch_stream_read(src, bytes, static_cast<unsigned*>(sink), 4 * sm_count(),
+                                     static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "stream_read launch");
+  return RA_OK;
+}
+
 int ra_l2_persist(const void* base, size_t bytes, float hit_ratio, void* stream) {
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaStreamAttrValue attr;

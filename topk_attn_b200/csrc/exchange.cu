@@ -61,6 +61,30 @@ exchange_wait_kernel(const unsigned* flags, int n, unsigned* epoch, int advance,
   if (advance && threadIdx.x == 0) *epoch = want + 1u;
 }
 
+// Read-only stream over a buffer (a measuring aid for benchmarks: what this GPU delivers to a
+// kernel that only reads, next to the copy figure the roofline is quoted against).  Eight 16-byte
+// loads in flight per thread; the folded words go to `sink` so that nothing is optimised away.
+__global__ void __launch_bounds__(512)
+stream_read_kernel(const uint4* __restrict__ src, size_t n16, unsigned* sink) {
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  unsigned acc = 0u;
+  for (size_t i0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i0 < n16; i0 += 8 * stride) {
+    uint4 v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+      v[u] = (i0 + u * stride < n16) ? ldg128_nc(src + i0 + u * stride) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) acc ^= v[u].x ^ v[u].y ^ v[u].z ^ v[u].w;
+  }
+  if (acc == 0x9e3779b9u) sink[0] = acc;   // practically never: keeps the loads alive
+}
+
+cudaError_t launch_stream_read(const void* src, size_t bytes, unsigned* sink, int grid, cudaStream_t stream) {
+  note_launch();
+  stream_read_kernel<<<grid, 512, 0, stream>>>(static_cast<const uint4*>(src), bytes / 16, sink);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_exchange_push(const PushParams& P, int grid, cudaStream_t stream) {
   note_launch();
   exchange_push_kernel<<<grid, kPushThreads, 0, stream>>>(P);

@@ -95,6 +95,7 @@ __device__ __forceinline__ void exchange_publish_in_kernel(const ExchangeHooks& 
   exchange_publish(X.done, X.epoch, X.peer_flag, X.npeers, X.advance ? X.epoch_rw : nullptr);
 }
 
+cudaError_t launch_stream_read(const void* src, size_t bytes, unsigned* sink, int grid, cudaStream_t stream);
 cudaError_t launch_exchange_push(const PushParams& P, int grid, cudaStream_t stream);
 cudaError_t launch_exchange_wait(const unsigned* flags, int n, unsigned* epoch, int advance,
                                  unsigned long long limit_ns, unsigned* status, cudaStream_t stream);

@@ -354,6 +354,14 @@ def lse_combine(partials: Tensor, out: Optional[Tensor] = None, exchange=None) -
     return out
 
 
+def stream_read_probe(buf: Tensor) -> None:
+    """Enqueue one kernel that only reads ``buf`` (a measuring aid: time it over a buffer much larger
+    than L2 to get the device's read-only streaming rate)."""
+    nbytes = buf.numel() * buf.element_size() // 16 * 16
+    sink = workspace(256, buf.device)
+    capi.check(capi.lib().ra_stream_read_probe(buf.data_ptr(), nbytes, sink.data_ptr() + 128, _stream_ptr()))
+
+
 def l2_persist(cache: Optional[Tensor], hit_ratio: float = 1.0) -> None:
     """Mark ``cache`` (a key cache shared by the batch, up to roughly the L2 size) as persisting in
     L2 for the kernels launched into the current stream from now on, so that consecutive decode
