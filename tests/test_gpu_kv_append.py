@@ -67,3 +67,13 @@ def test_l2_persistence_window_can_be_set_and_removed():
     ops.l2_persist(None)
     ops.check_status(dev)
     assert torch.equal(out, ref)
+
+
+def test_stream_read_probe_runs():
+    """The read-only stream used by the bench to measure the device's streaming rate."""
+    from topk_attn_b200 import ops
+    dev = torch.device("cuda:0")
+    buf = torch.ones(1 << 22, dtype=torch.int32, device=dev)
+    ops.stream_read_probe(buf)
+    torch.cuda.synchronize()
+    ops.check_status(dev)
