@@ -1,0 +1,120 @@
+"""The histogram route of the sharded step (ra_sharded_topk_partial) on one GPU.
+
+Its selection kernel waits for the other ranks' histograms inside the kernel, so logical ranks
+cannot be played by separate launches on one device.  Here a single rank runs the whole route (its
+own flags satisfy every wait): scoring, the rounds of the radix select over exchanged histograms,
+the share-out of copies of the k-th score, the partial and the combine -- against the
+single-device operator and the oracle.  The cross-rank sums are checked on real ranks by
+``bench.py --gpus N``, which verifies every rank's winners before it times anything.
+"""
+import pytest
+import torch
+
+from oracle import topk_attn_oracle as O
+
+from gpu_util import rand_case
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda:0")
+
+
+def one_rank(B, Hq, topk, timeout_s=2.0):
+    from topk_attn_b200.sharded import HistExchange
+    words = HistExchange.layout(1, B, Hq, topk)[-1]
+    buf = torch.zeros(words, dtype=torch.int32, device=DEV)
+    return HistExchange(buf, [buf.data_ptr()], 0, 1, B, Hq, topk, timeout_s)
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,N,topk,per_batch", [
+    (1, 8, 2, 20000, 256, False),      # a GQA group of 4
+    (2, 4, 4, 16384, 512, False),      # one cache shared by two batch rows
+    (1, 32, 8, 65536, 4096, False),    # the long-context configuration, shortened
+    (2, 8, 4, 9000, 128, True),        # a cache per batch row, group of 2, ragged length
+])
+def test_one_rank_matches_the_single_device_operator(B, Hq, Hkv, N, topk, per_batch):
+    from topk_attn_b200 import ops
+    from topk_attn_b200.sharded import ShardedTopkAttention, verify_sharded_step
+    q, k, v = rand_case(B, Hq, Hkv, N, per_batch, seed=11)
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    ex = one_rank(B, Hq, topk)
+    op = ShardedTopkAttention(topk, 0.5, exchange=ex, mode="histograms")
+    ref, ridx, _ = ops.topk_attention(qd, kd, vd, topk, 0.5, return_indices=True)
+    for _ in range(2):                                   # the buffers are reused step after step
+        out = op.step(qd, kd, vd, 0)
+    torch.cuda.synchronize()
+    ops.check_status(DEV)
+    assert torch.allclose(out.float(), ref.float(), rtol=1e-2, atol=1e-3)
+    idx, _ = ops.sharded_topk_partial(qd, kd, vd, topk, 0.5, 0, ex, return_indices=True)
+    ops.lse_combine(ex.partials, exchange=ex)            # ends the step
+    torch.cuda.synchronize()
+    assert torch.equal(idx.sort(-1).values, ridx.sort(-1).values)
+    res = verify_sharded_step(op, qd, kd, vd, 0)
+    assert res["ok"], res
+    want = O.topk_sparse_attention(q, k, v, topk, 0.5)[0]
+    assert torch.allclose(out.float().cpu(), want.float(), rtol=1e-2, atol=1e-3)
+
+
+def test_copies_of_the_kth_score_are_taken_in_token_order():
+    """Every key of a head is the same vector: all scores tie, the k winners are tokens 0..k-1
+    (round 2 of the select runs, and the copies exceed the candidate list)."""
+    from topk_attn_b200 import ops
+    from topk_attn_b200.sharded import ShardedTopkAttention
+    B, Hq, Hkv, N, topk = 1, 8, 2, 40000, 300
+    g = torch.Generator().manual_seed(5)
+    q = torch.randn(B, Hq, 128, generator=g).half()
+    k = torch.randn(1, Hkv, 128, generator=g).half().expand(N, Hkv, 128).contiguous()
+    v = torch.randn(N, Hkv, 128, generator=g).half()
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    ex = one_rank(B, Hq, topk)
+    idx, _ = ops.sharded_topk_partial(qd, kd, vd, topk, 1.0, 0, ex, return_indices=True)
+    out = ops.lse_combine(ex.partials, exchange=ex)
+    torch.cuda.synchronize()
+    ops.check_status(DEV)
+    want_ids = torch.arange(topk, dtype=torch.int32, device=DEV).expand(B, Hq, topk)
+    assert torch.equal(idx.sort(-1).values, want_ids)
+    ref = vd[:topk].float().mean(0)                      # equal weights over tokens 0..k-1
+    for h in range(Hq):
+        assert torch.allclose(out[0, h].float(), ref[h // (Hq // Hkv)], rtol=1e-2, atol=2e-3)
+
+
+def test_step_replays_from_a_cuda_graph():
+    from topk_attn_b200 import ops
+    from topk_attn_b200.sharded import ShardedTopkAttention
+    q, k, v = rand_case(1, 8, 2, 30000, False, seed=4)
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    ex = one_rank(1, 8, 256)
+    op = ShardedTopkAttention(256, 1.0, exchange=ex, mode="histograms")
+    replay = op.capture(qd, kd, vd, 0)
+    ref = ops.topk_attention(qd, kd, vd, 256, 1.0)
+    for _ in range(3):
+        out = replay()
+    op.check_graph_status()
+    assert torch.allclose(out.float(), ref.float(), rtol=1e-2, atol=1e-3)
+
+
+def test_a_histogram_that_never_arrives_ends_in_a_timeout():
+    """World of two with nobody playing rank 1: the wait for its histogram runs out, the kernel
+    returns, the status word reports it and the context stays usable."""
+    from topk_attn_b200 import capi, ops
+    from topk_attn_b200.sharded import HistExchange
+    B, Hq, topk = 1, 8, 128
+    words = HistExchange.layout(2, B, Hq, topk)[-1]
+    bufs = [torch.zeros(words, dtype=torch.int32, device=DEV) for _ in range(2)]
+    ex = HistExchange(bufs[0], [b.data_ptr() for b in bufs], 0, 2, B, Hq, topk, timeout_s=0.05)
+    q, k, v = rand_case(B, Hq, 2, 8192, False, seed=2)
+    ops.sharded_topk_partial(q.to(DEV), k.to(DEV), v.to(DEV), topk, 1.0, 0, ex)
+    torch.cuda.synchronize()
+    with pytest.raises(capi.RaError) as err:
+        ops.check_status(DEV)
+    assert err.value.status == capi.RA_ERR_DEVICE_TIMEOUT
+    ops.workspace(256, DEV)[:4].zero_()                  # the status bits are sticky
+    ops.check_status(DEV)
+
+
+def test_shapes_outside_the_route_are_refused():
+    from topk_attn_b200 import capi, ops
+    q, k, v = rand_case(1, 4, 4, 8192, False, seed=1)   # one query per K row
+    ex = one_rank(1, 4, 64)
+    with pytest.raises(capi.RaError) as err:
+        ops.sharded_topk_partial(q.to(DEV), k.to(DEV), v.to(DEV), 64, 1.0, 0, ex)
+    assert err.value.status == capi.RA_ERR_UNSUPPORTED

@@ -23,10 +23,10 @@ LIB = os.path.join(LIBDIR, "libtopk_attn_b200.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 TUNING_LIB = os.path.join(LIBDIR, "libtopk_attn_b200_tuning.so")
-CU_SOURCES = ["api.cu", "scan_select.cu", "scan_store.cu", "select_stored.cu", "merge_attend.cu",
+CU_SOURCES = ["api.cu", "scan_select.cu", "scan_store.cu", "select_stored.cu", "select_sharded.cu", "merge_attend.cu",
               "gather_attend.cu", "flash_decode.cu", "center_select.cu", "dense_select.cu", "exchange.cu"]
 # sources that read the route / phase overrides when compiled with -DRA_TUNING
-TUNING_SOURCES = ["api.cu", "scan_select.cu", "select_stored.cu", "dense_select.cu", "center_select.cu", "merge_attend.cu"]
+TUNING_SOURCES = ["api.cu", "scan_select.cu", "select_stored.cu", "select_sharded.cu", "dense_select.cu", "center_select.cu", "merge_attend.cu"]
 
 
 def _newer(target: str, deps) -> bool:

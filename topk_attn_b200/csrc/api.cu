@@ -19,6 +19,7 @@
 #include "merge_attend.cuh"
 #include "scan_select.cuh"
 #include "scan_store.cuh"
+#include "select_sharded.cuh"
 
 namespace ra {
 int scan_max_active_clusters(int hg, int nq, int cluster, size_t smem, int threads);
@@ -508,7 +509,8 @@ struct PartIds {
   int* coarse_ids_out = nullptr;
 };
 
-int run_store(const ra_params* p, const Shape& s, int group, bool attend, unsigned* status);
+int run_store(const ra_params* p, const Shape& s, int group, bool attend, unsigned* status,
+              const ra_shard_exchange* sx = nullptr, bool scan_only = false);
 
 int run(const ra_params* p, bool attend, const PartIds* ext = nullptr) {
   Checked c;
@@ -702,7 +704,8 @@ int run(const ra_params* p, bool attend, const PartIds* ext = nullptr) {
 // Several queries per K row, one global selection: scan_store_kernel streams K once and stores every
 // score, select_stored_kernel picks the exact top-k per (batch row, query head) from the stored
 // scores and attends over the winners (or writes them out when attend is false).
-int run_store(const ra_params* p, const Shape& s, int group, bool attend, unsigned* status) {
+int run_store(const ra_params* p, const Shape& s, int group, bool attend, unsigned* status,
+              const ra_shard_exchange* sx, bool scan_only) {
   int bshare = 1;
   const int nq_valid = shared_queries(s, &bshare);
   const int rows = s.batch * s.hq;
@@ -764,11 +767,13 @@ int run_store(const ra_params* p, const Shape& s, int group, bool attend, unsign
     per2 = ceil_div(s.topk, c2);
     chunk2 = ceil_div(ceil_div(s.n, c2), kTileRows) * kTileRows;
     det2 = det_words_for(chunk2);
-    fixed = select_stored_fixed_smem_bytes(per2, det2);
+    fixed = sx ? select_sharded_fixed_smem_bytes(per2, det2) : select_stored_fixed_smem_bytes(per2, det2);
     cap2 = fixed < kSmemBudget ? (int)std::min<size_t>(16384, (kSmemBudget - fixed) / 8) : 0;
     if (cap2 >= s.topk + 512 || c2 >= kSelMaxCluster) break;
   }
   if (cap2 < s.topk + 512) return unsupported("topk too large for the stored-score selection");
+  // the selection CTAs of all ranks wait for one another row by row: all of them must be resident
+  if (sx && rows * c2 > sms) return unsupported("too many (batch row, head) pairs for the histogram exchange");
   if (verbose_plan()) {
     static thread_local Shape last_shown = {};
     if ((last_shown < s) || (s < last_shown)) {
@@ -781,6 +786,7 @@ int run_store(const ra_params* p, const Shape& s, int group, bool attend, unsign
   }
   cudaError_t e = launch_scan_store(sp, items * nparts, scan_store_smem_bytes(nq_valid, sp.nstages), stream);
   if (e != cudaSuccess) return cuda_fail(e, "scan_store launch");
+  if (scan_only) return RA_OK;
 
   SelectStoredParams qp;
   memset(&qp, 0, sizeof qp);
@@ -800,6 +806,32 @@ int run_store(const ra_params* p, const Shape& s, int group, bool attend, unsign
   qp.n_tokens = s.n; qp.n_pad = sp.n_pad; qp.nparts = nparts;
   qp.chunk = chunk2;
   qp.cap = cap2; qp.group = group;
+  if (sx) {
+    SelectShardedParams hp;
+    memset(&hp, 0, sizeof hp);
+    m.out_mode = kOutPartial;
+    m.out = nullptr; m.out_lse = nullptr; m.out_partial = sx->out_partial;
+    hp.s = qp;
+    hp.x.world = sx->world; hp.x.rank = sx->rank;
+    hp.x.epoch = static_cast<const unsigned*>(sx->epoch);
+    hp.x.limit_ns = sx->wait_timeout_ns;
+    for (int r = 0; r < sx->world; ++r) {
+      hp.x.hist_peer[r] = static_cast<uint32_t*>(sx->hist_bufs[r]);
+      hp.x.flag_peer[r] = static_cast<unsigned*>(sx->hist_flags[r]);
+    }
+    if (sx->peer_partials) {
+      hp.part.epoch = hp.x.epoch;
+      hp.part.npeers = sx->world;
+      for (int r = 0; r < sx->world; ++r) {
+        hp.part.peer_rows[r] = static_cast<float*>(sx->peer_partials[r]);
+        hp.part.peer_flag[r] = static_cast<unsigned*>(sx->peer_flags[r]);
+      }
+      hp.part.done = static_cast<unsigned*>(sx->done_counter);
+    }
+    e = launch_select_sharded(hp, rows, fixed + (size_t)cap2 * 8, stream);
+    if (e != cudaSuccess) return cuda_fail(e, "select_sharded launch");
+    return RA_OK;
+  }
   e = launch_select_stored(qp, rows, fixed + (size_t)cap2 * 8, stream);
   if (e != cudaSuccess) return cuda_fail(e, "select_stored launch");
   return RA_OK;
@@ -1440,6 +1472,45 @@ int ra_lse_combine(const float* partials, int32_t num_parts, int32_t rows, void*
                                      static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail(e, "lse_combine launch");
   return RA_OK;
+}
+
+size_t ra_shard_hist_bytes(int32_t rows, int32_t world) {
+  if (rows < 1 || world < 1) return 0;
+  return (size_t)kShardRounds * world * rows * kHistBins * sizeof(uint32_t);
+}
+
+int ra_sharded_topk_partial(const ra_params* p, const ra_shard_exchange* x) {
+  if (!p || !x) return invalid("params and exchange must be given");
+  if (x->world < 1 || x->world > kMaxPeers || x->rank < 0 || x->rank >= x->world)
+    return invalid("bad world / rank");
+  if (!x->hist_bufs || !x->hist_flags || !x->epoch || !x->out_partial || x->wait_timeout_ns == 0)
+    return invalid("histogram buffers, flags, epoch word, out_partial and a wait bound are required");
+  for (int r = 0; r < x->world; ++r)
+    if (!x->hist_bufs[r] || !x->hist_flags[r]) return invalid("a rank's histogram buffer or flags are missing");
+  if (x->peer_partials) {
+    if (!x->peer_flags || !x->done_counter) return invalid("peer_partials need peer_flags and done_counter");
+    for (int r = 0; r < x->world; ++r)
+      if (!x->peer_partials[r] || !x->peer_flags[r]) return invalid("a rank's partial slot or flag is missing");
+    if (x->peer_partials[x->rank] != x->out_partial) return invalid("out_partial must be peer_partials[rank]");
+  }
+  Checked c;
+  int st = check_params(p, true, false, c);
+  if (st != RA_OK) return st;
+  Shape s = c.shape;
+  s.fused_ok = 1;
+  if (!store_shape(s)) return unsupported("the histogram exchange needs several queries per K row and one segment");
+  return run_store(p, s, c.group, true, static_cast<unsigned*>(p->workspace), x);
+}
+
+int ra_score_store_probe(const ra_params* p) {
+  if (!p) return invalid("params is null");
+  Checked c;
+  int st = check_params(p, false, false, c);
+  if (st != RA_OK) return st;
+  Shape s = c.shape;
+  s.fused_ok = 1;
+  if (!store_shape(s)) return unsupported("not a shape of the stored-score route");
+  return run_store(p, s, c.group, false, static_cast<unsigned*>(p->workspace), nullptr, true);
 }
 
 int ra_stream_read_probe(const void* src, size_t bytes, void* sink, void* stream) {

@@ -57,7 +57,9 @@ enum OutMode : int {
 
 struct MergeArgs {
   int topk;        // winners per list
-  int per;         // ceil(topk / cluster)
+  int per;         // ceil(topk / cluster): winner slots per CTA (shared-memory layout)
+  int deal_per;    // winners dealt to each CTA in turn; 0 = per.  Smaller when a caller lowers topk
+                   // for one row at run time and wants its fewer winners spread over all CTAs.
   int cluster;
   int out_mode;
   int hq_total;    // query heads (row pitch of the outputs)
@@ -221,6 +223,7 @@ __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char*
                                       uint32_t sel_base = 0u, int sel_shift = 32, int sel_above = 0) {
   MergeScratch* ms = reinterpret_cast<MergeScratch*>(scratch);
   const int per = A.per, k = A.topk, C = A.cluster;
+  const int dper = A.deal_per > 0 ? A.deal_per : per;
   uint32_t* sel_key = reinterpret_cast<uint32_t*>(scratch + sizeof(MergeScratch));
   int* sel_idx = reinterpret_cast<int*>(sel_key + (size_t)NL * per);
   uint32_t* det_bits = reinterpret_cast<uint32_t*>(scratch + select_scratch_bytes(NL, per, 0));
@@ -371,7 +374,7 @@ __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char*
     }
     __syncthreads();
   } else {
-  // deal the winners evenly and in order: global position p goes to CTA p / per, slot p % per
+  // deal the winners evenly and in order: global position p goes to CTA p / dper, slot p % dper
   const int trange = (tag_lo == kTagByPosition) ? cap : max(tag_range, 1);
 #pragma unroll 1
   for (int l = 0; l < NL; ++l) {
@@ -432,8 +435,8 @@ __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char*
         if ((key > kth || (key == kth && tg <= cut)) && t < (unsigned)det_window) {
           const int p = off_win + base + det_pre[t >> 5] + __popc(det_bits[t >> 5] & ((1u << (t & 31)) - 1u));
           if (p < k) {
-            const int dst = A.per_cta_select ? crank : p / per;
-            const int slot = A.per_cta_select ? p : p - dst * per;
+            const int dst = A.per_cta_select ? crank : p / dper;
+            const int slot = A.per_cta_select ? p : p - dst * dper;
             uint32_t* rk = cluster.map_shared_rank(sel_key, dst);
             int* ri = cluster.map_shared_rank(sel_idx, dst);
             rk[(size_t)l * per + slot] = key;
@@ -458,14 +461,14 @@ __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char*
       const ListDest ld = dest(l);
       if (!ld.valid) continue;
       const int total = ms->total_sel[l];
-      const int n_l = max(0, min(per, total - crank * per));
+      const int n_l = max(0, min(dper, total - crank * dper));
       const size_t rowi = (size_t)ld.bq * A.hq_total + ld.hq;
       for (int e = warp; e < n_l; e += nwarps) {
         const uint32_t mk = sel_key[(size_t)l * per + e];
         const int mi = sel_idx[(size_t)l * per + e];
         int rank = 0;
         for (int j = lane; j < total; j += 32) {
-          const int c = j / per, slot = j - c * per;
+          const int c = j / dper, slot = j - c * dper;
           const uint32_t ok = cluster.map_shared_rank(sel_key, c)[(size_t)l * per + slot];
           const int oi = cluster.map_shared_rank(sel_idx, c)[(size_t)l * per + slot];
           rank += (ok > mk) || (ok == mk && oi < mi);
@@ -486,18 +489,18 @@ __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char*
   for (int l = 0; l < NL; ++l) {
     const ListDest ld = dest(l);
     if (!ld.valid) continue;  // uniform over the CTA
-    const int n_l = A.per_cta_select ? ms->total_sel[l] : max(0, min(per, ms->total_sel[l] - crank * per));
+    const int n_l = A.per_cta_select ? ms->total_sel[l] : max(0, min(dper, ms->total_sel[l] - crank * dper));
     const uint32_t* sk = sel_key + (size_t)l * per;
     const int* si = sel_idx + (size_t)l * per;
     if (A.sel_idx) {
       const size_t dst = ((size_t)ld.bq * A.hq_total + ld.hq) * A.list_pitch + A.list_off +
-                         (A.per_cta_select ? (size_t)0 : (size_t)crank * per);
+                         (A.per_cta_select ? (size_t)0 : (size_t)crank * dper);
       for (int e = tid; e < n_l; e += nthr) {
         A.sel_idx[dst + e] = si[e] + A.index_base;
         if (A.sel_score) A.sel_score[dst + e] = key_score(sk[e]);
       }
       // a part with fewer than k keys pads its slots with entries that can never win
-      const int slots = A.per_cta_select ? k : max(0, min(per, k - crank * per));
+      const int slots = A.per_cta_select ? k : max(0, min(dper, k - crank * dper));
       for (int e = n_l + tid; e < slots; e += nthr) {
         A.sel_idx[dst + e] = -1;
         if (A.sel_score) A.sel_score[dst + e] = -INFINITY;
@@ -582,7 +585,8 @@ __device__ void cluster_select_attend(cg::cluster_group& cluster, unsigned char*
         lt += rl[l];
       }
       const size_t row = (size_t)ld.bq * A.hq_total + ld.hq;
-      const float mscaled = key_score(ms->maxkey[l]) * A.sm_scale;
+      // a list without winners (a shard that holds none of a row's top-k) weighs nothing
+      const float mscaled = ms->total_sel[l] > 0 ? key_score(ms->maxkey[l]) * A.sm_scale : -INFINITY;
       if (A.out_mode == kOutFinal) {
         A.out[row * kHeadDim + d] = __float2half_rn(o / lt);
         if (A.out_lse && d == 0) {

@@ -56,6 +56,11 @@ class CudaBackend:
         from . import ops
         return ops.lse_combine(partials, exchange=exchange)
 
+    def sharded_partial(self, q: Tensor, k: Tensor, v: Tensor, topk: int, sm_scale: float,
+                        index_base: int, exchange, return_indices: bool = False):
+        from . import ops
+        return ops.sharded_topk_partial(q, k, v, topk, sm_scale, index_base, exchange, return_indices)
+
 
 class PeerExchange:
     """Receive buffers of one rank for the two exchanges of a step, laid out identically on every
@@ -92,7 +97,7 @@ class PeerExchange:
 
     def __init__(self, buf: Tensor, base_ptrs: List[int], rank: int, world: int, B: int, Hq: int,
                  topk: int, timeout_s: float = 2.0):
-        slot_c, slot_p, off_c, off_p, off_f, words = self.layout(world, B, Hq, topk)
+        slot_c, slot_p, off_c, off_p, off_f, words = PeerExchange.layout(world, B, Hq, topk)
         if buf.dtype != torch.int32 or buf.numel() < words or world > 32:
             raise ValueError("buffer too small or of the wrong type, or more than 32 ranks")
         self.buf, self.rank, self.world, self.timeout_s = buf, rank, world, timeout_s
@@ -127,7 +132,38 @@ class PeerExchange:
         ops.exchange_wait(self.flags_p, self.epoch, advance=True, timeout_s=self.timeout_s)
 
 
-def make_peer_exchange(B: int, Hq: int, topk: int, device, group=None) -> Optional[PeerExchange]:
+class HistExchange(PeerExchange):
+    """PeerExchange plus the receive buffers of the histogram route (``mode="histograms"`` of
+    ShardedTopkAttention): after the regions of the base class come
+
+        histograms  [3][world][B*Hq][2048]  slot (round, r) = rank r's counts of that round
+        hflags      [3][world][B*Hq]        epoch of rank r's last push of (round, row)
+
+    The candidate region keeps its place (a step of the other route can run on the same buffers)."""
+
+    HIST_ROUNDS, HIST_BINS = 3, 2048
+
+    @classmethod
+    def layout(cls, world: int, B: int, Hq: int, topk: int):
+        base = PeerExchange.layout(world, B, Hq, topk)
+        up = lambda x: (x + cls.ALIGN - 1) // cls.ALIGN * cls.ALIGN
+        rows = B * Hq
+        off_h = up(base[-1])
+        off_hf = up(off_h + cls.HIST_ROUNDS * world * rows * cls.HIST_BINS)
+        return base[:-1] + (off_h, off_hf, up(off_hf + cls.HIST_ROUNDS * world * rows))
+
+    def __init__(self, buf: Tensor, base_ptrs: List[int], rank: int, world: int, B: int, Hq: int,
+                 topk: int, timeout_s: float = 2.0):
+        *_, off_h, off_hf, words = self.layout(world, B, Hq, topk)
+        if buf.numel() < words:
+            raise ValueError("buffer too small for the histogram regions")
+        super().__init__(buf, base_ptrs, rank, world, B, Hq, topk, timeout_s)
+        self.hist_ptrs = [b + 4 * off_h for b in base_ptrs]
+        self.hflag_ptrs = [b + 4 * off_hf for b in base_ptrs]
+
+
+def make_peer_exchange(B: int, Hq: int, topk: int, device, group=None,
+                       histograms: bool = False) -> Optional[PeerExchange]:
     """Receive buffers in symmetric memory (``torch.distributed._symmetric_memory``: one allocation
     per rank, mapped into every rank of the node).  Returns None -- on every rank alike -- when the
     buffers cannot be set up, and the caller stays on the collectives.  Multicast binding of the
@@ -137,11 +173,12 @@ def make_peer_exchange(B: int, Hq: int, topk: int, device, group=None) -> Option
     try:
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm
-        words = PeerExchange.layout(world, B, Hq, topk)[-1]
+        kind = HistExchange if histograms else PeerExchange
+        words = kind.layout(world, B, Hq, topk)[-1]
         buf = symm.empty(words, dtype=torch.int32, device=device)
         buf.zero_()
         hdl = symm.rendezvous(buf, group if group is not None else dist.group.WORLD)
-        ex = PeerExchange(buf, [int(p) for p in hdl.buffer_ptrs], rank, world, B, Hq, topk)
+        ex = kind(buf, [int(p) for p in hdl.buffer_ptrs], rank, world, B, Hq, topk)
         ex._handle = hdl     # keeps the mappings alive
     except Exception as e:   # noqa: BLE001 - any failure means "use the collectives"
         print(f"[topk_attn_b200] rank {rank}: peer exchange unavailable ({type(e).__name__}: {e})",
@@ -156,7 +193,16 @@ def make_peer_exchange(B: int, Hq: int, topk: int, device, group=None) -> Option
 
 class ShardedTopkAttention:
     def __init__(self, topk: int, sm_scale: float = 1.0, group=None, backend=None,
-                 exchange: Optional[PeerExchange] = None):
+                 exchange: Optional[PeerExchange] = None, mode: str = "candidates"):
+        """``mode="histograms"`` (needs a HistExchange and several queries per K row -- a GQA group
+        or one cache shared by the batch): the ranks agree on the global k-th score through
+        exchanged histograms of their scores and no candidate lists travel; steps 1-3 above become
+        one call (``ra_sharded_topk_partial``)."""
+        if mode not in ("candidates", "histograms"):
+            raise ValueError("mode must be 'candidates' or 'histograms'")
+        if mode == "histograms" and not isinstance(exchange, HistExchange):
+            raise ValueError("the histogram route needs a HistExchange")
+        self.mode = mode
         self.topk, self.sm_scale, self.group = topk, sm_scale, group
         self.backend = backend if backend is not None else CudaBackend()
         self.exchange = exchange
@@ -208,6 +254,9 @@ class ShardedTopkAttention:
         if index_base is None:
             index_base = self.rank * n
         cand_sc, cand_idx, partials = self._buffers(B, Hq, q.device)
+        if self.mode == "histograms":
+            self.backend.sharded_partial(q, k, v, self.topk, self.sm_scale, index_base, self.exchange)
+            return self.backend.combine(partials, exchange=self.exchange)
         idx, sc = self.local_candidates(q, k, index_base)
         self.exchange_candidates(idx, sc)
         self.merge_and_exchange(cand_sc, cand_idx, partials, v, index_base)
@@ -373,8 +422,29 @@ def verify_sharded_step(op: "ShardedTopkAttention", q: Tensor, k: Tensor, v: Ten
                         index_base: int) -> dict:
     """One untimed sharded step and its check (see verify_winners)."""
     from . import ops
-    out = op.step(q, k, v, index_base)
     B, Hq, _ = q.shape
+    if op.mode == "histograms":
+        # every rank reports its own winners; all of them together must be the global top-k
+        _, _, partials = op._buffers(B, Hq, q.device)
+        idx, sc = op.backend.sharded_partial(q, k, v, op.topk, op.sm_scale, index_base, op.exchange,
+                                             return_indices=True)
+        out = op.backend.combine(partials, exchange=op.exchange)
+        torch.cuda.synchronize()
+        ops.check_status(q.device)
+        if op.world > 1 and dist.is_initialized():
+            ids = torch.empty(op.world, B, Hq, op.topk, dtype=torch.int32, device=q.device)
+            scs = torch.empty(op.world, B, Hq, op.topk, dtype=torch.float32, device=q.device)
+            dist.all_gather_into_tensor(ids.view(-1, Hq, op.topk), idx, group=op.group)
+            dist.all_gather_into_tensor(scs.view(-1, Hq, op.topk), sc, group=op.group)
+            ids = ids.permute(1, 2, 0, 3).reshape(B, Hq, -1)
+            scs = scs.permute(1, 2, 0, 3).reshape(B, Hq, -1)
+            gsc, pos = scs.topk(op.topk, dim=-1)
+            gidx = ids.gather(-1, pos)
+        else:
+            gidx, gsc = idx, sc
+        return verify_winners(q, k, v, out, gidx.contiguous(), gsc.contiguous(), op.topk, op.sm_scale,
+                              index_base, op.world)
+    out = op.step(q, k, v, index_base)
     cand_sc, cand_idx, _ = op._buffers(B, Hq, q.device)
     if op.exchange is not None and op.world > 1 and dist.is_initialized():
         # the peer exchange moves scores only; the check wants every rank's ids as well
@@ -413,7 +483,10 @@ def time_sharded(op: "ShardedTopkAttention", q: Tensor, k: Tensor, v: Tensor, in
         dist.barrier()
     a.record()
     for _ in range(steps):
-        op.local_candidates(q, k, index_base)
+        if op.mode == "histograms":
+            ops.stored_scores_probe(q, k, op.topk)     # the scan kernel of this route alone
+        else:
+            op.local_candidates(q, k, index_base)
     b.record()
     torch.cuda.synchronize()
     scan_ms = a.elapsed_time(b) / steps
@@ -444,7 +517,7 @@ def time_sharded(op: "ShardedTopkAttention", q: Tensor, k: Tensor, v: Tensor, in
 
 
 def bench_long_context(rank: int, world: int, dev, steps: int, warmup: int, peak_gbs: float,
-                       collectives: bool = False) -> dict:
+                       collectives: bool = False, histograms: bool = True) -> dict:
     """Configuration 4 (1 048 576 tokens, 32 query / 8 kv heads, k = 4096) cut over ``world`` ranks:
     total work is fixed, so the time per step should fall as ranks are added (strong scaling).  On
     one GPU the step is the single fused call; on several it is the sharded step.  Every record
@@ -473,8 +546,11 @@ def bench_long_context(rank: int, world: int, dev, steps: int, warmup: int, peak
         scan_ms = per_ms
         how, ex = "eager", None
     else:
-        ex = None if collectives else make_peer_exchange(q.size(0), q.size(1), w.topk, dev)
-        op = ShardedTopkAttention(w.topk, w.sm_scale, exchange=ex)
+        ex = None if collectives else make_peer_exchange(q.size(0), q.size(1), w.topk, dev,
+                                                         histograms=histograms)
+        hist = histograms and isinstance(ex, HistExchange)
+        op = ShardedTopkAttention(w.topk, w.sm_scale, exchange=ex,
+                                  mode="histograms" if hist else "candidates")
         parity = verify_sharded_step(op, q, k, v, base)
         per_ms, scan_ms, _, how = time_sharded(op, q, k, v, base, steps, warmup)
     n_total = world * n_local
@@ -483,7 +559,9 @@ def bench_long_context(rank: int, world: int, dev, steps: int, warmup: int, peak
             "n_gpus": world, "context": n_total, "context_per_gpu": n_local, "scaling": "strong",
             "us_per_step": per_ms * 1e3, "tokens_per_s": n_total / (per_ms * 1e-3),
             "scan_us": scan_ms * 1e3, "exchange_us": (per_ms - scan_ms) * 1e3,
-            "exchange": "none" if world == 1 else ("peer stores + flags" if ex is not None else "nccl all_gather x2"),
+            "exchange": "none" if world == 1 else (
+                ("histograms over peer stores + flags" if op.mode == "histograms" else "peer stores + flags")
+                if ex is not None else "nccl all_gather x2"),
             "issued_as": how,
             "roofline_frac_step": alg_per_gpu / (per_ms * 1e-3) / 1e9 / peak_gbs,
             "algorithmic_bytes_per_gpu": alg_per_gpu, "parity": parity}
