@@ -532,6 +532,8 @@ def main():
                          "the cache marked persisting in L2) instead of cold steps")
     ap.add_argument("--collectives", action="store_true",
                     help="multi-GPU: exchange through NCCL all-gathers instead of peer stores")
+    ap.add_argument("--candidates", action="store_true",
+                    help="multi-GPU, configuration 4: exchange candidate lists instead of histograms")
     ap.add_argument("--no-cfg4", action="store_true",
                     help="skip the configuration-4 strong-scaling record that follows the headline run")
     ap.add_argument("--phases", action="store_true",

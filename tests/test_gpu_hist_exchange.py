@@ -30,6 +30,7 @@ def one_rank(B, Hq, topk, timeout_s=2.0):
     (2, 4, 4, 16384, 512, False),      # one cache shared by two batch rows
     (1, 32, 8, 65536, 4096, False),    # the long-context configuration, shortened
     (2, 8, 4, 9000, 128, True),        # a cache per batch row, group of 2, ragged length
+    (1, 32, 8, 524288, 4096, False),   # a shard of the long-context configuration cut over 2 ranks
 ])
 def test_one_rank_matches_the_single_device_operator(B, Hq, Hkv, N, topk, per_batch):
     from topk_attn_b200 import ops
@@ -50,6 +51,8 @@ def test_one_rank_matches_the_single_device_operator(B, Hq, Hkv, N, topk, per_ba
     assert torch.equal(idx.sort(-1).values, ridx.sort(-1).values)
     res = verify_sharded_step(op, qd, kd, vd, 0)
     assert res["ok"], res
+    if N > 100000:
+        return                                           # the oracle would take minutes
     want = O.topk_sparse_attention(q, k, v, topk, 0.5)[0]
     assert torch.allclose(out.float().cpu(), want.float(), rtol=1e-2, atol=1e-3)
 

@@ -767,8 +767,10 @@ int run_store(const ra_params* p, const Shape& s, int group, bool attend, unsign
     per2 = ceil_div(s.topk, c2);
     chunk2 = ceil_div(ceil_div(s.n, c2), kTileRows) * kTileRows;
     det2 = det_words_for(chunk2);
-    fixed = sx ? select_sharded_fixed_smem_bytes(per2, det2) : select_stored_fixed_smem_bytes(per2, det2);
-    cap2 = fixed < kSmemBudget ? (int)std::min<size_t>(16384, (kSmemBudget - fixed) / 8) : 0;
+    fixed = sx ? select_sharded_fixed_smem_bytes() : select_stored_fixed_smem_bytes(per2, det2);
+    // (the sharded kernel also has a few bytes of static shared memory, which count against the limit)
+    const size_t budget = kSmemBudget - (sx ? 1024 : 0);
+    cap2 = fixed < budget ? (int)std::min<size_t>(16384, (budget - fixed) / 8) : 0;
     if (cap2 >= s.topk + 512 || c2 >= kSelMaxCluster) break;
   }
   if (cap2 < s.topk + 512) return unsupported("topk too large for the stored-score selection");

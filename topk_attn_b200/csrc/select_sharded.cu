@@ -3,22 +3,26 @@
 // key together by a radix select whose histograms -- never the keys or candidates themselves --
 // cross the links, and each rank then attends over the winners among its own tokens.
 //
-// One cluster of CTAs per (batch row, query head) on every rank, all ranks in step per row:
+// One cluster of CTAs per (batch row, query head) on every rank, all ranks in step per row; CTA c
+// owns a contiguous range of the shard's token axis:
 //   round 0   the coarse histogram (top 11 bits, counted during the scan) of this rank goes to
 //             every rank; the sum over ranks gives the bin of the global k-th key;
-//   round 1+  while that bin holds more keys than are still wanted from it, the bin is split by
-//             its next 11 (then 10) bits: one pass over the stored keys of this rank, the counts
-//             summed over the cluster through distributed shared memory, exchanged and summed over
-//             the ranks.  Distinct scores end after round 1; only copies or near-copies of the k-th
-//             score need round 2;
-//   then      keys above the k-th key win; of its copies each rank takes its share in rank order
-//             (lower ranks hold lower token ids), inside a rank in token order.  The winners' V
-//             rows are mixed into an un-normalised partial, which goes to every rank for the
-//             log-sum-exp combine.
+//   collect   the keys of this CTA's range at or above the lower edge of that bin go into a list
+//             in shared memory, in ascending token order (when the bin and everything above it
+//             are too many for a list the collection waits until the k-th key is known);
+//   round 1+  while the bin holds more keys than are still wanted from it, it is split by its next
+//             11 (then 10) bits: counts over the list, summed over the cluster through distributed
+//             shared memory, exchanged and summed over the ranks.  Distinct scores end after
+//             round 1; only copies or near-copies of the k-th score need round 2;
+//   winners   keys above the k-th key win; of its copies each rank takes its share in rank order
+//             (lower ranks hold lower token ids), inside a rank in token order.  Every CTA mixes
+//             the V rows of its own winners, in token order, so that the same inputs always give
+//             the same bits; the CTAs' sums are merged through their maxima into the rank's
+//             un-normalised partial, which goes to every rank for the log-sum-exp combine.
 // An exchange is plain stores into the sender's slot of every rank's receive buffer, one
 // system-scope fence, then the sender's flag word for that (round, row) on every rank; a receiver
 // polls its own flag words, every wait bounded in time (status bit on giving up).  Since all
-// ranks see the same sums they take the same number of rounds.
+// ranks see the same sums they take the same decisions and the same number of rounds.
 //
 // The reference is single-device; the result is defined as equal to the single-device operator on
 // the concatenated cache (retrieval_attn/test_ra.py:88-160 generalised to a global top-k).
@@ -29,8 +33,18 @@ namespace ra {
 namespace {
 
 struct ShardCtrl {
-  int own_above;   // this rank's keys above the current interval
   int red[32];
+  int wt[kSelUnroll][32];      // ordered collection: hits of every warp per segment of an iteration
+  int wbase[kSelUnroll][32];
+  int utot[kSelUnroll];
+  int ftot[32];                // ordered prefix over list flags
+  int n_eq_cta;                // copies of the k-th key in this CTA's list (read by the peers)
+  int n_win;                   // winners of this CTA (read by the peers)
+  uint32_t max_key;            // best winner of this CTA (read by the peers)
+  float l_part;                // read by the peers
+  float lred[32];
+  float o_part[kHeadDim];      // read by the peers
+  float red_o[32][kHeadDim];
 };
 
 // Sum over the block of v; result to every thread.  Two barriers.
@@ -47,6 +61,183 @@ __device__ __forceinline__ int block_sum(int v, int* red, int tid) {
   return s;
 }
 
+// Exclusive prefix of a flag in thread order over the block, and the block's total.  Two barriers.
+__device__ __forceinline__ int block_flag_prefix(bool flag, int* ftot, int tid, int& total) {
+  const int lane = tid & 31, warp = tid >> 5;
+  const unsigned bal = __ballot_sync(0xffffffffu, flag);
+  __syncthreads();
+  if (lane == 0) ftot[warp] = __popc(bal);
+  __syncthreads();
+  int before = 0, tot = 0;
+#pragma unroll
+  for (int w = 0; w < 32; ++w) {
+    const int c = ftot[w];
+    before += w < warp ? c : 0;
+    tot += c;
+  }
+  total = tot;
+  return before + __popc(bal & ((1u << lane) - 1u));
+}
+
+// Keys of the token range [lo, hi) that are >= lo_key into the list, in ascending token order
+// (`take` == nullptr), or -- when a single key value has more copies than a list can hold -- keys
+// above lo_key and the first *take copies of lo_key.  Returns the list length to every thread.
+__device__ __forceinline__ int ordered_collect(const uint32_t* krow, int lo, int hi, uint32_t lo_key,
+                                               const int* take, uint32_t* keys, int* idxs, int cap,
+                                               ShardCtrl* hc, unsigned* status, int tid) {
+  const int lane = tid & 31, warp = tid >> 5;
+  int count = 0;
+  if (take == nullptr) {
+    constexpr int U = kSelUnroll;
+    // one iteration covers U segments of 4 * kSelThreads tokens; list order is (segment, thread, element)
+    for (int base = lo; base < hi; base += kSelThreads * 4 * U) {   // same trip count for all threads
+      uint4 kk[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int i = base + (u * kSelThreads + tid) * 4;
+        kk[u] = i < hi ? ldg128_nc(krow + i) : make_uint4(0u, 0u, 0u, 0u);
+      }
+      int c[U], incl[U], all = 0;
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int i = base + (u * kSelThreads + tid) * 4;
+        const uint32_t kv[4] = {kk[u].x, kk[u].y, kk[u].z, kk[u].w};
+        c[u] = 0;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) c[u] += (i + e < hi && kv[e] >= lo_key);
+        incl[u] = c[u];
+        all += c[u];
+      }
+      if (__ballot_sync(0xffffffffu, all > 0)) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+#pragma unroll
+          for (int off = 1; off < 32; off <<= 1) {
+            const int n = __shfl_up_sync(0xffffffffu, incl[u], off);
+            if (lane >= off) incl[u] += n;
+          }
+        }
+      }
+      if (lane == 31) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) hc->wt[u][warp] = incl[u];
+      }
+      __syncthreads();
+      if (warp < U) {
+        const int v = hc->wt[warp][lane];
+        int inc = v;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+          const int n = __shfl_up_sync(0xffffffffu, inc, off);
+          if (lane >= off) inc += n;
+        }
+        hc->wbase[warp][lane] = inc - v;
+        if (lane == 31) hc->utot[warp] = inc;
+      }
+      __syncthreads();
+      int ubase = count;
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (c[u]) {
+          int pos = ubase + hc->wbase[u][warp] + incl[u] - c[u];
+          const int i = base + (u * kSelThreads + tid) * 4;
+          const uint32_t kv[4] = {kk[u].x, kk[u].y, kk[u].z, kk[u].w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            if (i + e < hi && kv[e] >= lo_key) {
+              if (pos < cap) {
+                keys[pos] = kv[e];
+                idxs[pos] = i + e;
+              } else {
+                atomicOr(status, kStatusOverflow);
+              }
+              ++pos;
+            }
+          }
+        }
+        ubase += hc->utot[u];
+      }
+      count = ubase;
+      __syncthreads();   // the totals are read before the next iteration overwrites them
+    }
+  } else {
+    const int tie_take = *take;
+    int tie_base = 0;   // copies of lo_key seen so far in this CTA
+    for (int base = lo; base < hi; base += kSelThreads * 4) {   // thread order is token order
+      const int i = base + tid * 4;
+      uint4 kk = make_uint4(0u, 0u, 0u, 0u);
+      if (i < hi) kk = ldg128_nc(krow + i);
+      const uint32_t kv[4] = {kk.x, kk.y, kk.z, kk.w};
+      bool pass[4];
+      // copies of lo_key: per-thread count, ordered prefix over threads
+      int mine_eq = 0;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) mine_eq += (i + e < hi && kv[e] == lo_key);
+      int incl = mine_eq;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += n;
+      }
+      __syncthreads();
+      if (lane == 31) hc->ftot[warp] = incl;
+      __syncthreads();
+      int wb = 0, tot = 0;
+#pragma unroll
+      for (int w = 0; w < 32; ++w) {
+        const int cw = hc->ftot[w];
+        wb += w < warp ? cw : 0;
+        tot += cw;
+      }
+      int o = tie_base + wb + incl - mine_eq;
+      int mine_pass = 0;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        pass[e] = i + e < hi && kv[e] > lo_key;
+        if (i + e < hi && kv[e] == lo_key) {
+          pass[e] = o < tie_take;
+          ++o;
+        }
+        mine_pass += pass[e];
+      }
+      tie_base += tot;
+      // positions of the passing keys: the same ordered prefix
+      int pincl = mine_pass;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, pincl, off);
+        if (lane >= off) pincl += n;
+      }
+      __syncthreads();
+      if (lane == 31) hc->ftot[warp] = pincl;
+      __syncthreads();
+      int pb = 0, ptot = 0;
+#pragma unroll
+      for (int w = 0; w < 32; ++w) {
+        const int cw = hc->ftot[w];
+        pb += w < warp ? cw : 0;
+        ptot += cw;
+      }
+      int p = count + pb + pincl - mine_pass;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        if (pass[e]) {
+          if (p < cap) {
+            keys[p] = kv[e];
+            idxs[p] = i + e;
+          } else {
+            atomicOr(status, kStatusOverflow);
+          }
+          ++p;
+        }
+      }
+      count += ptot;
+    }
+  }
+  __syncthreads();
+  return min(count, cap);
+}
+
 }  // namespace
 
 __global__ void __launch_bounds__(kSelThreads, 1)
@@ -57,20 +248,19 @@ select_sharded_kernel(const __grid_constant__ SelectShardedParams P) {
   cg::cluster_group cluster = cg::this_cluster();
   const SelectStoredParams& S = P.s;
   const ShardHist& X = P.x;
-  const int C = S.m.cluster;
+  const MergeArgs& A = S.m;
+  const int C = A.cluster;
   const int crank = (int)cluster.block_rank();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int row = blockIdx.x / C;   // (batch row, query head)
   const int rows = gridDim.x / C;
-  const int bq = row / S.m.hq_total, hq = row % S.m.hq_total;
-  const int k = S.m.topk, cap = S.cap;
+  const int bq = row / A.hq_total, hq = row % A.hq_total, hkv = hq / S.group;
+  const int k = A.topk, cap = S.cap;
   const int G = X.world, me = X.rank;
 
-  const size_t scratch_bytes = select_scratch_bytes(1, S.m.per, S.m.det_words);
-  uint32_t* keys = reinterpret_cast<uint32_t*>(smem + scratch_bytes);
+  uint32_t* keys = reinterpret_cast<uint32_t*>(smem);
   int* idxs = reinterpret_cast<int*>(keys + cap);
-  int* cnt = idxs + cap;
-  int* hist_all = cnt + 4;                   // [kHistBins] sum over the ranks
+  int* hist_all = idxs + cap;                // [kHistBins] sum over the ranks
   int* hist_own = hist_all + kHistBins;      // [kHistBins] this rank
   int* hist_cta = hist_own + kHistBins;      // [kHistBins] this CTA's token range (read by the peers)
   SelCtrl* sc = reinterpret_cast<SelCtrl*>(hist_cta + kHistBins);
@@ -98,7 +288,7 @@ select_sharded_kernel(const __grid_constant__ SelectShardedParams P) {
       const unsigned long long t0 = global_timer_ns();
       while ((int)(ld_acquire_sys(my_flag + flag_of(round, tid)) - epoch) < 0) {
         if (global_timer_ns() - t0 > X.limit_ns) {
-          atomicOr(S.m.status, kStatusTimeout);
+          atomicOr(A.status, kStatusTimeout);
           break;
         }
       }
@@ -117,7 +307,7 @@ select_sharded_kernel(const __grid_constant__ SelectShardedParams P) {
     __syncthreads();
   };
 
-  RA_STAMP(S.m.status, 0);
+  RA_STAMP(A.status, 0);
   // ---- round 0: the coarse histograms counted by the scan
   {
     const uint32_t* hrow = S.hist_ws + (size_t)row * S.nparts * kHistBins;
@@ -127,34 +317,35 @@ select_sharded_kernel(const __grid_constant__ SelectShardedParams P) {
       for (int r = 0; r < G; ++r) X.hist_peer[r][slot_of(0, me) + bin] = s;
     }
     if (tid == 0) {
-      cnt[0] = 0;
       sc->bin = -1; sc->n_above = 0; sc->rem = k; sc->n_in = 0;
-      sc->n_eq_local = 0;
-      hc->own_above = 0;
+      hc->n_eq_cta = 0;
     }
     publish_round(0);
     gather_round(0);
     find_coarse_bin(hist_all, k, sc, tid);
   }
-  RA_STAMP(S.m.status, 1);
+  RA_STAMP(A.status, 1);
   const int lo = min(S.n_tokens, crank * S.chunk), hi = min(S.n_tokens, lo + S.chunk);
   const uint32_t* krow = S.keys_ws + (size_t)row * S.n_pad;
 
   uint32_t lo_key = 0u;
-  int shift = 32, rem = k, n_in = 0, own_above = 0, own_in = 0, last_local = 0, last_bin = 0, last_round = 0;
-  bool everything = sc->bin < 0;   // fewer than k keys on all ranks together: every key wins
+  int shift = 32, rem = k, n_in = 0, own_in = 0, last_bin = 0, last_round = 0;
+  const bool everything = sc->bin < 0;   // fewer than k keys on all ranks together: every key wins
+  bool listed = everything;              // the list is filled before the further rounds
   if (!everything) {
     const int bin = sc->bin;
     lo_key = (uint32_t)bin << kHistShift;
     shift = kHistShift;
     rem = sc->rem;
     n_in = sc->n_in;
-    int part = 0;
-    for (int b = bin + 1 + tid; b < kHistBins; b += kSelThreads) part += hist_own[b];
-    own_above = block_sum(part, hc->red, tid);
     own_in = hist_own[bin];
     last_bin = bin;
+    // all candidates of the row fit in any one list: collect now, split the bin over the list
+    listed = sc->n_above + n_in <= cap;
   }
+  int n_list = 0;
+  if (listed) n_list = ordered_collect(krow, lo, hi, lo_key, nullptr, keys, idxs, cap, hc, A.status, tid);
+  RA_STAMP(A.status, 2);
 
   // ---- further rounds: split the bin while it holds more keys than are wanted from it
   int round = 1;
@@ -164,21 +355,28 @@ select_sharded_kernel(const __grid_constant__ SelectShardedParams P) {
     for (int bin = tid; bin < kHistBins; bin += kSelThreads) hist_cta[bin] = 0;
     __syncthreads();
     const uint32_t span = 1u << shift;
-    for (int base = lo; base < hi; base += kSelThreads * 4 * kSelUnroll) {
-      uint4 kk[kSelUnroll];
-#pragma unroll
-      for (int u = 0; u < kSelUnroll; ++u) {
-        const int i = base + (u * kSelThreads + tid) * 4;
-        kk[u] = i < hi ? ldg128_nc(krow + i) : make_uint4(0u, 0u, 0u, 0u);
+    if (listed) {
+      for (int e = tid; e < n_list; e += kSelThreads) {
+        const uint32_t rel = keys[e] - lo_key;
+        if (rel < span) atomicAdd(&hist_cta[rel >> new_shift], 1);
       }
+    } else {
+      for (int base = lo; base < hi; base += kSelThreads * 4 * kSelUnroll) {
+        uint4 kk[kSelUnroll];
 #pragma unroll
-      for (int u = 0; u < kSelUnroll; ++u) {
-        const int i = base + (u * kSelThreads + tid) * 4;
-        const uint32_t kv[4] = {kk[u].x, kk[u].y, kk[u].z, kk[u].w};
+        for (int u = 0; u < kSelUnroll; ++u) {
+          const int i = base + (u * kSelThreads + tid) * 4;
+          kk[u] = i < hi ? ldg128_nc(krow + i) : make_uint4(0u, 0u, 0u, 0u);
+        }
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const uint32_t rel = kv[e] - lo_key;   // wraps to a huge value below the bin
-          if (i + e < hi && rel < span) atomicAdd(&hist_cta[rel >> new_shift], 1);
+        for (int u = 0; u < kSelUnroll; ++u) {
+          const int i = base + (u * kSelThreads + tid) * 4;
+          const uint32_t kv[4] = {kk[u].x, kk[u].y, kk[u].z, kk[u].w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const uint32_t rel = kv[e] - lo_key;   // wraps to a huge value below the bin
+            if (i + e < hi && rel < span) atomicAdd(&hist_cta[rel >> new_shift], 1);
+          }
         }
       }
     }
@@ -196,18 +394,14 @@ select_sharded_kernel(const __grid_constant__ SelectShardedParams P) {
     const int d = max(sc->bin, 0);
     rem = sc->rem;
     n_in = sc->n_in;
-    int part = 0;
-    for (int b = d + 1 + tid; b < kHistBins; b += kSelThreads) part += hist_own[b];
-    own_above += block_sum(part, hc->red, tid);
     own_in = hist_own[d];
-    last_local = hist_cta[d];
     last_bin = d;
     last_round = round;
     lo_key += (uint32_t)d << new_shift;
     shift = new_shift;
     ++round;
   }
-  RA_STAMP(S.m.status, 2);
+  RA_STAMP(A.status, 3);
 
   // ---- this rank's winners: keys >= lo_key when the whole bin wins, else keys > lo_key and this
   // rank's share of the copies of lo_key (the ranks before it take theirs first)
@@ -218,55 +412,172 @@ select_sharded_kernel(const __grid_constant__ SelectShardedParams P) {
     for (int r = 0; r < me; ++r) before += (int)__ldcg(my_hist + slot_of(last_round, r) + last_bin);
     quota = max(0, min(own_in, rem - before));
   }
-  const int own_total = everything ? min(S.n_tokens, k) : min(own_above + quota, k);
-  const bool tie_mode = !whole_bin && own_above + own_in > cap;   // copies beyond the list's capacity
-  int tie_take = 0;
-  if (tie_mode) {
-    if (tid == 0) sc->n_eq_local = last_local;
+  // this CTA's share of the rank's copies, in CTA (= token) order
+  int cta_take = 0x7fffffff;
+  if (!whole_bin && quota < own_in) {
+    int cta_eq;
+    if (listed) {
+      int mine = 0;
+      for (int e = tid; e < n_list; e += kSelThreads) mine += keys[e] == lo_key;
+      cta_eq = block_sum(mine, hc->red, tid);
+    } else {
+      cta_eq = hist_cta[last_bin];   // the last round counted the single values of this CTA's range
+    }
+    if (tid == 0) hc->n_eq_cta = cta_eq;
     cluster_barrier(cluster, C);
     int before = 0;
-    for (int c = 0; c < crank; ++c) before += *cluster.map_shared_rank(&sc->n_eq_local, c);
-    tie_take = max(0, min(last_local, quota - before));
+    for (int c = 0; c < crank; ++c) before += *cluster.map_shared_rank(&hc->n_eq_cta, c);
+    cta_take = max(0, min(cta_eq, quota - before));
   }
-  if (!tie_mode)
-    collect_candidates(krow, lo, hi, lo_key, keys, idxs, cnt, cap, S.m.status, tid, lane);
-  else
-    collect_candidates_ties(krow, lo, hi, lo_key, tie_take, keys, idxs, cnt, cap, sc, S.m.status, tid, warp, lane);
-  __syncthreads();
-  RA_STAMP(S.m.status, 3);
+  if (!listed)
+    n_list = ordered_collect(krow, lo, hi, lo_key, (whole_bin || cta_take == 0x7fffffff) ? nullptr : &cta_take,
+                             keys, idxs, cap, hc, A.status, tid);
 
-  // ---- winners dealt over the cluster's CTAs, their V rows mixed into this rank's partial
-  MergeArgs A = S.m;
-  A.list_off = 0;
-  A.topk = own_total;
-  A.deal_per = max(1, min(A.per, ceil_div(max(own_total, 1), C)));
-  auto dest = [&](int) {
-    ListDest d;
-    d.valid = true;
-    d.bq = bq;
-    d.hq = hq;
-    d.hkv = hq / S.group;
-    return d;
-  };
-  // With the whole bin winning the threshold passed on is the key just below the bin (nothing in
-  // the list equals it); with copies to share it is the k-th key itself and `quota` copies are taken.
-  uint32_t thr = lo_key;
-  int above = own_above;
-  if (whole_bin) {
-    if (lo_key > 0u) {
-      thr = lo_key - 1u;
-      above = own_total;
-    } else {
-      above = own_total - 0x40000000;   // every copy of key 0 wins as well
+  // ---- winners compacted to the front of the list, still in token order
+  int n_win = 0;
+  uint32_t best = 0u;
+  {
+    int eq_seen = 0;
+    for (int base = 0; base < n_list; base += kSelThreads) {   // same trip count for all threads
+      const int e = base + tid;
+      const uint32_t key = e < n_list ? keys[e] : 0u;
+      const int id = e < n_list ? idxs[e] : 0;
+      bool win = e < n_list && (whole_bin ? key >= lo_key : key > lo_key);
+      if (!whole_bin && cta_take > 0) {
+        const bool eq = e < n_list && key == lo_key;
+        int eq_tot;
+        const int ord = eq_seen + block_flag_prefix(eq, hc->ftot, tid, eq_tot);
+        if (eq && ord < cta_take) win = true;
+        eq_seen += eq_tot;
+      }
+      int tot;
+      const int pos = n_win + block_flag_prefix(win, hc->ftot, tid, tot);
+      // every thread holds its entry in registers: positions at or below the ones just read are free
+      if (win) {
+        keys[pos] = key;
+        idxs[pos] = id;
+        best = max(best, key);
+      }
+      n_win += tot;
+    }
+#pragma unroll
+    for (int off = 16; off; off >>= 1) best = max(best, __shfl_xor_sync(0xffffffffu, best, off));
+    __syncthreads();
+    if (lane == 0) hc->red[warp] = (int)best;
+    __syncthreads();
+    best = (uint32_t)hc->red[lane];
+#pragma unroll
+    for (int off = 16; off; off >>= 1) best = max(best, __shfl_xor_sync(0xffffffffu, best, off));
+  }
+  RA_STAMP(A.status, 4);
+
+  // ---- V rows of this CTA's winners mixed by half-warps, weights against the CTA's best score
+  {
+    const float smax = key_score(best);
+    const __half* vb = A.v + (size_t)bq * A.v_batch_stride + (size_t)hkv * A.v_head_stride + (lane & 15) * 8;
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    float lsum = 0.f;
+    constexpr int UN = 8, NW = kSelThreads / 32;
+    for (int e0 = warp * 2 + (lane >> 4); e0 < n_win; e0 += 2 * NW * UN) {
+      uint4 vv[UN];
+      float w[UN];
+#pragma unroll
+      for (int u = 0; u < UN; ++u) {
+        const int e = e0 + 2 * NW * u;
+        const int id = (e < n_win) ? idxs[e] : -1;
+        if (e < n_win && (unsigned)id >= (unsigned)A.n_tokens) atomicOr(A.status, kStatusBadId);
+        if ((unsigned)id < (unsigned)A.n_tokens) {
+          w[u] = fast_exp2((key_score(keys[e]) - smax) * A.scale_log2e);
+          vv[u] = ldg128_nc(vb + (size_t)id * A.v_token_stride);
+        } else {
+          w[u] = 0.f;
+          vv[u] = make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < UN; ++u) {
+        const uint32_t ww[4] = {vv[u].x, vv[u].y, vv[u].z, vv[u].w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = h2f2(ww[i]);
+          acc[2 * i] = fmaf(w[u], f.x, acc[2 * i]);
+          acc[2 * i + 1] = fmaf(w[u], f.y, acc[2 * i + 1]);
+        }
+        lsum += w[u];
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], 16);
+    lsum += __shfl_xor_sync(0xffffffffu, lsum, 16);
+    if (lane < 16) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) hc->red_o[warp][lane * 8 + i] = acc[i];
+    }
+    if (lane == 0) hc->lred[warp] = lsum;
+    __syncthreads();
+    if (tid < kHeadDim) {
+      float o = 0.f;
+      for (int w = 0; w < NW; ++w) o += hc->red_o[w][tid];
+      hc->o_part[tid] = o;
+      if (tid == 0) {
+        float ls = 0.f;
+        for (int w = 0; w < NW; ++w) ls += hc->lred[w];
+        hc->l_part = ls;
+        hc->max_key = best;
+        hc->n_win = n_win;
+      }
     }
   }
-  cluster_select_attend<1>(cluster, smem, keys, idxs, cnt, cap, A, dest, lo, max(hi - lo, 1), thr, 0, above);
+  RA_STAMP(A.status, 5);
+  cluster_barrier(cluster, C);
 
-  // ---- the partial row goes to every rank (the cluster's CTAs each wrote some of its elements;
-  // the cluster barrier that ends the common code ordered those stores)
+  // ---- the CTAs' sums merged through their maxima: CTA c finishes the dimensions d % C == c
+  {
+    uint32_t mk = 0u;
+    int total_win = 0, win_before = 0;
+    for (int c = 0; c < C; ++c) {
+      const int nw = *cluster.map_shared_rank(&hc->n_win, c);
+      if (nw > 0) mk = max(mk, *cluster.map_shared_rank(&hc->max_key, c));
+      win_before += c < crank ? nw : 0;
+      total_win += nw;
+    }
+    const float smax = key_score(mk);
+    if (tid < kHeadDim && tid % C == crank) {
+      float o = 0.f, lt = 0.f;
+      for (int c = 0; c < C; ++c) {
+        if (*cluster.map_shared_rank(&hc->n_win, c) == 0) continue;
+        const float wc = fast_exp2((key_score(*cluster.map_shared_rank(&hc->max_key, c)) - smax) * A.scale_log2e);
+        o = fmaf(wc, cluster.map_shared_rank(&hc->o_part[0], c)[tid], o);
+        lt = fmaf(wc, *cluster.map_shared_rank(&hc->l_part, c), lt);
+      }
+      float* dstp = A.out_partial + (size_t)row * (kHeadDim + 2);
+      dstp[tid] = o;
+      if (tid == 0) {
+        dstp[kHeadDim] = lt;
+        // a rank without winners for this row weighs nothing in the combine
+        dstp[kHeadDim + 1] = total_win > 0 ? smax * A.sm_scale : -INFINITY;
+      }
+    }
+    if (A.sel_idx) {
+      const size_t dst = (size_t)row * A.list_pitch + win_before;
+      for (int e = tid; e < n_win; e += kSelThreads) {
+        if (win_before + e < A.list_pitch) {
+          A.sel_idx[dst + e] = idxs[e] + A.index_base;
+          if (A.sel_score) A.sel_score[dst + e] = key_score(keys[e]);
+        }
+      }
+    }
+  }
+  cluster_barrier(cluster, C);  // nobody leaves while a peer may still read its shared memory; the
+                                // row's elements written by the other CTAs are visible after it
+  RA_STAMP(A.status, 6);
+
+  // ---- the partial row goes to every rank
   if (P.part.done != nullptr) {
     if (crank == 0) {
-      const float* src = S.m.out_partial + (size_t)row * (kHeadDim + 2);
+      const float* src = A.out_partial + (size_t)row * (kHeadDim + 2);
       for (int i = tid; i < (kHeadDim + 2) * P.part.npeers; i += kSelThreads) {
         const int peer = i / (kHeadDim + 2), j = i - peer * (kHeadDim + 2);
         float* dst = P.part.peer_rows[peer] + (size_t)row * (kHeadDim + 2);
@@ -275,12 +586,11 @@ select_sharded_kernel(const __grid_constant__ SelectShardedParams P) {
     }
     exchange_publish_in_kernel(P.part);
   }
-  RA_STAMP(S.m.status, 9);
+  RA_STAMP(A.status, 7);
 }
 
-size_t select_sharded_fixed_smem_bytes(int per, int det_words) {
-  return select_scratch_bytes(1, per, det_words) + 16 + (size_t)3 * kHistBins * 4 + sizeof(SelCtrl) +
-         sizeof(ShardCtrl) + 128;
+size_t select_sharded_fixed_smem_bytes() {
+  return (size_t)3 * kHistBins * 4 + sizeof(SelCtrl) + sizeof(ShardCtrl) + 256;
 }
 
 cudaError_t launch_select_sharded(const SelectShardedParams& P, int rows, size_t smem, cudaStream_t stream) {

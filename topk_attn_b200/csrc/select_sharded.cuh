@@ -22,7 +22,7 @@ struct SelectShardedParams {
   ExchangeHooks part;     // push of the partial rows (peer_rows, peer_flag, npeers, done), or done == NULL
 };
 
-size_t select_sharded_fixed_smem_bytes(int per, int det_words);
+size_t select_sharded_fixed_smem_bytes();
 cudaError_t launch_select_sharded(const SelectShardedParams& P, int rows, size_t smem, cudaStream_t stream);
 
 }  // namespace ra

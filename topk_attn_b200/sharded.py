@@ -582,8 +582,10 @@ def bench(args, rank: int, local: int, world: int, ClockSampler, measured_peak_g
         w = W.fused_topk_128k_shard(rank, world, device=dev)
     q, k, v = w.q, w.k, w.v
     collectives = bool(getattr(args, "collectives", False))
-    ex = None if collectives else make_peer_exchange(q.size(0), q.size(1), w.topk, dev)
-    op = ShardedTopkAttention(w.topk, w.sm_scale, exchange=ex)
+    hist = strong and not getattr(args, "candidates", False)
+    ex = None if collectives else make_peer_exchange(q.size(0), q.size(1), w.topk, dev, histograms=hist)
+    hist = hist and isinstance(ex, HistExchange)
+    op = ShardedTopkAttention(w.topk, w.sm_scale, exchange=ex, mode="histograms" if hist else "candidates")
     n_local = w.n_tokens
     base = rank * n_local
 
@@ -616,14 +618,15 @@ def bench(args, rank: int, local: int, world: int, ClockSampler, measured_peak_g
     alg = w.algorithmic_bytes()
     heads_q, heads_kv, batch, bkv, topk = q.size(1), k.size(-2), w.batch, w.bkv, w.topk
     peak, kind = measured_peak_gbs()
-    exchange_label = "peer stores + flags" if ex is not None else "nccl all_gather x2"
+    exchange_label = (("histograms over peer stores + flags" if hist else "peer stores + flags")
+                      if ex is not None else "nccl all_gather x2")
 
     long_ctx = None
     if not strong and not args.no_cfg4:
         del w, q, k, v, op, q_dev, ex
         torch.cuda.empty_cache()
         long_ctx = bench_long_context(rank, world, dev, min(args.steps, 100), args.warmup, peak,
-                                      collectives)
+                                      collectives, histograms=not getattr(args, "candidates", False))
 
     if rank == 0:
         achieved = alg / (scan_ms * 1e-3) / 1e9
