@@ -323,41 +323,41 @@ int ra_lse_combine_wait(const float* partials, int32_t num_parts, int32_t rows, 
 
 /* ---- sequence-sharded decode by exchanged histograms (no counterpart in the reference) ----
  * For shards that take the stored-score route (several queries per K row: a GQA group or one cache
- * shared by the batch, one global selection).  Every rank scores its shard once and keeps the
- * scores; the ranks then find the exact global k-th score together by a radix select whose
- * histograms travel between them (2048 counters per row, rank and round; 2 rounds for distinct
- * scores, 3 at most) instead of k candidates per row and rank, and each rank mixes the winners among
- * its own tokens into out_partial ([batch, num_q_heads, 130], as ra_merge_attend writes it), which
- * it also stores into its slot on every rank.  ra_lse_combine_wait on the partial flags then ends
- * the step.  Copies of the k-th score are taken in rank order, inside a rank in token order, so the
- * result equals the single-device operator's on the concatenated cache, ties included.
+ * shared by the batch, one global selection).  One call per rank and step: the rank scores its
+ * shard once and keeps the scores; the ranks then find the exact global k-th score together by a
+ * radix select whose histograms travel between them (2048 counters per row, rank and round; 2
+ * rounds for distinct scores, 3 at most) instead of k candidates per row and rank; each rank mixes
+ * the winners among its own tokens into an un-normalised partial, sends it to every rank, waits
+ * for the others' and writes the full output p->out ([batch, num_q_heads, 128] fp16, the same bits
+ * on every rank).  Copies of the k-th score are taken in rank order, inside a rank in token
+ * order, so the result equals the single-device operator's on the concatenated cache, ties
+ * included.
  *
- * hist_bufs[r] / hist_flags[r] (host arrays of `world` device pointers) are rank r's histogram
- * receive buffer (ra_shard_hist_bytes(rows, world) bytes) and flag words (3 * world * rows 32-bit
- * words, zero before the first step) as mapped in this process; entry `rank` is this rank's own.
- * peer_partials / peer_flags / done_counter / epoch: as in ra_exchange_hooks; out_partial must be
- * peer_partials[rank].  Every wait is bounded by wait_timeout_ns (RA_ERR_DEVICE_TIMEOUT through
- * ra_check_status).  p->out_indices / out_scores, when given ([batch, num_q_heads, topk]), receive
- * this rank's winners (global ids) followed by -1 / -inf entries.  p->out is not written.
+ * bufs[r] (host array of `world` device pointers) is rank r's receive buffer as mapped in this
+ * process (peer-mapped memory: CUDA IPC, virtual memory management, symmetric memory), each of
+ * ra_shard_exchange_bytes(batch * num_q_heads, world) bytes and zero before the first step; entry
+ * `rank` is this rank's own.  All traffic is 8-byte words that carry their step's epoch, polled
+ * by the receiver: no flags, no fences, no collective library.  `epoch` is a device word that
+ * holds 1 before the first step; the call adds one when it has finished (so a captured call can be
+ * replayed).  done_counter is a zero-initialised device word.  Every wait is bounded by
+ * wait_timeout_ns (RA_ERR_DEVICE_TIMEOUT through ra_check_status).  p->out_indices / out_scores,
+ * when given ([batch, num_q_heads, topk], pre-filled by the caller), receive this rank's winners
+ * (global ids) from the start of each row.
  * All ranks must call with the same batch, heads, topk and world; the selection kernel needs
  * batch * num_q_heads * its cluster size CTAs resident at once and refuses shapes beyond that. */
 typedef struct ra_shard_exchange {
   int32_t world, rank;
-  void* const* hist_bufs;
-  void* const* hist_flags;
-  const void* epoch;
+  void* const* bufs;
+  void* epoch;
   uint64_t wait_timeout_ns;
-  float* out_partial;
-  void* const* peer_partials;
-  void* const* peer_flags;
   void* done_counter;
 } ra_shard_exchange;
-size_t ra_shard_hist_bytes(int32_t rows, int32_t world);
-int ra_sharded_topk_partial(const ra_params* p, const ra_shard_exchange* x);
+size_t ra_shard_exchange_bytes(int32_t rows, int32_t world);
+int ra_sharded_topk_attention(const ra_params* p, const ra_shard_exchange* x);
 
 /* Measuring aid: the scoring pass of the stored-score route alone (K streamed once, every score
  * and the coarse histograms into the workspace, nothing selected), for timing the dominant kernel
- * of ra_sharded_topk_partial and of ra_topk_attention on such shapes.  RA_ERR_UNSUPPORTED for
+ * of ra_sharded_topk_attention and of ra_topk_attention on such shapes.  RA_ERR_UNSUPPORTED for
  * shapes that take another route. */
 int ra_score_store_probe(const ra_params* p);
 

@@ -1,8 +1,8 @@
-"""The histogram route of the sharded step (ra_sharded_topk_partial) on one GPU.
+"""The histogram route of the sharded step (ra_sharded_topk_attention) on one GPU.
 
 Its selection kernel waits for the other ranks' histograms inside the kernel, so logical ranks
 cannot be played by separate launches on one device.  Here a single rank runs the whole route (its
-own flags satisfy every wait): scoring, the rounds of the radix select over exchanged histograms,
+own words satisfy every wait): scoring, the rounds of the radix select over exchanged histograms,
 the share-out of copies of the k-th score, the partial and the combine -- against the
 single-device operator and the oracle.  The cross-rank sums are checked on real ranks by
 ``bench.py --gpus N``, which verifies every rank's winners before it times anything.
@@ -45,9 +45,9 @@ def test_one_rank_matches_the_single_device_operator(B, Hq, Hkv, N, topk, per_ba
     torch.cuda.synchronize()
     ops.check_status(DEV)
     assert torch.allclose(out.float(), ref.float(), rtol=1e-2, atol=1e-3)
-    idx, _ = ops.sharded_topk_partial(qd, kd, vd, topk, 0.5, 0, ex, return_indices=True)
-    ops.lse_combine(ex.partials, exchange=ex)            # ends the step
+    out2, idx, _ = ops.sharded_topk_attention(qd, kd, vd, topk, 0.5, 0, ex, return_indices=True)
     torch.cuda.synchronize()
+    assert torch.equal(out2, out)                        # the same bits step after step
     assert torch.equal(idx.sort(-1).values, ridx.sort(-1).values)
     res = verify_sharded_step(op, qd, kd, vd, 0)
     assert res["ok"], res
@@ -69,8 +69,7 @@ def test_copies_of_the_kth_score_are_taken_in_token_order():
     v = torch.randn(N, Hkv, 128, generator=g).half()
     qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
     ex = one_rank(B, Hq, topk)
-    idx, _ = ops.sharded_topk_partial(qd, kd, vd, topk, 1.0, 0, ex, return_indices=True)
-    out = ops.lse_combine(ex.partials, exchange=ex)
+    out, idx, _ = ops.sharded_topk_attention(qd, kd, vd, topk, 1.0, 0, ex, return_indices=True)
     torch.cuda.synchronize()
     ops.check_status(DEV)
     want_ids = torch.arange(topk, dtype=torch.int32, device=DEV).expand(B, Hq, topk)
@@ -105,7 +104,7 @@ def test_a_histogram_that_never_arrives_ends_in_a_timeout():
     bufs = [torch.zeros(words, dtype=torch.int32, device=DEV) for _ in range(2)]
     ex = HistExchange(bufs[0], [b.data_ptr() for b in bufs], 0, 2, B, Hq, topk, timeout_s=0.05)
     q, k, v = rand_case(B, Hq, 2, 8192, False, seed=2)
-    ops.sharded_topk_partial(q.to(DEV), k.to(DEV), v.to(DEV), topk, 1.0, 0, ex)
+    ops.sharded_topk_attention(q.to(DEV), k.to(DEV), v.to(DEV), topk, 1.0, 0, ex)
     torch.cuda.synchronize()
     with pytest.raises(capi.RaError) as err:
         ops.check_status(DEV)
@@ -119,5 +118,5 @@ def test_shapes_outside_the_route_are_refused():
     q, k, v = rand_case(1, 4, 4, 8192, False, seed=1)   # one query per K row
     ex = one_rank(1, 4, 64)
     with pytest.raises(capi.RaError) as err:
-        ops.sharded_topk_partial(q.to(DEV), k.to(DEV), v.to(DEV), 64, 1.0, 0, ex)
+        ops.sharded_topk_attention(q.to(DEV), k.to(DEV), v.to(DEV), 64, 1.0, 0, ex)
     assert err.value.status == capi.RA_ERR_UNSUPPORTED

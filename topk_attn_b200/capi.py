@@ -50,11 +50,8 @@ class RaExchangeHooks(C.Structure):
 class RaShardExchange(C.Structure):
     """Mirror of ``struct ra_shard_exchange``."""
     _fields_ = [
-        ("world", C.c_int32), ("rank", C.c_int32),
-        ("hist_bufs", C.POINTER(C.c_void_p)), ("hist_flags", C.POINTER(C.c_void_p)),
-        ("epoch", C.c_void_p), ("wait_timeout_ns", C.c_uint64), ("out_partial", C.c_void_p),
-        ("peer_partials", C.POINTER(C.c_void_p)), ("peer_flags", C.POINTER(C.c_void_p)),
-        ("done_counter", C.c_void_p),
+        ("world", C.c_int32), ("rank", C.c_int32), ("bufs", C.POINTER(C.c_void_p)),
+        ("epoch", C.c_void_p), ("wait_timeout_ns", C.c_uint64), ("done_counter", C.c_void_p),
     ]
 
 
@@ -205,8 +202,8 @@ def _declare(l: C.CDLL) -> None:
         "ra_stream_read_probe": (C.c_int, [vp, sz, vp, vp]),
         "ra_l2_persist": (C.c_int, [vp, sz, f32, vp]),
         "ra_score_store_probe": (C.c_int, [C.POINTER(RaParams)]),
-        "ra_shard_hist_bytes": (C.c_size_t, [i32, i32]),
-        "ra_sharded_topk_partial": (C.c_int, [C.POINTER(RaParams), C.POINTER(RaShardExchange)]),
+        "ra_shard_exchange_bytes": (C.c_size_t, [i32, i32]),
+        "ra_sharded_topk_attention": (C.c_int, [C.POINTER(RaParams), C.POINTER(RaShardExchange)]),
         "ra_lse_combine_wait": (C.c_int, [vp, i32, i32, vp, vp, i32, vp, C.c_uint64, vp, vp, vp]),
         "ra_exchange_push": (C.c_int, [vp, sz, C.POINTER(vp), C.POINTER(vp), i32, vp, vp, vp]),
         "ra_exchange_wait": (C.c_int, [vp, i32, vp, i32, C.c_uint64, vp, vp]),

@@ -811,25 +811,13 @@ int run_store(const ra_params* p, const Shape& s, int group, bool attend, unsign
   if (sx) {
     SelectShardedParams hp;
     memset(&hp, 0, sizeof hp);
-    m.out_mode = kOutPartial;
-    m.out = nullptr; m.out_lse = nullptr; m.out_partial = sx->out_partial;
     hp.s = qp;
     hp.x.world = sx->world; hp.x.rank = sx->rank;
     hp.x.epoch = static_cast<const unsigned*>(sx->epoch);
+    hp.x.epoch_rw = static_cast<unsigned*>(sx->epoch);
+    hp.x.done = static_cast<unsigned*>(sx->done_counter);
     hp.x.limit_ns = sx->wait_timeout_ns;
-    for (int r = 0; r < sx->world; ++r) {
-      hp.x.hist_peer[r] = static_cast<uint32_t*>(sx->hist_bufs[r]);
-      hp.x.flag_peer[r] = static_cast<unsigned*>(sx->hist_flags[r]);
-    }
-    if (sx->peer_partials) {
-      hp.part.epoch = hp.x.epoch;
-      hp.part.npeers = sx->world;
-      for (int r = 0; r < sx->world; ++r) {
-        hp.part.peer_rows[r] = static_cast<float*>(sx->peer_partials[r]);
-        hp.part.peer_flag[r] = static_cast<unsigned*>(sx->peer_flags[r]);
-      }
-      hp.part.done = static_cast<unsigned*>(sx->done_counter);
-    }
+    for (int r = 0; r < sx->world; ++r) hp.x.buf_peer[r] = static_cast<unsigned long long*>(sx->bufs[r]);
     e = launch_select_sharded(hp, rows, fixed + (size_t)cap2 * 8, stream);
     if (e != cudaSuccess) return cuda_fail(e, "select_sharded launch");
     return RA_OK;
@@ -1476,27 +1464,22 @@ int ra_lse_combine(const float* partials, int32_t num_parts, int32_t rows, void*
   return RA_OK;
 }
 
-size_t ra_shard_hist_bytes(int32_t rows, int32_t world) {
+size_t ra_shard_exchange_bytes(int32_t rows, int32_t world) {
   if (rows < 1 || world < 1) return 0;
-  return (size_t)kShardRounds * world * rows * kHistBins * sizeof(uint32_t);
+  return (size_t)world * rows * (kShardRounds * kHistBins + kPartWords) * sizeof(unsigned long long);
 }
 
-int ra_sharded_topk_partial(const ra_params* p, const ra_shard_exchange* x) {
+int ra_sharded_topk_attention(const ra_params* p, const ra_shard_exchange* x) {
   if (!p || !x) return invalid("params and exchange must be given");
   if (x->world < 1 || x->world > kMaxPeers || x->rank < 0 || x->rank >= x->world)
     return invalid("bad world / rank");
-  if (!x->hist_bufs || !x->hist_flags || !x->epoch || !x->out_partial || x->wait_timeout_ns == 0)
-    return invalid("histogram buffers, flags, epoch word, out_partial and a wait bound are required");
+  if (!x->bufs || !x->epoch || !x->done_counter || x->wait_timeout_ns == 0)
+    return invalid("receive buffers, epoch word, done counter and a wait bound are required");
   for (int r = 0; r < x->world; ++r)
-    if (!x->hist_bufs[r] || !x->hist_flags[r]) return invalid("a rank's histogram buffer or flags are missing");
-  if (x->peer_partials) {
-    if (!x->peer_flags || !x->done_counter) return invalid("peer_partials need peer_flags and done_counter");
-    for (int r = 0; r < x->world; ++r)
-      if (!x->peer_partials[r] || !x->peer_flags[r]) return invalid("a rank's partial slot or flag is missing");
-    if (x->peer_partials[x->rank] != x->out_partial) return invalid("out_partial must be peer_partials[rank]");
-  }
+    if (!x->bufs[r] || (reinterpret_cast<uintptr_t>(x->bufs[r]) & 7u))
+      return invalid("a rank's receive buffer is missing or not 8-byte aligned");
   Checked c;
-  int st = check_params(p, true, false, c);
+  int st = check_params(p, true, true, c);
   if (st != RA_OK) return st;
   Shape s = c.shape;
   s.fused_ok = 1;

@@ -19,10 +19,15 @@
 //             the V rows of its own winners, in token order, so that the same inputs always give
 //             the same bits; the CTAs' sums are merged through their maxima into the rank's
 //             un-normalised partial, which goes to every rank for the log-sum-exp combine.
-// An exchange is plain stores into the sender's slot of every rank's receive buffer, one
-// system-scope fence, then the sender's flag word for that (round, row) on every rank; a receiver
-// polls its own flag words, every wait bounded in time (status bit on giving up).  Since all
-// ranks see the same sums they take the same decisions and the same number of rounds.
+//   combine   the cluster waits for the row's partials of all ranks and writes the final output
+//             (the log-sum-exp merge of baseline_1.cu:549-598 across devices).
+// Everything that crosses the links travels as 8-byte words, each carrying 32 bits of payload and
+// the step's epoch as a tag, written with plain system-scope stores into the sender's slot of
+// every rank's receive buffer.  A receiver polls the words themselves in its own memory until
+// they carry the current epoch (an aligned 8-byte store arrives whole), so there are no separate
+// flags and no fences; every wait is bounded in time (status bit on giving up).  Since all ranks
+// see the same sums they take the same decisions and the same number of rounds.  The last CTA to
+// finish adds one to the epoch word.
 //
 // The reference is single-device; the result is defined as equal to the single-device operator on
 // the concatenated cache (retrieval_attn/test_ra.py:88-160 generalised to a global top-k).
@@ -46,6 +51,29 @@ struct ShardCtrl {
   float o_part[kHeadDim];      // read by the peers
   float red_o[32][kHeadDim];
 };
+
+__device__ __forceinline__ void st_tagged(unsigned long long* p, unsigned epoch, uint32_t payload) {
+  const unsigned long long v = ((unsigned long long)epoch << 32) | payload;
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+// Payload of a tagged word once it carries `epoch`; gives up after limit_ns (status bit, payload of
+// whatever is there).
+__device__ __forceinline__ uint32_t ld_tagged(const unsigned long long* p, unsigned epoch,
+                                              unsigned long long limit_ns, unsigned* status) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  if ((unsigned)(v >> 32) != epoch) {
+    const unsigned long long t0 = global_timer_ns();
+    do {
+      asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+      if (global_timer_ns() - t0 > limit_ns) {
+        atomicOr(status, kStatusTimeout);
+        break;
+      }
+    } while ((unsigned)(v >> 32) != epoch);
+  }
+  return (uint32_t)v;
+}
 
 // Sum over the block of v; result to every thread.  Two barriers.
 __device__ __forceinline__ int block_sum(int v, int* red, int tid) {
@@ -267,37 +295,19 @@ select_sharded_kernel(const __grid_constant__ SelectShardedParams P) {
   ShardCtrl* hc = reinterpret_cast<ShardCtrl*>(sc + 1);
 
   const unsigned epoch = *X.epoch;
-  const uint32_t* my_hist = X.hist_peer[me];      // this rank's receive buffer [round][rank][row][bin]
-  const unsigned* my_flag = X.flag_peer[me];      // [round][rank][row]
+  // this rank's receive buffer: histograms [round][rank][row][bin], then partials [rank][row][132]
+  const unsigned long long* my_buf = X.buf_peer[me];
   const int slice = kHistBins / C, b0 = crank * slice;
   auto slot_of = [&](int round, int r) { return ((size_t)(round * G + r) * rows + row) * kHistBins; };
-  auto flag_of = [&](int round, int r) { return (size_t)(round * G + r) * rows + row; };
+  const size_t part_base = (size_t)kShardRounds * G * rows * kHistBins;
+  auto part_of = [&](int r) { return part_base + ((size_t)r * rows + row) * kPartWords; };
 
-  // Publish this row's round: called by all threads of every CTA of the cluster after their stores
-  // into the peers' slots.  One system-scope fence for the row, then its flag on every rank.
-  auto publish_round = [&](int round) {
-    cluster_barrier(cluster, C);   // every CTA's slice is stored (and nobody still reads hist_cta)
-    if (crank == 0 && warp == 0) {
-      __threadfence_system();   // one fence instruction for the warp, cumulative over the barrier
-      if (lane < G) st_relaxed_sys(X.flag_peer[lane] + flag_of(round, me), epoch);
-    }
-  };
-  // Wait for every rank's flag of this (round, row), then sum the ranks' histograms.
+  // Every rank's histogram of this (round, row), summed; each word is polled until it has arrived.
   auto gather_round = [&](int round) {
-    if (tid < G) {
-      const unsigned long long t0 = global_timer_ns();
-      while ((int)(ld_acquire_sys(my_flag + flag_of(round, tid)) - epoch) < 0) {
-        if (global_timer_ns() - t0 > X.limit_ns) {
-          atomicOr(A.status, kStatusTimeout);
-          break;
-        }
-      }
-    }
-    __syncthreads();
     for (int bin = tid; bin < kHistBins; bin += kSelThreads) {
       int s = 0, own = 0;
       for (int r = 0; r < G; ++r) {
-        const int c = (int)__ldcg(my_hist + slot_of(round, r) + bin);
+        const int c = (int)ld_tagged(my_buf + slot_of(round, r) + bin, epoch, X.limit_ns, A.status);
         s += c;
         if (r == me) own = c;
       }
@@ -314,13 +324,13 @@ select_sharded_kernel(const __grid_constant__ SelectShardedParams P) {
     for (int bin = b0 + tid; bin < b0 + slice; bin += kSelThreads) {
       uint32_t s = 0;
       for (int p = 0; p < S.nparts; ++p) s += hrow[(size_t)p * kHistBins + bin];
-      for (int r = 0; r < G; ++r) X.hist_peer[r][slot_of(0, me) + bin] = s;
+      for (int r = 0; r < G; ++r) st_tagged(X.buf_peer[r] + slot_of(0, me) + bin, epoch, s);
     }
     if (tid == 0) {
       sc->bin = -1; sc->n_above = 0; sc->rem = k; sc->n_in = 0;
       hc->n_eq_cta = 0;
     }
-    publish_round(0);
+    __syncthreads();
     gather_round(0);
     find_coarse_bin(hist_all, k, sc, tid);
   }
@@ -351,6 +361,7 @@ select_sharded_kernel(const __grid_constant__ SelectShardedParams P) {
   int round = 1;
   while (!everything && shift > 0 && n_in != rem) {
     const int new_shift = max(0, shift - 11);
+    if (round > 1) cluster_barrier(cluster, C);   // nobody still reads this CTA's counts of the last round
     __syncthreads();
     for (int bin = tid; bin < kHistBins; bin += kSelThreads) hist_cta[bin] = 0;
     __syncthreads();
@@ -384,9 +395,8 @@ select_sharded_kernel(const __grid_constant__ SelectShardedParams P) {
     for (int bin = b0 + tid; bin < b0 + slice; bin += kSelThreads) {
       int s = 0;
       for (int c = 0; c < C; ++c) s += cluster.map_shared_rank(hist_cta, c)[bin];
-      for (int r = 0; r < G; ++r) X.hist_peer[r][slot_of(round, me) + bin] = (uint32_t)s;
+      for (int r = 0; r < G; ++r) st_tagged(X.buf_peer[r] + slot_of(round, me) + bin, epoch, (uint32_t)s);
     }
-    publish_round(round);
     gather_round(round);
     if (tid == 0) sc->bin = -1;
     __syncthreads();
@@ -409,7 +419,7 @@ select_sharded_kernel(const __grid_constant__ SelectShardedParams P) {
   int quota = own_in;
   if (!whole_bin) {
     int before = 0;
-    for (int r = 0; r < me; ++r) before += (int)__ldcg(my_hist + slot_of(last_round, r) + last_bin);
+    for (int r = 0; r < me; ++r) before += (int)ld_tagged(my_buf + slot_of(last_round, r) + last_bin, epoch, X.limit_ns, A.status);
     quota = max(0, min(own_in, rem - before));
   }
   // this CTA's share of the rank's copies, in CTA (= token) order
@@ -533,7 +543,8 @@ select_sharded_kernel(const __grid_constant__ SelectShardedParams P) {
   RA_STAMP(A.status, 5);
   cluster_barrier(cluster, C);
 
-  // ---- the CTAs' sums merged through their maxima: CTA c finishes the dimensions d % C == c
+  // ---- the CTAs' sums merged through their maxima: CTA c finishes the dimensions d % C == c and
+  // sends them to every rank
   {
     uint32_t mk = 0u;
     int total_win = 0, win_before = 0;
@@ -552,12 +563,15 @@ select_sharded_kernel(const __grid_constant__ SelectShardedParams P) {
         o = fmaf(wc, cluster.map_shared_rank(&hc->o_part[0], c)[tid], o);
         lt = fmaf(wc, *cluster.map_shared_rank(&hc->l_part, c), lt);
       }
-      float* dstp = A.out_partial + (size_t)row * (kHeadDim + 2);
-      dstp[tid] = o;
-      if (tid == 0) {
-        dstp[kHeadDim] = lt;
-        // a rank without winners for this row weighs nothing in the combine
-        dstp[kHeadDim + 1] = total_win > 0 ? smax * A.sm_scale : -INFINITY;
+      // a rank without winners for this row weighs nothing in the combine
+      const float mscaled = total_win > 0 ? smax * A.sm_scale : -INFINITY;
+      for (int r = 0; r < G; ++r) {
+        unsigned long long* dst = X.buf_peer[r] + part_of(me);
+        st_tagged(dst + tid, epoch, __float_as_uint(o));
+        if (tid == 0) {
+          st_tagged(dst + kHeadDim, epoch, __float_as_uint(lt));
+          st_tagged(dst + kHeadDim + 1, epoch, __float_as_uint(mscaled));
+        }
       }
     }
     if (A.sel_idx) {
@@ -570,21 +584,33 @@ select_sharded_kernel(const __grid_constant__ SelectShardedParams P) {
       }
     }
   }
-  cluster_barrier(cluster, C);  // nobody leaves while a peer may still read its shared memory; the
-                                // row's elements written by the other CTAs are visible after it
   RA_STAMP(A.status, 6);
 
-  // ---- the partial row goes to every rank
-  if (P.part.done != nullptr) {
-    if (crank == 0) {
-      const float* src = A.out_partial + (size_t)row * (kHeadDim + 2);
-      for (int i = tid; i < (kHeadDim + 2) * P.part.npeers; i += kSelThreads) {
-        const int peer = i / (kHeadDim + 2), j = i - peer * (kHeadDim + 2);
-        float* dst = P.part.peer_rows[peer] + (size_t)row * (kHeadDim + 2);
-        if (dst != src) dst[j] = __ldcg(src + j);
-      }
+  // ---- combine: out = sum_r w_r o_r / sum_r w_r l_r with w_r = exp(m_r - max m) over the ranks'
+  // partials of this row, in rank order (the same bits on every rank)
+  if (tid < kHeadDim && tid % C == crank) {
+    float m = -INFINITY;
+    for (int r = 0; r < G; ++r)
+      m = fmaxf(m, __uint_as_float(ld_tagged(my_buf + part_of(r) + kHeadDim + 1, epoch, X.limit_ns, A.status)));
+    float o = 0.f, l = 0.f;
+    for (int r = 0; r < G; ++r) {
+      const unsigned long long* src = my_buf + part_of(r);
+      const float lp = __uint_as_float(ld_tagged(src + kHeadDim, epoch, X.limit_ns, A.status));
+      const float mp = __uint_as_float(ld_tagged(src + kHeadDim + 1, epoch, X.limit_ns, A.status));
+      const float w = (lp > 0.f) ? __expf(mp - m) : 0.f;
+      o = fmaf(w, __uint_as_float(ld_tagged(src + tid, epoch, X.limit_ns, A.status)), o);
+      l = fmaf(w, lp, l);
     }
-    exchange_publish_in_kernel(P.part);
+    A.out[(size_t)row * kHeadDim + tid] = __float2half_rn(o / l);
+  }
+  cluster_barrier(cluster, C);  // nobody leaves while a peer may still read its shared memory
+
+  // ---- the step ends: the last CTA to finish advances the epoch (every CTA read it long ago)
+  if (tid == 0) {
+    if (atomicAdd(X.done, 1u) == gridDim.x - 1) {
+      *X.done = 0u;
+      *X.epoch_rw = epoch + 1u;
+    }
   }
   RA_STAMP(A.status, 7);
 }

@@ -6,20 +6,23 @@
 
 namespace ra {
 
-constexpr int kShardRounds = 3;   // 11 + 11 + 10 bits of a key
+constexpr int kShardRounds = 3;    // 11 + 11 + 10 bits of a key
+constexpr int kPartWords = 132;    // a partial row: 128 sums, weight, maximum, 2 words of padding
 
+// Every rank owns one receive buffer of 8-byte words (32 bits of payload under a 32-bit epoch tag):
+//   histograms [kShardRounds][world][rows][kHistBins], then partial rows [world][rows][kPartWords].
 struct ShardHist {
-  uint32_t* hist_peer[kMaxPeers];   // rank p's receive buffer [kShardRounds][world][rows][kHistBins]
-  unsigned* flag_peer[kMaxPeers];   // rank p's flag words    [kShardRounds][world][rows]
+  unsigned long long* buf_peer[kMaxPeers];   // rank p's receive buffer as mapped here
   int world, rank;
   const unsigned* epoch;            // device word holding the current step's epoch
+  unsigned* epoch_rw;               // the same word: the last CTA adds one
+  unsigned* done;                   // zero between launches: CTAs that have finished
   unsigned long long limit_ns;      // bound of every wait
 };
 
 struct SelectShardedParams {
-  SelectStoredParams s;   // s.m.out_partial = this rank's slot of its own partial buffer
+  SelectStoredParams s;   // s.m.out = the final fp16 output of this rank
   ShardHist x;
-  ExchangeHooks part;     // push of the partial rows (peer_rows, peer_flag, npeers, done), or done == NULL
 };
 
 size_t select_sharded_fixed_smem_bytes();

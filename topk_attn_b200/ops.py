@@ -339,33 +339,30 @@ def stored_scores_probe(q: Tensor, k: Tensor, topk: int) -> None:
     capi.check(capi.lib().ra_score_store_probe(C.byref(p)))
 
 
-def sharded_topk_partial(q: Tensor, k: Tensor, v: Tensor, topk: int, sm_scale: float, index_base: int,
-                         exchange, return_indices: bool = False):
-    """This rank's part of a sequence-sharded step by exchanged histograms: scores the shard, finds
+def sharded_topk_attention(q: Tensor, k: Tensor, v: Tensor, topk: int, sm_scale: float, index_base: int,
+                           exchange, out: Optional[Tensor] = None, return_indices: bool = False):
+    """One rank's call of a sequence-sharded step by exchanged histograms: scores the shard, finds
     the global k-th score together with the other ranks, mixes the winners among the shard's
-    tokens into this rank's partial slot and stores it on every rank.  ``exchange`` has the fields
-    of sharded.HistExchange.  With ``return_indices`` also gives (ids int32, scores fp32) [B,Hq,topk]
-    of this rank's winners, padded with (-1, -inf)."""
+    tokens, exchanges the partials and writes the full output [B,Hq,128] fp16.  ``exchange`` has the
+    fields of sharded.HistExchange.  With ``return_indices`` also gives (ids int32, scores fp32)
+    [B,Hq,topk] of this rank's winners, padded with (-1, -inf)."""
     B, Hq, _ = q.shape
+    if out is None:
+        out = torch.empty_like(q)
     idx = sc = None
     if return_indices:
         idx = torch.full((B, Hq, topk), -1, dtype=torch.int32, device=q.device)
         sc = torch.full((B, Hq, topk), float("-inf"), dtype=torch.float32, device=q.device)
-    p = _params(q, k, v, None, topk, sm_scale, 1, index_base, idx, sc, None)
+    p = _params(q, k, v, out, topk, sm_scale, 1, index_base, idx, sc, None)
     n = exchange.world
-    arr = C.c_void_p * n
+    keep = (C.c_void_p * n)(*exchange.ll_ptrs)
     x = capi.RaShardExchange()
     x.world, x.rank = n, exchange.rank
-    keep = (arr(*exchange.hist_ptrs), arr(*exchange.hflag_ptrs), arr(*exchange.dst_p), arr(*exchange.flg_p))
-    x.hist_bufs = C.cast(keep[0], C.POINTER(C.c_void_p))
-    x.hist_flags = C.cast(keep[1], C.POINTER(C.c_void_p))
+    x.bufs = C.cast(keep, C.POINTER(C.c_void_p))
     x.epoch, x.wait_timeout_ns = exchange.epoch.data_ptr(), int(exchange.timeout_s * 1e9)
-    x.out_partial = exchange.partials[exchange.rank].data_ptr()
-    x.peer_partials = C.cast(keep[2], C.POINTER(C.c_void_p))
-    x.peer_flags = C.cast(keep[3], C.POINTER(C.c_void_p))
-    x.done_counter = exchange.done[1:2].data_ptr()
-    capi.check(capi.lib().ra_sharded_topk_partial(C.byref(p), C.byref(x)))
-    return (idx, sc) if return_indices else None
+    x.done_counter = exchange.done[2:3].data_ptr()
+    capi.check(capi.lib().ra_sharded_topk_attention(C.byref(p), C.byref(x)))
+    return (out, idx, sc) if return_indices else out
 
 
 def lse_combine(partials: Tensor, out: Optional[Tensor] = None, exchange=None) -> Tensor:

@@ -56,10 +56,11 @@ class CudaBackend:
         from . import ops
         return ops.lse_combine(partials, exchange=exchange)
 
-    def sharded_partial(self, q: Tensor, k: Tensor, v: Tensor, topk: int, sm_scale: float,
-                        index_base: int, exchange, return_indices: bool = False):
+    def sharded_attention(self, q: Tensor, k: Tensor, v: Tensor, topk: int, sm_scale: float,
+                          index_base: int, exchange, return_indices: bool = False):
         from . import ops
-        return ops.sharded_topk_partial(q, k, v, topk, sm_scale, index_base, exchange, return_indices)
+        return ops.sharded_topk_attention(q, k, v, topk, sm_scale, index_base, exchange,
+                                          return_indices=return_indices)
 
 
 class PeerExchange:
@@ -133,33 +134,33 @@ class PeerExchange:
 
 
 class HistExchange(PeerExchange):
-    """PeerExchange plus the receive buffers of the histogram route (``mode="histograms"`` of
-    ShardedTopkAttention): after the regions of the base class come
+    """PeerExchange plus the receive buffer of the histogram route (``mode="histograms"`` of
+    ShardedTopkAttention): after the regions of the base class come, as 8-byte words that carry
+    their step's epoch,
 
         histograms  [3][world][B*Hq][2048]  slot (round, r) = rank r's counts of that round
-        hflags      [3][world][B*Hq]        epoch of rank r's last push of (round, row)
+        partials    [world][B*Hq][132]      slot r = rank r's un-normalised partial row
 
-    The candidate region keeps its place (a step of the other route can run on the same buffers)."""
+    The other regions keep their place (a step of the candidate route can run on the same
+    buffers)."""
 
-    HIST_ROUNDS, HIST_BINS = 3, 2048
+    HIST_ROUNDS, HIST_BINS, PART_WORDS = 3, 2048, 132
 
     @classmethod
     def layout(cls, world: int, B: int, Hq: int, topk: int):
         base = PeerExchange.layout(world, B, Hq, topk)
         up = lambda x: (x + cls.ALIGN - 1) // cls.ALIGN * cls.ALIGN
-        rows = B * Hq
-        off_h = up(base[-1])
-        off_hf = up(off_h + cls.HIST_ROUNDS * world * rows * cls.HIST_BINS)
-        return base[:-1] + (off_h, off_hf, up(off_hf + cls.HIST_ROUNDS * world * rows))
+        off_ll = up(base[-1])
+        ll_words = 2 * world * B * Hq * (cls.HIST_ROUNDS * cls.HIST_BINS + cls.PART_WORDS)
+        return base[:-1] + (off_ll, up(off_ll + ll_words))
 
     def __init__(self, buf: Tensor, base_ptrs: List[int], rank: int, world: int, B: int, Hq: int,
                  topk: int, timeout_s: float = 2.0):
-        *_, off_h, off_hf, words = self.layout(world, B, Hq, topk)
+        *_, off_ll, words = self.layout(world, B, Hq, topk)
         if buf.numel() < words:
             raise ValueError("buffer too small for the histogram regions")
         super().__init__(buf, base_ptrs, rank, world, B, Hq, topk, timeout_s)
-        self.hist_ptrs = [b + 4 * off_h for b in base_ptrs]
-        self.hflag_ptrs = [b + 4 * off_hf for b in base_ptrs]
+        self.ll_ptrs = [b + 4 * off_ll for b in base_ptrs]
 
 
 def make_peer_exchange(B: int, Hq: int, topk: int, device, group=None,
@@ -196,8 +197,8 @@ class ShardedTopkAttention:
                  exchange: Optional[PeerExchange] = None, mode: str = "candidates"):
         """``mode="histograms"`` (needs a HistExchange and several queries per K row -- a GQA group
         or one cache shared by the batch): the ranks agree on the global k-th score through
-        exchanged histograms of their scores and no candidate lists travel; steps 1-3 above become
-        one call (``ra_sharded_topk_partial``)."""
+        exchanged histograms of their scores and no candidate lists travel; the whole step is one
+        call (``ra_sharded_topk_attention``: two kernels, no flags, no collective)."""
         if mode not in ("candidates", "histograms"):
             raise ValueError("mode must be 'candidates' or 'histograms'")
         if mode == "histograms" and not isinstance(exchange, HistExchange):
@@ -255,8 +256,7 @@ class ShardedTopkAttention:
             index_base = self.rank * n
         cand_sc, cand_idx, partials = self._buffers(B, Hq, q.device)
         if self.mode == "histograms":
-            self.backend.sharded_partial(q, k, v, self.topk, self.sm_scale, index_base, self.exchange)
-            return self.backend.combine(partials, exchange=self.exchange)
+            return self.backend.sharded_attention(q, k, v, self.topk, self.sm_scale, index_base, self.exchange)
         idx, sc = self.local_candidates(q, k, index_base)
         self.exchange_candidates(idx, sc)
         self.merge_and_exchange(cand_sc, cand_idx, partials, v, index_base)
@@ -425,10 +425,8 @@ def verify_sharded_step(op: "ShardedTopkAttention", q: Tensor, k: Tensor, v: Ten
     B, Hq, _ = q.shape
     if op.mode == "histograms":
         # every rank reports its own winners; all of them together must be the global top-k
-        _, _, partials = op._buffers(B, Hq, q.device)
-        idx, sc = op.backend.sharded_partial(q, k, v, op.topk, op.sm_scale, index_base, op.exchange,
-                                             return_indices=True)
-        out = op.backend.combine(partials, exchange=op.exchange)
+        out, idx, sc = op.backend.sharded_attention(q, k, v, op.topk, op.sm_scale, index_base, op.exchange,
+                                                    return_indices=True)
         torch.cuda.synchronize()
         ops.check_status(q.device)
         if op.world > 1 and dist.is_initialized():
