@@ -776,6 +776,8 @@ int run_store(const ra_params* p, const Shape& s, int group, bool attend, unsign
   if (cap2 < s.topk + 512) return unsupported("topk too large for the stored-score selection");
   // the selection CTAs of all ranks wait for one another row by row: all of them must be resident
   if (sx && rows * c2 > sms) return unsupported("too many (batch row, head) pairs for the histogram exchange");
+  // (the ranks' partial rows are staged in the candidate list's shared memory)
+  if (sx && cap2 < sx->world * kPartWords) return unsupported("candidate list too small for this many ranks");
   if (verbose_plan()) {
     static thread_local Shape last_shown = {};
     if ((last_shown < s) || (s < last_shown)) {

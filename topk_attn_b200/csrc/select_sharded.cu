@@ -56,16 +56,21 @@ __device__ __forceinline__ void st_tagged(unsigned long long* p, unsigned epoch,
   const unsigned long long v = ((unsigned long long)epoch << 32) | payload;
   asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
-// Payload of a tagged word once it carries `epoch`; gives up after limit_ns (status bit, payload of
-// whatever is there).
-__device__ __forceinline__ uint32_t ld_tagged(const unsigned long long* p, unsigned epoch,
-                                              unsigned long long limit_ns, unsigned* status) {
+// One look at a tagged word (several of these in a row are in flight together).
+__device__ __forceinline__ unsigned long long ld_word(const unsigned long long* p) {
   unsigned long long v;
-  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p));
+  return v;
+}
+// Payload of a tagged word once it carries `epoch`, given a first look `v` at it; polls on until it
+// does and gives up after limit_ns (status bit, payload of whatever is there).
+__device__ __forceinline__ uint32_t await_tagged(unsigned long long v, const unsigned long long* p,
+                                                 unsigned epoch, unsigned long long limit_ns,
+                                                 unsigned* status) {
   if ((unsigned)(v >> 32) != epoch) {
     const unsigned long long t0 = global_timer_ns();
     do {
-      asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+      v = ld_word(p);
       if (global_timer_ns() - t0 > limit_ns) {
         atomicOr(status, kStatusTimeout);
         break;
@@ -73,6 +78,10 @@ __device__ __forceinline__ uint32_t ld_tagged(const unsigned long long* p, unsig
     } while ((unsigned)(v >> 32) != epoch);
   }
   return (uint32_t)v;
+}
+__device__ __forceinline__ uint32_t ld_tagged(const unsigned long long* p, unsigned epoch,
+                                              unsigned long long limit_ns, unsigned* status) {
+  return await_tagged(ld_word(p), p, epoch, limit_ns, status);
 }
 
 // Sum over the block of v; result to every thread.  Two barriers.
@@ -304,15 +313,34 @@ select_sharded_kernel(const __grid_constant__ SelectShardedParams P) {
 
   // Every rank's histogram of this (round, row), summed; each word is polled until it has arrived.
   auto gather_round = [&](int round) {
-    for (int bin = tid; bin < kHistBins; bin += kSelThreads) {
-      int s = 0, own = 0;
-      for (int r = 0; r < G; ++r) {
-        const int c = (int)ld_tagged(my_buf + slot_of(round, r) + bin, epoch, X.limit_ns, A.status);
-        s += c;
-        if (r == me) own = c;
-      }
-      hist_all[bin] = s;
-      hist_own[bin] = own;
+    // a thread's words of up to 4 ranks x 2 bins are looked at together (one round trip), then
+    // the ones that have not arrived yet are polled
+    constexpr int NB = kHistBins / kSelThreads, RC = 4;
+    int s[NB], own[NB];
+#pragma unroll
+    for (int j = 0; j < NB; ++j) s[j] = own[j] = 0;
+    for (int r0 = 0; r0 < G; r0 += RC) {
+      unsigned long long v[RC][NB];
+#pragma unroll
+      for (int i = 0; i < RC; ++i)
+#pragma unroll
+        for (int j = 0; j < NB; ++j)
+          if (r0 + i < G) v[i][j] = ld_word(my_buf + slot_of(round, r0 + i) + tid + j * kSelThreads);
+#pragma unroll
+      for (int i = 0; i < RC; ++i)
+#pragma unroll
+        for (int j = 0; j < NB; ++j)
+          if (r0 + i < G) {
+            const int c = (int)await_tagged(v[i][j], my_buf + slot_of(round, r0 + i) + tid + j * kSelThreads,
+                                            epoch, X.limit_ns, A.status);
+            s[j] += c;
+            if (r0 + i == me) own[j] = c;
+          }
+    }
+#pragma unroll
+    for (int j = 0; j < NB; ++j) {
+      hist_all[tid + j * kSelThreads] = s[j];
+      hist_own[tid + j * kSelThreads] = own[j];
     }
     __syncthreads();
   };
@@ -587,21 +615,41 @@ select_sharded_kernel(const __grid_constant__ SelectShardedParams P) {
   RA_STAMP(A.status, 6);
 
   // ---- combine: out = sum_r w_r o_r / sum_r w_r l_r with w_r = exp(m_r - max m) over the ranks'
-  // partials of this row, in rank order (the same bits on every rank)
-  if (tid < kHeadDim && tid % C == crank) {
-    float m = -INFINITY;
-    for (int r = 0; r < G; ++r)
-      m = fmaxf(m, __uint_as_float(ld_tagged(my_buf + part_of(r) + kHeadDim + 1, epoch, X.limit_ns, A.status)));
-    float o = 0.f, l = 0.f;
-    for (int r = 0; r < G; ++r) {
-      const unsigned long long* src = my_buf + part_of(r);
-      const float lp = __uint_as_float(ld_tagged(src + kHeadDim, epoch, X.limit_ns, A.status));
-      const float mp = __uint_as_float(ld_tagged(src + kHeadDim + 1, epoch, X.limit_ns, A.status));
-      const float w = (lp > 0.f) ? __expf(mp - m) : 0.f;
-      o = fmaf(w, __uint_as_float(ld_tagged(src + tid, epoch, X.limit_ns, A.status)), o);
-      l = fmaf(w, lp, l);
+  // partials of this row, in rank order (the same bits on every rank).  Every thread fetches its
+  // share of the words into shared memory (the candidate list is no longer needed), all at once.
+  {
+    __syncthreads();   // the list has been written out if it was asked for
+    float* prow = reinterpret_cast<float*>(keys);   // [G][kPartWords]
+    const int nwords = G * kPartWords;
+    for (int w0 = tid; w0 < nwords; w0 += kSelThreads * 4) {
+      unsigned long long v[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int w = w0 + i * kSelThreads;
+        if (w < nwords) v[i] = ld_word(my_buf + part_base + ((size_t)(w / kPartWords) * rows + row) * kPartWords + w % kPartWords);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int w = w0 + i * kSelThreads;
+        if (w < nwords && w % kPartWords < kHeadDim + 2)
+          prow[w] = __uint_as_float(await_tagged(
+              v[i], my_buf + part_base + ((size_t)(w / kPartWords) * rows + row) * kPartWords + w % kPartWords, epoch,
+              X.limit_ns, A.status));
+      }
     }
-    A.out[(size_t)row * kHeadDim + tid] = __float2half_rn(o / l);
+    __syncthreads();
+    if (tid < kHeadDim && tid % C == crank) {
+      float m = -INFINITY;
+      for (int r = 0; r < G; ++r) m = fmaxf(m, prow[r * kPartWords + kHeadDim + 1]);
+      float o = 0.f, l = 0.f;
+      for (int r = 0; r < G; ++r) {
+        const float lp = prow[r * kPartWords + kHeadDim];
+        const float w = (lp > 0.f) ? __expf(prow[r * kPartWords + kHeadDim + 1] - m) : 0.f;
+        o = fmaf(w, prow[r * kPartWords + tid], o);
+        l = fmaf(w, lp, l);
+      }
+      A.out[(size_t)row * kHeadDim + tid] = __float2half_rn(o / l);
+    }
   }
   cluster_barrier(cluster, C);  // nobody leaves while a peer may still read its shared memory
 
