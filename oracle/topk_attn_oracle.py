@@ -361,6 +361,69 @@ def sharded_topk_attention(q: Tensor, k_shards: Sequence[Tensor], v_shards: Sequ
     return lse_combine(o_p, m_p, l_p), gi, gs
 
 
+def ordered_keys(scores: Tensor) -> Tensor:
+    """fp32 scores -> the 32-bit keys (as int64) whose unsigned order is the scores' order: sign
+    bit set for non-negative values, all bits flipped for negative ones."""
+    u = scores.contiguous().view(torch.int32).to(torch.int64) & 0xFFFFFFFF
+    return torch.where(u >= 0x80000000, 0xFFFFFFFF - u, u | 0x80000000)
+
+
+def histogram_select_shard(keys: Tensor, k: int, rank: int, gather_counts) -> Tensor:
+    """Which of this shard's tokens belong to the global top-k, found without moving any key or
+    candidate: a radix select (11 + 11 + 10 bits) whose per-round histograms are the only thing
+    the shards share.  keys int64 [R, n] (ordered_keys of the shard's scores); gather_counts(h) takes
+    this shard's counts int64 [R, bins] and returns every shard's [world, R, bins], rank-major.
+    A round's bin is split further while it holds more keys than are still wanted from it; at
+    the end keys above the k-th key win, and of its copies each shard takes its share in rank
+    order, inside a shard in token order -- the policy of a single device that keeps the lowest ids
+    (shards hold ascending id ranges).  Returns a bool mask [R, n].  The sharded step's result is
+    defined as the single-device operator's on the concatenated cache; this restates how the
+    histogram route reaches it."""
+    R, n = keys.shape
+    lo = torch.zeros(R, dtype=torch.int64)
+    rem = torch.full((R,), k, dtype=torch.int64)
+    n_in = torch.full((R,), -1, dtype=torch.int64)
+    ahead = torch.zeros(R, dtype=torch.int64)      # copies of the bin held by lower ranks
+    shift = 32
+    for bits in (11, 11, 10):
+        active = n_in != rem
+        if not bool(active.any()):
+            break
+        new_shift = shift - bits
+        rel = keys - lo.unsqueeze(-1)
+        inside = (rel >= 0) & (rel < (1 << shift)) & active.unsqueeze(-1)
+        hist = torch.zeros(R, 1 << bits, dtype=torch.int64)
+        hist.scatter_add_(1, torch.where(inside, rel >> new_shift, torch.zeros_like(rel)), inside.to(torch.int64))
+        per_rank = gather_counts(hist)
+        total = per_rank.sum(0)
+        from_top = total.flip(-1).cumsum(-1)
+        for r in range(R):
+            if not bool(active[r]):
+                continue
+            if int(from_top[r, -1]) < int(rem[r]):      # fewer keys than wanted: everything wins
+                n_in[r] = rem[r] = 0
+                lo[r] = 0
+                continue
+            j = int((from_top[r] >= rem[r]).nonzero()[0])
+            d = (1 << bits) - 1 - j
+            above = int(from_top[r, j] - total[r, d])
+            rem[r] -= above
+            n_in[r] = total[r, d]
+            ahead[r] = per_rank[:rank, r, d].sum()
+            lo[r] += d << new_shift
+        shift = new_shift
+    win = keys > lo.unsqueeze(-1)
+    for r in range(R):
+        eq = keys[r] == lo[r] if n_in[r] != rem[r] else keys[r] >= lo[r]
+        if n_in[r] == rem[r]:
+            win[r] |= eq                                 # the whole bin wins
+        else:
+            quota = int(max(0, min(int(eq.sum()), int(rem[r] - ahead[r]))))
+            pos = eq.nonzero().flatten()[:quota]         # token order
+            win[r, pos] = True
+    return win
+
+
 # --------------------------------------------------------------------------------------
 # the three acceptance checks
 # --------------------------------------------------------------------------------------

@@ -46,7 +46,7 @@ def struct_fields(name):
 
 @pytest.mark.parametrize("cname,pyname", [
     ("ra_params", "RaParams"), ("ra_merge_params", "RaMergeParams"),
-    ("ra_exchange_hooks", "RaExchangeHooks"),
+    ("ra_exchange_hooks", "RaExchangeHooks"), ("ra_shard_exchange", "RaShardExchange"),
     ("ra_gather_params", "RaGatherParams"), ("ra_center_params", "RaCenterParams"),
     ("ra_dense_params", "RaDenseParams"), ("ra_two_level_params", "RaTwoLevelParams"),
 ])
@@ -160,3 +160,29 @@ def test_setup_ra_build_ext_leaves_an_importable_module():
     code = ("import torch, retrieval_attention_cpp as m; "
             "assert hasattr(m, 'retrieval_attention_128') and hasattr(m, 'retrieval_attention_pipelined_global_1024')")
     subprocess.check_call([sys.executable, "-c", code], cwd=pkg)
+
+
+def test_histogram_exchange_layout_and_argument_checks():
+    """The receive buffer of the histogram route: its region inside the Python layout is exactly
+    what the library asks for, 8-byte aligned, after the regions of the candidate route; bad
+    arguments are refused before anything touches a device."""
+    import torch
+    from topk_attn_b200 import capi
+    from topk_attn_b200.sharded import HistExchange, PeerExchange
+    lib = capi.lib()
+    for world, B, Hq, topk in [(1, 1, 8, 256), (2, 1, 32, 4096), (8, 4, 32, 2048)]:
+        base = PeerExchange.layout(world, B, Hq, topk)
+        lay = HistExchange.layout(world, B, Hq, topk)
+        off_ll, words = lay[-2], lay[-1]
+        assert lay[:len(base) - 1] == base[:-1] and off_ll >= base[-1] and off_ll % 2 == 0
+        assert (words - off_ll) * 4 >= lib.ra_shard_exchange_bytes(B * Hq, world) > 0
+        buf = torch.zeros(words, dtype=torch.int32)
+        ex = HistExchange(buf, [buf.data_ptr()] * world, 0, world, B, Hq, topk)
+        assert all(p % 8 == 0 for p in ex.ll_ptrs)
+    assert lib.ra_shard_exchange_bytes(0, 2) == 0
+    p, x = capi.RaParams(), capi.RaShardExchange()
+    assert lib.ra_sharded_topk_attention(None, None) == capi.RA_ERR_INVALID_ARGUMENT
+    x.world, x.rank = 2, 2
+    assert lib.ra_sharded_topk_attention(C.byref(p), C.byref(x)) == capi.RA_ERR_INVALID_ARGUMENT
+    x.rank = 1                                               # no buffers, no epoch word
+    assert lib.ra_sharded_topk_attention(C.byref(p), C.byref(x)) == capi.RA_ERR_INVALID_ARGUMENT

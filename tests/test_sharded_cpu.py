@@ -96,3 +96,104 @@ def test_short_shard_is_padded():
     idx, sc = op.local_candidates(q, k, 1000)
     assert idx.shape == (1, 2, 64) and (idx[..., 40:] == -1).all() and torch.isinf(sc[..., 40:]).all()
     assert idx[..., :40].min().item() >= 1000
+
+
+# ---- the histogram route: the ranks agree on the k-th score through histograms only ------------
+
+class OracleHistBackend(OracleBackend):
+    """Stand-in for ra_sharded_topk_attention: the oracle's restatement of the distributed radix
+    select, its histograms gathered over gloo, then partials and the log-sum-exp combine."""
+
+    def sharded_attention(self, q, k, v, topk, sm_scale, index_base, exchange, return_indices=False):
+        B, Hq, _ = q.shape
+        s = O.full_scores(q, k)                                  # [B,Hq,n] fp32
+        n = s.size(-1)
+
+        def gather(h):
+            out = torch.empty(exchange.world, *h.shape, dtype=h.dtype)
+            dist.all_gather_into_tensor(out.view(-1, h.size(-1)), h.contiguous())
+            return out
+
+        win = O.histogram_select_shard(O.ordered_keys(s).view(B * Hq, n), topk, exchange.rank, gather)
+        win = win.view(B, Hq, n)
+        x = torch.where(win, s * sm_scale, torch.full_like(s, float("-inf")))
+        m = x.max(-1).values
+        e = torch.nan_to_num(torch.where(win, torch.exp(x - m.unsqueeze(-1)), torch.zeros_like(x)), nan=0.0)
+        grp = Hq // v.size(-2)
+        part = torch.zeros(B, Hq, 130)
+        for h in range(Hq):
+            part[:, h, :128] = e[:, h] @ v[:, h // grp].float()
+        part[..., 128], part[..., 129] = e.sum(-1), m
+        parts = torch.empty(exchange.world, B, Hq, 130)
+        dist.all_gather_into_tensor(parts.view(-1, Hq, 130), part)
+        out = self.combine(parts)
+        if return_indices:
+            return out, win
+        return out
+
+
+def _hist_worker(rank, world, port, q, k, v, topk, scale, ret):
+    from topk_attn_b200.sharded import HistExchange
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        n = k.size(0) // world
+        B, Hq = q.shape[:2]
+        buf = torch.zeros(HistExchange.layout(world, B, Hq, topk)[-1], dtype=torch.int32)
+        ex = HistExchange(buf, [buf.data_ptr()] * world, rank, world, B, Hq, topk)
+        op = ShardedTopkAttention(topk, scale, backend=OracleHistBackend(), exchange=ex, mode="histograms")
+        out = op.step(q, k[rank * n:(rank + 1) * n].contiguous(), v[rank * n:(rank + 1) * n].contiguous())
+        ret[rank] = out.float()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("topk,n,ties", [(64, 2048, False), (300, 1024, True)])
+def test_two_gloo_ranks_histogram_route_matches_single_device(topk, n, ties):
+    g = torch.Generator().manual_seed(9)
+    q = (torch.randn(1, 8, 128, generator=g) / 11.3).half()
+    k = torch.randn(n, 2, 128, generator=g).half()
+    if ties:
+        k[::3] = k[0]                                   # a third of the keys are copies of one key
+    v = torch.randn(n, 2, 128, generator=g).half()
+    # the single-device operator keeps the lowest ids among copies of the k-th score
+    ids = (-O.full_scores(q, k)).argsort(dim=-1, stable=True)[..., :topk]
+    want = O.gathered_attention(q, k, v, ids, 0.7)
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_hist_worker, args=(2, _free_port(), q, k, v, topk, 0.7, ret), nprocs=2, join=True)
+    for r in range(2):
+        O.check_output(want, ret[r])
+    assert torch.equal(ret[0], ret[1])
+
+
+def test_histogram_select_takes_copies_in_rank_then_token_order():
+    """Three shards in lockstep (threads): the winners are exactly the k best with copies of the
+    k-th score resolved towards the lowest token ids, whole rows of equal scores included."""
+    import threading
+    R, n, k, W = 4, 3000, 257, 3
+    g = torch.Generator().manual_seed(1)
+    s = torch.randn(R, W * n, generator=g)
+    s[0, ::7] = 0.5
+    s[1] = 1.25
+    s[2, 5::2] = s[2, 5]
+    keys = O.ordered_keys(s)
+    assert torch.equal(keys.argsort(dim=-1, stable=True), s.argsort(dim=-1, stable=True))
+    bar, slots, res = threading.Barrier(W), [None] * W, [None] * W
+
+    def run(r):
+        def gather(h):
+            slots[r] = h
+            bar.wait()
+            out = torch.stack(slots)
+            bar.wait()
+            return out
+        res[r] = O.histogram_select_shard(keys[:, r * n:(r + 1) * n], k, r, gather)
+
+    ts = [threading.Thread(target=run, args=(r,)) for r in range(W)]
+    [t.start() for t in ts]
+    [t.join() for t in ts]
+    win = torch.cat(res, -1)
+    ref = torch.zeros_like(win).scatter_(1, (-s).argsort(dim=-1, stable=True)[:, :k], True)
+    assert torch.equal(win, ref)
