@@ -120,3 +120,21 @@ def test_shapes_outside_the_route_are_refused():
     with pytest.raises(capi.RaError) as err:
         ops.sharded_topk_attention(q.to(DEV), k.to(DEV), v.to(DEV), 64, 1.0, 0, ex)
     assert err.value.status == capi.RA_ERR_UNSUPPORTED
+
+
+def test_auto_mode_picks_the_route_from_the_shapes():
+    from topk_attn_b200 import ops
+    from topk_attn_b200.sharded import ShardedTopkAttention
+    q, k, v = rand_case(1, 8, 2, 16384, False, seed=6)       # a GQA group of 4: histograms
+    op = ShardedTopkAttention(128, 1.0, exchange=one_rank(1, 8, 128))
+    out = op.step(q.to(DEV), k.to(DEV), v.to(DEV), 0)
+    assert op.mode == "histograms"
+    assert torch.allclose(out.float(), ops.topk_attention(q.to(DEV), k.to(DEV), v.to(DEV), 128, 1.0).float(),
+                          rtol=1e-2, atol=1e-3)
+    q, k, v = rand_case(1, 4, 4, 16384, False, seed=6)       # one query per K row: candidates
+    op = ShardedTopkAttention(128, 1.0, exchange=one_rank(1, 4, 128))
+    out = op.step(q.to(DEV), k.to(DEV), v.to(DEV), 0)
+    torch.cuda.synchronize()
+    assert op.mode == "candidates"
+    assert torch.allclose(out.float(), ops.topk_attention(q.to(DEV), k.to(DEV), v.to(DEV), 128, 1.0).float(),
+                          rtol=1e-2, atol=1e-3)

@@ -194,13 +194,15 @@ def make_peer_exchange(B: int, Hq: int, topk: int, device, group=None,
 
 class ShardedTopkAttention:
     def __init__(self, topk: int, sm_scale: float = 1.0, group=None, backend=None,
-                 exchange: Optional[PeerExchange] = None, mode: str = "candidates"):
+                 exchange: Optional[PeerExchange] = None, mode: str = "auto"):
         """``mode="histograms"`` (needs a HistExchange and several queries per K row -- a GQA group
         or one cache shared by the batch): the ranks agree on the global k-th score through
         exchanged histograms of their scores and no candidate lists travel; the whole step is one
-        call (``ra_sharded_topk_attention``: two kernels, no flags, no collective)."""
-        if mode not in ("candidates", "histograms"):
-            raise ValueError("mode must be 'candidates' or 'histograms'")
+        call (``ra_sharded_topk_attention``: two kernels, no flags, no collective).
+        ``mode="auto"`` (the default) takes that route whenever the exchange is a HistExchange and
+        the first step's shapes qualify, else the candidate route."""
+        if mode not in ("auto", "candidates", "histograms"):
+            raise ValueError("mode must be 'auto', 'candidates' or 'histograms'")
         if mode == "histograms" and not isinstance(exchange, HistExchange):
             raise ValueError("the histogram route needs a HistExchange")
         self.mode = mode
@@ -231,6 +233,16 @@ class ShardedTopkAttention:
         cand_idx = self._recv[:, 1]
         return cand_sc, cand_idx, self._partials
 
+    def resolve_mode(self, q: Tensor, k: Tensor) -> str:
+        """Settle ``mode="auto"`` from the shapes of a step: the histogram route needs a
+        HistExchange and several queries per K row."""
+        if self.mode == "auto":
+            B, Hq, _ = q.shape
+            shared_queries = (Hq // k.size(-2)) * (B if k.dim() == 3 else 1)
+            self.mode = "histograms" if isinstance(self.exchange, HistExchange) and shared_queries > 1 \
+                else "candidates"
+        return self.mode
+
     def local_candidates(self, q: Tensor, k: Tensor, index_base: int):
         """Local top-k of this shard, padded with (-inf, -1) when the shard holds fewer than k
         tokens."""
@@ -255,6 +267,7 @@ class ShardedTopkAttention:
         if index_base is None:
             index_base = self.rank * n
         cand_sc, cand_idx, partials = self._buffers(B, Hq, q.device)
+        self.resolve_mode(q, k)
         if self.mode == "histograms":
             return self.backend.sharded_attention(q, k, v, self.topk, self.sm_scale, index_base, self.exchange)
         idx, sc = self.local_candidates(q, k, index_base)
@@ -423,7 +436,7 @@ def verify_sharded_step(op: "ShardedTopkAttention", q: Tensor, k: Tensor, v: Ten
     """One untimed sharded step and its check (see verify_winners)."""
     from . import ops
     B, Hq, _ = q.shape
-    if op.mode == "histograms":
+    if op.resolve_mode(q, k) == "histograms":
         # every rank reports its own winners; all of them together must be the global top-k
         out, idx, sc = op.backend.sharded_attention(q, k, v, op.topk, op.sm_scale, index_base, op.exchange,
                                                     return_indices=True)
@@ -558,7 +571,7 @@ def bench_long_context(rank: int, world: int, dev, steps: int, warmup: int, peak
             "us_per_step": per_ms * 1e3, "tokens_per_s": n_total / (per_ms * 1e-3),
             "scan_us": scan_ms * 1e3, "exchange_us": (per_ms - scan_ms) * 1e3,
             "exchange": "none" if world == 1 else (
-                ("histograms over peer stores + flags" if op.mode == "histograms" else "peer stores + flags")
+                ("histograms as tagged words over peer stores" if op.mode == "histograms" else "peer stores + flags")
                 if ex is not None else "nccl all_gather x2"),
             "issued_as": how,
             "roofline_frac_step": alg_per_gpu / (per_ms * 1e-3) / 1e9 / peak_gbs,
@@ -616,7 +629,7 @@ def bench(args, rank: int, local: int, world: int, ClockSampler, measured_peak_g
     alg = w.algorithmic_bytes()
     heads_q, heads_kv, batch, bkv, topk = q.size(1), k.size(-2), w.batch, w.bkv, w.topk
     peak, kind = measured_peak_gbs()
-    exchange_label = (("histograms over peer stores + flags" if hist else "peer stores + flags")
+    exchange_label = (("histograms as tagged words over peer stores" if hist else "peer stores + flags")
                       if ex is not None else "nccl all_gather x2")
 
     long_ctx = None
