@@ -340,7 +340,9 @@ int ra_lse_combine_wait(const float* partials, int32_t num_parts, int32_t rows, 
  * by the receiver: no flags, no fences, no collective library.  `epoch` is a device word that
  * holds 1 before the first step; the call adds one when it has finished (so a captured call can be
  * replayed).  done_counter is a zero-initialised device word.  Every wait is bounded by
- * wait_timeout_ns (RA_ERR_DEVICE_TIMEOUT through ra_check_status).  p->out_indices / out_scores,
+ * wait_timeout_ns (RA_ERR_DEVICE_TIMEOUT through ra_check_status); the timeout bit of the status
+ * block is sticky, and while it is set no kernel of the library waits for a peer again, so a rank
+ * whose peers are gone finishes its step in one time limit.  Clear the status block to resume.  p->out_indices / out_scores,
  * when given ([batch, num_q_heads, topk], pre-filled by the caller), receive this rank's winners
  * (global ids) from the start of each row.
  * All ranks must call with the same batch, heads, topk and world; the selection kernel needs

@@ -51,7 +51,8 @@ exchange_wait_kernel(const unsigned* flags, int n, unsigned* epoch, int advance,
     const unsigned long long t0 = global_timer_ns();
     // flags only grow; compare as a signed distance so that a wrapped counter still works
     while ((int)(ld_acquire_sys(flags + threadIdx.x) - want) < 0) {
-      if (global_timer_ns() - t0 > limit_ns) {
+      // (a wait that ran out earlier left its sticky bit: do not wait a full limit again)
+      if ((*reinterpret_cast<volatile unsigned*>(status) & kStatusTimeout) || global_timer_ns() - t0 > limit_ns) {
         atomicOr(status, kStatusTimeout);
         break;
       }

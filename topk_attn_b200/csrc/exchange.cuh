@@ -47,7 +47,8 @@ __device__ __forceinline__ void exchange_wait_in_kernel(const ExchangeHooks& X, 
     const unsigned want = *X.epoch;
     const unsigned long long t0 = global_timer_ns();
     while ((int)(ld_acquire_sys(X.wait_flags + threadIdx.x) - want) < 0) {
-      if (global_timer_ns() - t0 > X.limit_ns) {
+      // (a wait that ran out earlier left its sticky bit: do not wait a full limit again)
+      if ((*reinterpret_cast<volatile unsigned*>(status) & kStatusTimeout) || global_timer_ns() - t0 > X.limit_ns) {
         atomicOr(status, kStatusTimeout);
         break;
       }

@@ -68,6 +68,9 @@ __device__ __forceinline__ uint32_t await_tagged(unsigned long long v, const uns
                                                  unsigned epoch, unsigned long long limit_ns,
                                                  unsigned* status) {
   if ((unsigned)(v >> 32) != epoch) {
+    // once a wait has run out (the bit is sticky) nothing waits again: a rank that lost its peers
+    // finishes in one time limit, not one per word
+    if (*reinterpret_cast<volatile unsigned*>(status) & kStatusTimeout) return (uint32_t)v;
     const unsigned long long t0 = global_timer_ns();
     do {
       v = ld_word(p);
