@@ -49,10 +49,11 @@ exchange_wait_kernel(const unsigned* flags, int n, unsigned* epoch, int advance,
   const unsigned want = *epoch;
   if ((int)threadIdx.x < n) {
     const unsigned long long t0 = global_timer_ns();
+    // a wait that ran out in an earlier kernel left its sticky bit: do not wait a full limit again
+    const bool gave_up = (*reinterpret_cast<volatile unsigned*>(status) & kStatusTimeout) != 0;
     // flags only grow; compare as a signed distance so that a wrapped counter still works
     while ((int)(ld_acquire_sys(flags + threadIdx.x) - want) < 0) {
-      // (a wait that ran out earlier left its sticky bit: do not wait a full limit again)
-      if ((*reinterpret_cast<volatile unsigned*>(status) & kStatusTimeout) || global_timer_ns() - t0 > limit_ns) {
+      if (gave_up || global_timer_ns() - t0 > limit_ns) {
         atomicOr(status, kStatusTimeout);
         break;
       }

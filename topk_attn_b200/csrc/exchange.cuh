@@ -46,9 +46,10 @@ __device__ __forceinline__ void exchange_wait_in_kernel(const ExchangeHooks& X, 
   if ((int)threadIdx.x < X.wait_n) {
     const unsigned want = *X.epoch;
     const unsigned long long t0 = global_timer_ns();
+    // a wait that ran out in an earlier kernel left its sticky bit: do not wait a full limit again
+    const bool gave_up = (*reinterpret_cast<volatile unsigned*>(status) & kStatusTimeout) != 0;
     while ((int)(ld_acquire_sys(X.wait_flags + threadIdx.x) - want) < 0) {
-      // (a wait that ran out earlier left its sticky bit: do not wait a full limit again)
-      if ((*reinterpret_cast<volatile unsigned*>(status) & kStatusTimeout) || global_timer_ns() - t0 > X.limit_ns) {
+      if (gave_up || global_timer_ns() - t0 > X.limit_ns) {
         atomicOr(status, kStatusTimeout);
         break;
       }

@@ -64,18 +64,19 @@ __device__ __forceinline__ unsigned long long ld_word(const unsigned long long* 
 }
 // Payload of a tagged word once it carries `epoch`, given a first look `v` at it; polls on until it
 // does and gives up after limit_ns (status bit, payload of whatever is there).
+// `gave_up` (per thread; starts out as the sticky timeout bit left by earlier kernels) is set when
+// a wait runs out, and nothing waits once it is set: a rank that lost its peers finishes in one
+// time limit, not one per word.
 __device__ __forceinline__ uint32_t await_tagged(unsigned long long v, const unsigned long long* p,
                                                  unsigned epoch, unsigned long long limit_ns,
-                                                 unsigned* status) {
-  if ((unsigned)(v >> 32) != epoch) {
-    // once a wait has run out (the bit is sticky) nothing waits again: a rank that lost its peers
-    // finishes in one time limit, not one per word
-    if (*reinterpret_cast<volatile unsigned*>(status) & kStatusTimeout) return (uint32_t)v;
+                                                 unsigned* status, bool& gave_up) {
+  if ((unsigned)(v >> 32) != epoch && !gave_up) {
     const unsigned long long t0 = global_timer_ns();
     do {
       v = ld_word(p);
       if (global_timer_ns() - t0 > limit_ns) {
         atomicOr(status, kStatusTimeout);
+        gave_up = true;
         break;
       }
     } while ((unsigned)(v >> 32) != epoch);
@@ -83,8 +84,8 @@ __device__ __forceinline__ uint32_t await_tagged(unsigned long long v, const uns
   return (uint32_t)v;
 }
 __device__ __forceinline__ uint32_t ld_tagged(const unsigned long long* p, unsigned epoch,
-                                              unsigned long long limit_ns, unsigned* status) {
-  return await_tagged(ld_word(p), p, epoch, limit_ns, status);
+                                              unsigned long long limit_ns, unsigned* status, bool& gave_up) {
+  return await_tagged(ld_word(p), p, epoch, limit_ns, status, gave_up);
 }
 
 // Sum over the block of v; result to every thread.  Two barriers.
@@ -307,6 +308,7 @@ select_sharded_kernel(const __grid_constant__ SelectShardedParams P) {
   ShardCtrl* hc = reinterpret_cast<ShardCtrl*>(sc + 1);
 
   const unsigned epoch = *X.epoch;
+  bool gave_up = (*A.status & kStatusTimeout) != 0;   // an earlier kernel's wait ran out: do not wait
   // this rank's receive buffer: histograms [round][rank][row][bin], then partials [rank][row][132]
   const unsigned long long* my_buf = X.buf_peer[me];
   const int slice = kHistBins / C, b0 = crank * slice;
@@ -335,7 +337,7 @@ select_sharded_kernel(const __grid_constant__ SelectShardedParams P) {
         for (int j = 0; j < NB; ++j)
           if (r0 + i < G) {
             const int c = (int)await_tagged(v[i][j], my_buf + slot_of(round, r0 + i) + tid + j * kSelThreads,
-                                            epoch, X.limit_ns, A.status);
+                                            epoch, X.limit_ns, A.status, gave_up);
             s[j] += c;
             if (r0 + i == me) own[j] = c;
           }
@@ -450,7 +452,7 @@ select_sharded_kernel(const __grid_constant__ SelectShardedParams P) {
   int quota = own_in;
   if (!whole_bin) {
     int before = 0;
-    for (int r = 0; r < me; ++r) before += (int)ld_tagged(my_buf + slot_of(last_round, r) + last_bin, epoch, X.limit_ns, A.status);
+    for (int r = 0; r < me; ++r) before += (int)ld_tagged(my_buf + slot_of(last_round, r) + last_bin, epoch, X.limit_ns, A.status, gave_up);
     quota = max(0, min(own_in, rem - before));
   }
   // this CTA's share of the rank's copies, in CTA (= token) order
@@ -637,7 +639,7 @@ select_sharded_kernel(const __grid_constant__ SelectShardedParams P) {
         if (w < nwords && w % kPartWords < kHeadDim + 2)
           prow[w] = __uint_as_float(await_tagged(
               v[i], my_buf + part_base + ((size_t)(w / kPartWords) * rows + row) * kPartWords + w % kPartWords, epoch,
-              X.limit_ns, A.status));
+              X.limit_ns, A.status, gave_up));
       }
     }
     __syncthreads();
