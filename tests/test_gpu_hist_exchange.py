@@ -143,3 +143,83 @@ def test_auto_mode_picks_the_route_from_the_shapes():
     assert op.mode == "candidates"
     assert torch.allclose(out.float(), ops.topk_attention(q.to(DEV), k.to(DEV), v.to(DEV), 128, 1.0).float(),
                           rtol=1e-2, atol=1e-3)
+
+
+def _tied_case(N, Hq=8, Hkv=2, every=7, seed=3):
+    """All query heads equal, every `every`-th key a copy of one vector along the query: the copies
+    score highest and there are far more of them than k, so the k-th score is tied."""
+    g = torch.Generator().manual_seed(seed)
+    q0 = torch.randn(128, generator=g) / 11.3
+    q = q0.expand(1, Hq, 128).contiguous().half()
+    k = torch.randn(N, Hkv, 128, generator=g).half()
+    k[::every] = (q0 * 40).half()
+    v = torch.randn(N, Hkv, 128, generator=g).half()
+    return q, k, v
+
+
+def test_copies_that_fit_the_list_are_shared_out_in_token_order():
+    """4286 copies of the best key, 300 wanted: the copies fit in the candidate lists, the CTAs
+    share them out in token order through the ordinals of the ordered list."""
+    from topk_attn_b200 import ops
+    N, topk = 30000, 300
+    q, k, v = _tied_case(N)
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    ex = one_rank(1, 8, topk)
+    out, idx, _ = ops.sharded_topk_attention(qd, kd, vd, topk, 1.0, 0, ex, return_indices=True)
+    torch.cuda.synchronize()
+    ops.check_status(DEV)
+    want = torch.arange(0, 7 * topk, 7, dtype=torch.int32, device=DEV).expand(1, 8, topk)
+    assert torch.equal(idx.sort(-1).values, want)
+    ref = vd[0:7 * topk:7].float().mean(0)               # equal weights over the first 300 copies
+    for h in range(8):
+        assert torch.allclose(out[0, h].float(), ref[h // 4], rtol=1e-2, atol=2e-3)
+
+
+def _two_rank_worker(rank, world, port, ret):
+    import os
+    import torch.distributed as dist
+    from topk_attn_b200 import ops
+    from topk_attn_b200.sharded import ShardedTopkAttention, make_peer_exchange
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        N, topk = 32768, 2500
+        q, k, v = _tied_case(N)
+        n = N // world
+        qd = q.to(dev)
+        ks, vs = k[rank * n:(rank + 1) * n].contiguous().to(dev), v[rank * n:(rank + 1) * n].contiguous().to(dev)
+        ex = make_peer_exchange(1, 8, topk, dev, histograms=True)
+        assert ex is not None
+        op = ShardedTopkAttention(topk, 1.0, exchange=ex)
+        out, idx, _ = ops.sharded_topk_attention(qd, ks, vs, topk, 1.0, rank * n, ex, return_indices=True)
+        out2 = op.step(qd, ks, vs, rank * n)
+        torch.cuda.synchronize()
+        ops.check_status(dev)
+        ret[rank] = (out.cpu(), out2.cpu(), idx.cpu())
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_real_ranks_share_out_copies_of_the_kth_score():
+    """4682 copies of the best key lie on both ranks, 2500 are wanted: rank 0 takes all 2341 it has,
+    rank 1 the remaining 159 from its lowest ids -- together the lowest k ids, as on one device.
+    NVLS is not involved (plain peer stores); every wait is bounded."""
+    import socket
+    import torch.multiprocessing as mp
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ret = mp.Manager().dict()
+    mp.spawn(_two_rank_worker, args=(2, port, ret), nprocs=2, join=True)
+    topk = 2500
+    assert int((ret[0][2] >= 0).sum(-1)[0, 0]) == 2341 and int((ret[1][2] >= 0).sum(-1)[0, 0]) == 159
+    ids = torch.cat([ret[0][2], ret[1][2]], -1)
+    got = ids.masked_fill(ids < 0, 2 ** 30).sort(-1).values[..., :topk]
+    want = torch.arange(0, 7 * topk, 7, dtype=torch.int32).expand(1, 8, topk)
+    assert torch.equal(got, want)
+    assert (ids >= 0).sum(-1).eq(topk).all()
+    assert torch.equal(ret[0][0], ret[1][0]) and torch.equal(ret[0][0], ret[0][1])
