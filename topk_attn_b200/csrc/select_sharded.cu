@@ -138,30 +138,36 @@ __device__ __forceinline__ int ordered_collect(const uint32_t* krow, int lo, int
         const int i = base + (u * kSelThreads + tid) * 4;
         kk[u] = i < hi ? ldg128_nc(krow + i) : make_uint4(0u, 0u, 0u, 0u);
       }
-      int c[U], incl[U], all = 0;
+      // per-segment hit counts of this thread (at most 4 each), packed: 4 bits per segment in cpk,
+      // and 8 bits per segment in two registers for the warp scans (a warp holds at most 128 hits
+      // of one segment, so the packed fields never carry into each other)
+      static_assert(U == 8, "two registers of four 8-bit fields");
+      uint32_t cpk = 0u, lo4 = 0u, hi4 = 0u;
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const int i = base + (u * kSelThreads + tid) * 4;
         const uint32_t kv[4] = {kk[u].x, kk[u].y, kk[u].z, kk[u].w};
-        c[u] = 0;
+        uint32_t c = 0u;
 #pragma unroll
-        for (int e = 0; e < 4; ++e) c[u] += (i + e < hi && kv[e] >= lo_key);
-        incl[u] = c[u];
-        all += c[u];
+        for (int e = 0; e < 4; ++e) c += (i + e < hi && kv[e] >= lo_key);
+        cpk |= c << (4 * u);
+        if (u < 4) lo4 |= c << (8 * u); else hi4 |= c << (8 * (u - 4));
       }
-      if (__ballot_sync(0xffffffffu, all > 0)) {
+      if (__ballot_sync(0xffffffffu, cpk != 0u)) {
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-#pragma unroll
-          for (int off = 1; off < 32; off <<= 1) {
-            const int n = __shfl_up_sync(0xffffffffu, incl[u], off);
-            if (lane >= off) incl[u] += n;
+        for (int off = 1; off < 32; off <<= 1) {
+          const uint32_t a = __shfl_up_sync(0xffffffffu, lo4, off);
+          const uint32_t b = __shfl_up_sync(0xffffffffu, hi4, off);
+          if (lane >= off) {
+            lo4 += a;
+            hi4 += b;
           }
         }
       }
+      auto incl_of = [&](int u) { return (int)(((u < 4 ? lo4 : hi4) >> (8 * (u & 3))) & 255u); };
       if (lane == 31) {
 #pragma unroll
-        for (int u = 0; u < U; ++u) hc->wt[u][warp] = incl[u];
+        for (int u = 0; u < U; ++u) hc->wt[u][warp] = incl_of(u);
       }
       __syncthreads();
       if (warp < U) {
@@ -179,8 +185,9 @@ __device__ __forceinline__ int ordered_collect(const uint32_t* krow, int lo, int
       int ubase = count;
 #pragma unroll
       for (int u = 0; u < U; ++u) {
-        if (c[u]) {
-          int pos = ubase + hc->wbase[u][warp] + incl[u] - c[u];
+        const int c = (int)((cpk >> (4 * u)) & 15u);
+        if (c) {
+          int pos = ubase + hc->wbase[u][warp] + incl_of(u) - c;
           const int i = base + (u * kSelThreads + tid) * 4;
           const uint32_t kv[4] = {kk[u].x, kk[u].y, kk[u].z, kk[u].w};
 #pragma unroll
@@ -522,7 +529,7 @@ select_sharded_kernel(const __grid_constant__ SelectShardedParams P) {
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = 0.f;
     float lsum = 0.f;
-    constexpr int UN = 8, NW = kSelThreads / 32;
+    constexpr int UN = 4, NW = kSelThreads / 32;
     for (int e0 = warp * 2 + (lane >> 4); e0 < n_win; e0 += 2 * NW * UN) {
       uint4 vv[UN];
       float w[UN];
