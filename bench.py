@@ -537,7 +537,8 @@ def main():
     ap.add_argument("--no-cfg4", action="store_true",
                     help="skip the configuration-4 strong-scaling record that follows the headline run")
     ap.add_argument("--phases", action="store_true",
-                    help="also time the fused kernel with selection / attention switched off")
+                    help="also time the fused kernel with selection / attention switched off; on several "
+                         "GPUs: per-rank phase times of the histogram route's selection kernel (tuning build)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -527,8 +527,43 @@ def time_sharded(op: "ShardedTopkAttention", q: Tensor, k: Tensor, v: Tensor, in
     return t.item() / steps, scan_ms, launches, how
 
 
+HIST_PHASES = ("round 0 (with the wait for the slowest rank's scan)", "collect", "further rounds",
+               "winners", "V mixing", "merge + send", "combine (with the wait for the slowest rank's partial)")
+
+
+def hist_phase_stamps(op: "ShardedTopkAttention", q: Tensor, k: Tensor, v: Tensor, index_base: int,
+                      iters: int = 12) -> Optional[dict]:
+    """Where a step of the histogram route spends its time on every rank: wall-clock stamps that
+    thread 0 of CTA 0 of the selection kernel writes into the status block in the tuning build,
+    median over ``iters`` eager steps with L2 flushed and the ranks aligned by a barrier before
+    each.  Rank 0 gets {phase: [us on rank 0, rank 1, ...]}; a measuring aid, not a timed result."""
+    from . import capi, ops
+    dev = q.device
+    multi = op.world > 1 and dist.is_initialized()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    rows = []
+    with capi.tuning_library():
+        for _ in range(iters):
+            flush.zero_()
+            torch.cuda.synchronize()
+            if multi:
+                dist.barrier()
+            op.step(q, k, v, index_base)
+            torch.cuda.synchronize()
+            t = ops.workspace(256, dev)[:256].view(torch.int64)[4:12].tolist()
+            rows.append([(t[i] - t[i - 1]) / 1e3 for i in range(1, 8)])
+    rows = rows[min(3, iters - 1):]
+    med = torch.tensor([sorted(r[i] for r in rows)[len(rows) // 2] for i in range(7)], device=dev)
+    allm = [torch.empty_like(med) for _ in range(op.world)] if multi else [med]
+    if multi:
+        dist.all_gather(allm, med)
+    if op.rank != 0:
+        return None
+    return {name: [round(float(m[i]), 2) for m in allm] for i, name in enumerate(HIST_PHASES)}
+
+
 def bench_long_context(rank: int, world: int, dev, steps: int, warmup: int, peak_gbs: float,
-                       collectives: bool = False, histograms: bool = True) -> dict:
+                       collectives: bool = False, histograms: bool = True, phases: bool = False) -> dict:
     """Configuration 4 (1 048 576 tokens, 32 query / 8 kv heads, k = 4096) cut over ``world`` ranks:
     total work is fixed, so the time per step should fall as ranks are added (strong scaling).  On
     one GPU the step is the single fused call; on several it is the sharded step.  Every record
@@ -566,7 +601,11 @@ def bench_long_context(rank: int, world: int, dev, steps: int, warmup: int, peak
         per_ms, scan_ms, _, how = time_sharded(op, q, k, v, base, steps, warmup)
     n_total = world * n_local
     alg_per_gpu = w.kv_bytes_scanned() + q.size(1) * w.topk * 128 * 2 // world
-    return {"workload": "cfg4: B1 Hq32/Hkv8 N1048576 k4096, tokens cut over the ranks",
+    stamps = None
+    if phases and world > 1 and op.mode == "histograms":
+        stamps = hist_phase_stamps(op, q, k, v, base)
+    return {"phases_us_per_rank": stamps,
+            "workload": "cfg4: B1 Hq32/Hkv8 N1048576 k4096, tokens cut over the ranks",
             "n_gpus": world, "context": n_total, "context_per_gpu": n_local, "scaling": "strong",
             "us_per_step": per_ms * 1e3, "tokens_per_s": n_total / (per_ms * 1e-3),
             "scan_us": scan_ms * 1e3, "exchange_us": (per_ms - scan_ms) * 1e3,
@@ -632,12 +671,14 @@ def bench(args, rank: int, local: int, world: int, ClockSampler, measured_peak_g
     exchange_label = (("histograms as tagged words over peer stores" if hist else "peer stores + flags")
                       if ex is not None else "nccl all_gather x2")
 
+    stamps = hist_phase_stamps(op, q, k, v, base) if (getattr(args, "phases", False) and hist) else None
     long_ctx = None
     if not strong and not args.no_cfg4:
         del w, q, k, v, op, q_dev, ex
         torch.cuda.empty_cache()
         long_ctx = bench_long_context(rank, world, dev, min(args.steps, 100), args.warmup, peak,
-                                      collectives, histograms=not getattr(args, "candidates", False))
+                                      collectives, histograms=not getattr(args, "candidates", False),
+                                      phases=bool(getattr(args, "phases", False)))
 
     if rank == 0:
         achieved = alg / (scan_ms * 1e-3) / 1e9
@@ -667,6 +708,8 @@ def bench(args, rank: int, local: int, world: int, ClockSampler, measured_peak_g
             "clocks": clocks,
             "parity": parity,
         }
+        if stamps is not None:
+            line["phases_us_per_rank"] = stamps
         if long_ctx is not None:
             line["cfg4_strong"] = long_ctx
         print(json.dumps(line), flush=True)
